@@ -1,0 +1,468 @@
+"""autograph_b200 — B200 (sm_100a) backend for autograph's dense-contraction path.
+
+The product is the C-ABI shared library ``libautograph_b200.so`` (declared in
+``include/autograph_b200.h``).  This package is a thin ctypes front end over it
+that mirrors the reference's operator interface (``dot``, ``Conv2`` / ``Dense`` /
+``MaxPool2`` / ``Relu`` forward and backward, cross-entropy, SGD, and the
+LeNet5-style model object) so that tests and benchmarks read like the
+reference's own.  PyTorch is used only to hold device memory, streams and for
+``torch.distributed``.
+
+There is no CPU fallback: if the library is missing, importing this package
+fails; if there is no B200, creating a :class:`Device` fails.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+from . import _capi
+from ._capi import AgError, lib, lib_path  # noqa: F401
+
+__all__ = ["AgError", "Device", "Model", "lib", "lib_path", "LENET5_SPEC", "WIDE_STACK_SPEC"]
+
+_HERE = Path(__file__).resolve().parent
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    table = {torch.float32: _capi.AG_F32, torch.bfloat16: _capi.AG_BF16, torch.uint8: _capi.AG_U8,
+             torch.uint16: _capi.AG_U16, torch.uint32: _capi.AG_U32}
+    if t not in table:
+        raise AgError(_capi.AG_ERR_DTYPE, f"dtype {t} unimplemented")
+    return table[t]
+
+
+def _ptr(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _conv_options(filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+    o = _capi.ConvOptions()
+    o.filter[0], o.filter[1] = filter
+    o.padding[0], o.padding[1] = padding
+    o.stride[0], o.stride[1] = stride
+    o.dilation[0], o.dilation[1] = dilation
+    return o
+
+
+class Device:
+    """≙ ``Device::builder().index(i).build()``.  Work is submitted to a CUDA
+    stream: by default a torch stream created here, which also becomes torch's
+    current stream for the GPU, so that torch allocations, copies and events are
+    ordered with the library's kernels."""
+
+    def __init__(self, index: int = 0, stream=None):
+        torch = _torch()
+        if not torch.cuda.is_available():
+            raise AgError(_capi.AG_ERR_CUDA, "no CUDA device is visible (there is no CPU fallback)")
+        self.index = index
+        self.torch_device = torch.device("cuda", index)
+        with torch.cuda.device(index):
+            self.stream = stream if stream is not None else torch.cuda.Stream(device=index)
+            torch.cuda.set_stream(self.stream)
+        handle = ctypes.c_void_p()
+        _capi.check(lib().ag_device_create_on_stream(index, ctypes.c_void_p(self.stream.cuda_stream),
+                                                     ctypes.byref(handle)))
+        self._h = handle
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().ag_device_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ≙ device.wait()
+    def wait(self):
+        _capi.check(lib().ag_device_wait(self._h))
+
+    # -- tensors -------------------------------------------------------------
+    def empty(self, shape, dtype):
+        torch = _torch()
+        return torch.empty(shape, dtype=dtype, device=self.torch_device)
+
+    def tensor(self, array, dtype=None):
+        """Host numpy array -> device tensor (≙ Tensor::from(array).into_device(device))."""
+        torch = _torch()
+        t = torch.from_numpy(array)
+        if dtype is not None:
+            t = t.to(dtype)
+        out = t.to(self.torch_device)
+        torch.cuda.current_stream(self.index).synchronize()
+        return out
+
+    def _sync_in(self):
+        # Inputs were produced on torch's current stream; order this stream after it.
+        torch = _torch()
+        self.stream.wait_stream(torch.cuda.current_stream(self.index))
+
+    # -- linalg ----------------------------------------------------------------
+    def gemm(self, alpha, a, b, beta, c):
+        """C = alpha*A.B + beta*C on 2-D (possibly transposed) views; ≙ fn gemm."""
+        if a.dtype != b.dtype:
+            raise AgError(_capi.AG_ERR_DTYPE, "a_scalar_type != b_scalar_type")
+        if a.dtype != c.dtype:
+            raise AgError(_capi.AG_ERR_DTYPE, "a_scalar_type != c_scalar_type")
+        m, k = a.shape
+        k2, n = b.shape
+        m2, n2 = c.shape
+        if m != m2:
+            raise AgError(_capi.AG_ERR_SHAPE, f"a_rows != c_rows, {m} != {m2}")
+        if k != k2:
+            raise AgError(_capi.AG_ERR_SHAPE, f"a_cols != b_rows, {k} != {k2}")
+        if n != n2:
+            raise AgError(_capi.AG_ERR_SHAPE, f"b_cols != c_rows, {n} != {n2}")
+        self._sync_in()
+        _capi.check(lib().ag_gemm(
+            self._h, _dtype_code(a.dtype), m, k, n, ctypes.c_float(alpha),
+            _ptr(a), 0, a.stride(0), a.stride(1), _ptr(b), 0, b.stride(0), b.stride(1),
+            ctypes.c_float(beta), _ptr(c), 0, c.stride(0), c.stride(1)))
+        return c
+
+    def dot(self, a, b):
+        """≙ ``a.dot(&b)`` (Dot for TensorBase / ScalarTensorBase): fresh [m, n] output."""
+        if a.dtype != b.dtype:
+            raise AgError(_capi.AG_ERR_DTYPE,
+                          f"Can not dot tensors of different types {a.dtype} != {b.dtype}!")
+        if a.shape[1] != b.shape[0]:
+            raise AgError(_capi.AG_ERR_SHAPE, f"a_cols != b_rows, {a.shape[1]} != {b.shape[0]}")
+        c = self.empty((a.shape[0], b.shape[1]), a.dtype)
+        return self.gemm(1.0, a, b, 0.0, c)
+
+    # -- convolution -----------------------------------------------------------
+    def conv2_output_shape(self, ih, iw, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+        oh, ow = ctypes.c_int64(), ctypes.c_int64()
+        o = _conv_options(filter, padding, stride, dilation)
+        _capi.check(lib().ag_conv2_output_shape(ih, iw, ctypes.byref(o), ctypes.byref(oh),
+                                                ctypes.byref(ow)))
+        return oh.value, ow.value
+
+    def conv2_forward(self, x, w, bias=None, padding=(0, 0), stride=(1, 1), dilation=(1, 1),
+                      relu=False):
+        bs, ic, ih, iw = x.shape
+        oc, ic2, fh, fw = w.shape
+        if ic != ic2:
+            raise AgError(_capi.AG_ERR_SHAPE, "input channels do not match the weight")
+        o = _conv_options((fh, fw), padding, stride, dilation)
+        oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
+        y = self.empty((bs, oc, oh, ow), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_conv2_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
+                                           ic, ih, iw, _ptr(w.contiguous()), oc, _ptr(bias),
+                                           ctypes.byref(o), int(relu), _ptr(y)))
+        return y
+
+    def conv2_backward_input(self, w, dy, input_hw, padding=(0, 0), stride=(1, 1),
+                             dilation=(1, 1)):
+        oc, ic, fh, fw = w.shape
+        bs = dy.shape[0]
+        ih, iw = input_hw
+        o = _conv_options((fh, fw), padding, stride, dilation)
+        dx = self.empty((bs, ic, ih, iw), dy.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_conv2_backward_input(self._h, _dtype_code(dy.dtype),
+                                                  _ptr(w.contiguous()), oc, ic,
+                                                  _ptr(dy.contiguous()), bs, ih, iw,
+                                                  ctypes.byref(o), _ptr(dx)))
+        return dx
+
+    def conv2_backward_weight(self, x, dy, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1),
+                              beta=0.0, dw=None):
+        bs, ic, ih, iw = x.shape
+        oc = dy.shape[1]
+        o = _conv_options(filter, padding, stride, dilation)
+        if dw is None:
+            dw = self.empty((oc, ic, filter[0], filter[1]), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_conv2_backward_weight(self._h, _dtype_code(x.dtype),
+                                                   _ptr(x.contiguous()), bs, ic, ih, iw,
+                                                   _ptr(dy.contiguous()), oc, ctypes.byref(o),
+                                                   ctypes.c_float(beta), _ptr(dw)))
+        return dw
+
+    def im2col_conv2(self, x, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+        bs, c, ih, iw = x.shape
+        o = _conv_options(filter, padding, stride, dilation)
+        oh, ow = self.conv2_output_shape(ih, iw, filter, padding, stride, dilation)
+        y = self.empty((bs * oh * ow, c * filter[0] * filter[1]), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_im2col_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
+                                          c, ih, iw, ctypes.byref(o), _ptr(y)))
+        return y
+
+    def col2im_conv2(self, x, shape, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+        gh, gw = shape
+        fh, fw = filter
+        rows, cols = x.shape
+        bs, c = rows // (gh * gw), cols // (fh * fw)
+        oh = (gh - 1) * stride[0] + dilation[0] * (fh - 1) + 1 - 2 * padding[0]
+        ow = (gw - 1) * stride[1] + dilation[1] * (fw - 1) + 1 - 2 * padding[1]
+        o = _conv_options(filter, padding, stride, dilation)
+        y = self.empty((bs, c, oh, ow), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_col2im_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
+                                          c, gh, gw, ctypes.byref(o), _ptr(y)))
+        return y
+
+    # -- pooling / relu ----------------------------------------------------------
+    def max_pool2(self, x, size=(2, 2), strides=None):
+        strides = strides or size
+        bs, c, ih, iw = x.shape
+        if ih < size[0] or iw < size[1]:
+            raise AgError(_capi.AG_ERR_SHAPE, "pool window does not fit input")
+        oh, ow = (ih - size[0]) // strides[0] + 1, (iw - size[1]) // strides[1] + 1
+        y = self.empty((bs, c, oh, ow), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_max_pool2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, c,
+                                       ih, iw, size[0], size[1], strides[0], strides[1], _ptr(y)))
+        return y
+
+    def max_pool2_backward(self, x, dy, size=(2, 2), strides=None):
+        """≙ the MaxPool2 backward edge: clone the input, run max_pool2_backward in place."""
+        strides = strides or size
+        dx = x.contiguous().clone()
+        bs, c, ih, iw = dx.shape
+        self._sync_in()
+        _capi.check(lib().ag_max_pool2_backward(self._h, _dtype_code(dx.dtype), _ptr(dx), bs, c, ih,
+                                                iw, size[0], size[1], strides[0], strides[1],
+                                                _ptr(dy.contiguous())))
+        return dx
+
+    def relu(self, x, inplace=False):
+        x = x.contiguous()
+        y = x if inplace else self.empty(x.shape, x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_relu(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(y), x.numel()))
+        return y
+
+    def relu_backward(self, x, dy, inplace=False):
+        x, dy = x.contiguous(), dy.contiguous()
+        dx = dy if inplace else self.empty(dy.shape, dy.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_relu_backward(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(dy),
+                                           _ptr(dx), x.numel()))
+        return dx
+
+    # -- elementwise ---------------------------------------------------------------
+    def scaled_add(self, y, alpha, x):
+        """≙ ``y.scaled_add(alpha, &x)`` (in place on y)."""
+        assert y.is_contiguous() and x.is_contiguous() and x.shape == y.shape
+        self._sync_in()
+        _capi.check(lib().ag_scaled_add(self._h, _dtype_code(y.dtype), ctypes.c_float(alpha),
+                                        _ptr(x), _ptr(y), y.numel()))
+        return y
+
+    def bias_add(self, y, bias):
+        rows, cols = y.shape[0], y.shape[1]
+        inner = y[0, 0].numel() if y.dim() > 2 else 1
+        self._sync_in()
+        _capi.check(lib().ag_bias_add(self._h, _dtype_code(y.dtype), _ptr(y), _ptr(bias), rows,
+                                      cols, inner))
+        return y
+
+    def bias_grad(self, dy, beta=0.0, out=None):
+        rows, cols = dy.shape[0], dy.shape[1]
+        inner = dy[0, 0].numel() if dy.dim() > 2 else 1
+        if out is None:
+            out = self.empty((cols,), dy.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_bias_grad(self._h, _dtype_code(dy.dtype), _ptr(dy.contiguous()), rows,
+                                       cols, inner, ctypes.c_float(beta), _ptr(out)))
+        return out
+
+    # -- criterion -------------------------------------------------------------------
+    def cross_entropy_loss(self, x, t) -> float:
+        bs, classes = x.shape
+        if t.shape[0] != bs:
+            raise AgError(_capi.AG_ERR_SHAPE, f"Expected target with shape [{bs}], found "
+                                              f"[{t.shape[0]}]")
+        loss = ctypes.c_float()
+        self._sync_in()
+        _capi.check(lib().ag_cross_entropy_loss(self._h, _dtype_code(x.dtype), _dtype_code(t.dtype),
+                                                _ptr(x.contiguous()), _ptr(t), bs, classes,
+                                                ctypes.byref(loss)))
+        return loss.value
+
+    def cross_entropy_loss_backward(self, x, t, dy=1.0):
+        bs, classes = x.shape
+        dx = self.empty(x.shape, x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_cross_entropy_loss_backward(
+            self._h, _dtype_code(x.dtype), _dtype_code(t.dtype), _ptr(x.contiguous()), _ptr(t), bs,
+            classes, ctypes.c_float(dy), _ptr(dx)))
+        return dx
+
+    def accuracy(self, x, t) -> int:
+        bs, classes = x.shape
+        out = ctypes.c_uint64()
+        self._sync_in()
+        _capi.check(lib().ag_accuracy(self._h, _dtype_code(x.dtype), _dtype_code(t.dtype),
+                                      _ptr(x.contiguous()), _ptr(t), bs, classes,
+                                      ctypes.byref(out)))
+        return out.value
+
+    # -- optimizer ----------------------------------------------------------------------
+    def sgd_update(self, w, g, lr):
+        self._sync_in()
+        _capi.check(lib().ag_sgd_update(self._h, _dtype_code(w.dtype), _ptr(w), _ptr(g), w.numel(),
+                                        ctypes.c_float(lr)))
+        return w
+
+    def sgd_update_momentum(self, w, g, v, lr, momentum):
+        self._sync_in()
+        _capi.check(lib().ag_sgd_update_momentum(self._h, _dtype_code(w.dtype), _ptr(w), _ptr(g),
+                                                 _ptr(v), w.numel(), ctypes.c_float(lr),
+                                                 ctypes.c_float(momentum)))
+        return w, v
+
+
+# Layer specs shared with the oracle's composition (kind, a, b, c, d, bias).
+LENET5_SPEC = [
+    ("conv", 1, 6, (5, 5), False), ("relu",), ("pool", (2, 2)),
+    ("conv", 6, 16, (5, 5), False), ("relu",), ("pool", (2, 2)),
+    ("flatten",),
+    ("dense", 256, 128, False), ("relu",),
+    ("dense", 128, 84, False), ("relu",),
+    ("dense", 84, 10, True),
+]
+
+WIDE_STACK_SPEC = [
+    ("conv", 3, 64, (3, 3), False), ("relu",), ("pool", (2, 2)),
+    ("conv", 64, 128, (3, 3), False), ("relu",), ("pool", (2, 2)),
+    ("flatten",),
+    ("dense", 128 * 14 * 14, 512, False), ("relu",),
+    ("dense", 512, 10, True),
+]
+
+
+def _c_specs(spec):
+    arr = (_capi.LayerSpec * len(spec))()
+    for i, layer in enumerate(spec):
+        kind = layer[0]
+        s = arr[i]
+        if kind == "conv":
+            s.kind, s.a, s.b, s.c, s.d, s.bias = (_capi.AG_LAYER_CONV2, layer[1], layer[2],
+                                                  layer[3][0], layer[3][1], int(layer[4]))
+        elif kind == "dense":
+            s.kind, s.a, s.b, s.bias = _capi.AG_LAYER_DENSE, layer[1], layer[2], int(layer[3])
+        elif kind == "relu":
+            s.kind = _capi.AG_LAYER_RELU
+        elif kind == "pool":
+            s.kind, s.c, s.d = _capi.AG_LAYER_MAXPOOL2, layer[1][0], layer[1][1]
+        elif kind == "flatten":
+            s.kind = _capi.AG_LAYER_FLATTEN
+        else:
+            raise ValueError(kind)
+    return arr
+
+
+class Model:
+    """≙ ``LeNet5Classifier`` of the reference's bench crate: a chain of layers with
+    resident parameters, ``infer`` and ``train`` steps."""
+
+    def __init__(self, device: Device, spec=None, dtype=None, seed: int = 0):
+        torch = _torch()
+        self.device = device
+        self.spec = spec or LENET5_SPEC
+        self.dtype = dtype or torch.float32
+        arr = _c_specs(self.spec)
+        h = ctypes.c_void_p()
+        _capi.check(lib().ag_model_create(device._h, _dtype_code(self.dtype), arr, len(arr),
+                                          ctypes.c_uint64(seed), ctypes.byref(h)))
+        self._h = h
+        n = ctypes.c_int32()
+        _capi.check(lib().ag_model_parameter_count(self._h, ctypes.byref(n)))
+        self.parameter_lens = []
+        for i in range(n.value):
+            ln = ctypes.c_int64()
+            _capi.check(lib().ag_model_parameter_len(self._h, i, ctypes.byref(ln)))
+            self.parameter_lens.append(ln.value)
+        self.out_features = [l for l in self.spec if l[0] == "dense"][-1][2]
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().ag_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _host(self, array):
+        """numpy float32 array -> contiguous host torch tensor of the model dtype."""
+        torch = _torch()
+        return torch.from_numpy(array).to(self.dtype).contiguous()
+
+    def set_parameters(self, arrays):
+        for i, a in enumerate(arrays):
+            h = self._host(a)
+            assert h.numel() == self.parameter_lens[i]
+            _capi.check(lib().ag_model_set_parameter(self._h, i, _ptr(h)))
+
+    def _fetch(self, fn, index):
+        torch = _torch()
+        h = torch.empty(self.parameter_lens[index], dtype=self.dtype)
+        _capi.check(fn(self._h, index, _ptr(h)))
+        return h.float().numpy()
+
+    def get_parameter(self, index):
+        return self._fetch(lib().ag_model_get_parameter, index)
+
+    def get_gradient(self, index):
+        return self._fetch(lib().ag_model_get_gradient, index)
+
+    def set_sgd(self, momentum=None):
+        _capi.check(lib().ag_model_set_sgd(self._h,
+                                           ctypes.c_float(-1.0 if momentum is None else momentum)))
+
+    def set_grad_scale(self, scale: float):
+        _capi.check(lib().ag_model_set_grad_scale(self._h, ctypes.c_float(scale)))
+
+    def infer(self, x_host, out_host=None):
+        """Host tensor [bs,c,h,w] (model dtype, ideally pinned) -> host logits (blocking)."""
+        torch = _torch()
+        bs, c, h, w = x_host.shape
+        if out_host is None:
+            out_host = torch.empty((bs, self.out_features), dtype=self.dtype)
+        _capi.check(lib().ag_model_infer(self._h, _ptr(x_host), bs, c, h, w, _ptr(out_host)))
+        return out_host
+
+    def forward_device(self, x_dev, out_dev=None):
+        bs, c, h, w = x_dev.shape
+        if out_dev is None:
+            out_dev = self.device.empty((bs, self.out_features), self.dtype)
+        _capi.check(lib().ag_model_forward_device(self._h, _ptr(x_dev), bs, c, h, w, _ptr(out_dev)))
+        return out_dev
+
+    def train_step(self, x_host, t_host, lr) -> float:
+        bs, c, h, w = x_host.shape
+        loss = ctypes.c_float()
+        _capi.check(lib().ag_model_train_step(self._h, _ptr(x_host), _ptr(t_host), bs, c, h, w,
+                                              ctypes.c_float(lr), ctypes.byref(loss)))
+        return loss.value
+
+    def train_forward_backward(self, x_dev, t_dev):
+        """Returns (loss, grad bucket pointer, bucket length); the bucket can be all-reduced."""
+        bs, c, h, w = x_dev.shape
+        loss = ctypes.c_float()
+        bucket = ctypes.c_void_p()
+        length = ctypes.c_int64()
+        _capi.check(lib().ag_model_train_forward_backward(
+            self._h, _ptr(x_dev), _ptr(t_dev), bs, c, h, w, ctypes.byref(loss),
+            ctypes.byref(bucket), ctypes.byref(length)))
+        return loss.value, bucket.value, length.value
+
+    def apply_update(self, lr):
+        _capi.check(lib().ag_model_apply_update(self._h, ctypes.c_float(lr)))

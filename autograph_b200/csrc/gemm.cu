@@ -1,0 +1,85 @@
+// ag_gemm: argument checks and routing to the SIMT tile engine (f32, and bf16
+// shapes the tensor-core kernel does not take) or the tcgen05 kernel (bf16).
+#include "gemm_simt_launch.cuh"
+#include "gemm_tc.cuh"
+
+namespace ag {
+
+template <class T>
+static bool aligned_for_vec(const T *p) {
+    return (reinterpret_cast<uintptr_t>(p) % (4 * sizeof(T))) == 0;
+}
+
+template <class T, bool AK, bool BK_>
+static int gemm_simt_typed(ag_device *dev, int m, int k, int n, float alpha, const T *a,
+                           int64_t rsa, int64_t csa, const T *b, int64_t rsb, int64_t csb,
+                           float beta, T *c, int64_t rsc, int64_t csc) {
+    simt::StridedOperand<T, AK> A{a, rsa, csa, m, k, false};
+    simt::StridedOperand<T, BK_> B{b, csb, rsb, n, k, false};
+    if (AK)
+        A.vec = (csa == 1) && (rsa % 4 == 0 || m == 1) && aligned_for_vec(a);
+    else
+        A.vec = (rsa == 1) && (csa % 4 == 0 || k == 1) && aligned_for_vec(a);
+    if (BK_)
+        B.vec = (rsb == 1) && (csb % 4 == 0 || n == 1) && aligned_for_vec(b);
+    else
+        B.vec = (csb == 1) && (rsb % 4 == 0 || k == 1) && aligned_for_vec(b);
+    simt::StridedEpilogue<T> E{c, rsc, csc, alpha, beta, false, n};
+    E.vec = (csc == 1) && (rsc % 4 == 0 || m == 1) && aligned_for_vec(c);
+    return simt::gemm(dev, m, n, k, A, B, E, /*allow_split=*/true);
+}
+
+template <class T>
+static int gemm_simt_dispatch(ag_device *dev, int m, int k, int n, float alpha, const T *a,
+                              int64_t rsa, int64_t csa, const T *b, int64_t rsb, int64_t csb,
+                              float beta, T *c, int64_t rsc, int64_t csc) {
+    // Walk k fastest when the operand is contiguous along k.
+    bool ak = (csa == 1 && rsa != 1) || (csa == 1 && m == 1);
+    bool bk = (rsb == 1 && csb != 1) || (rsb == 1 && n == 1);
+    if (ak && bk)
+        return gemm_simt_typed<T, true, true>(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta,
+                                              c, rsc, csc);
+    if (ak)
+        return gemm_simt_typed<T, true, false>(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta,
+                                               c, rsc, csc);
+    if (bk)
+        return gemm_simt_typed<T, false, true>(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta,
+                                               c, rsc, csc);
+    return gemm_simt_typed<T, false, false>(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta, c,
+                                            rsc, csc);
+}
+
+}  // namespace ag
+
+using namespace ag;
+
+extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t n,
+                       float alpha, const void *a, int64_t off_a, int64_t rsa, int64_t csa,
+                       const void *b, int64_t off_b, int64_t rsb, int64_t csb, float beta,
+                       void *c, int64_t off_c, int64_t rsc, int64_t csc) {
+    AG_ENTER(dev);
+    AG_REQUIRE(dtype == AG_F32 || dtype == AG_BF16, AG_ERR_DTYPE,
+               "Dot unimplemented for dtype %d", (int)dtype);
+    AG_REQUIRE(m >= 0 && k >= 0 && n >= 0, AG_ERR_SHAPE, "negative dimension m=%lld k=%lld n=%lld",
+               (long long)m, (long long)k, (long long)n);
+    AG_REQUIRE(m < (1ll << 31) && k < (1ll << 31) && n < (1ll << 31) && m * n < (1ll << 40),
+               AG_ERR_LIMIT, "dimension beyond 2^31");
+    if (m == 0 || n == 0) return AG_OK;
+    AG_REQUIRE(c != nullptr && (k == 0 || (a != nullptr && b != nullptr)), AG_ERR_INVALID,
+               "null operand pointer");
+    AG_REQUIRE(off_a >= 0 && off_b >= 0 && off_c >= 0, AG_ERR_INVALID, "negative offset");
+    if (dtype == AG_F32) {
+        return gemm_simt_dispatch<float>(dev, (int)m, (int)k, (int)n, alpha,
+                                         (const float *)a + off_a, rsa, csa,
+                                         (const float *)b + off_b, rsb, csb, beta,
+                                         (float *)c + off_c, rsc, csc);
+    }
+    const __nv_bfloat16 *pa = (const __nv_bfloat16 *)a + off_a;
+    const __nv_bfloat16 *pb = (const __nv_bfloat16 *)b + off_b;
+    __nv_bfloat16 *pc = (__nv_bfloat16 *)c + off_c;
+    if (tc::gemm_bf16_eligible(m, k, n, pa, rsa, csa, pb, rsb, csb, pc, rsc, csc))
+        return tc::gemm_bf16(dev, (int)m, (int)k, (int)n, alpha, pa, rsa, csa, pb, rsb, csb, beta,
+                             pc, rsc, csc);
+    return gemm_simt_dispatch<__nv_bfloat16>(dev, (int)m, (int)k, (int)n, alpha, pa, rsa, csa, pb,
+                                             rsb, csb, beta, pc, rsc, csc);
+}

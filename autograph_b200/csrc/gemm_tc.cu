@@ -1,0 +1,553 @@
+// bf16 GEMM on the Blackwell tensor cores: C = alpha * A.B + beta * C with f32
+// accumulation in tensor memory (TMEM).
+//
+// One persistent CTA per SM walks 128 x 256 output tiles.  Warp roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128x64 (A) and
+//               256x64 (B) bf16 tiles, 128-byte swizzled, into a 4-stage ring
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=256,
+//               K=16) reading the ring through shared-memory descriptors and
+//               accumulating into one of two 256-column TMEM buffers
+//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, alpha/beta,
+//               bf16 rounding, 16-byte global stores -- overlapped with the
+//               main loop of the next tile through the second TMEM buffer
+// All four transpose layouts are handled without copies: an operand that is
+// contiguous along k is loaded as a K-major tile, one contiguous along m / n
+// as an MN-major tile (64-element swizzle atoms, several TMA boxes per stage).
+// Every mbarrier wait is bounded; on expiry the kernel raises a status word,
+// releases TMEM and returns.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "gemm_tc.cuh"
+
+namespace ag {
+namespace tc {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 256;
+constexpr int BLOCK_K = 64;  // 128 bytes of bf16: one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB
+constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int ATOM_BYTES = 64 * BLOCK_K * 2;  // one 64(mn) x 64(k) MN-major box: 8 KiB
+constexpr int TMEM_COLS = 512;                // two 256-column f32 accumulators
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 8;
+
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait: gives up after about two seconds, or as soon as another thread
+// of the CTA has given up, and reports through *abort_flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023u) == 1023u) {
+            if (*abort_flag) return false;
+            uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                 "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem] . B[smem]; one thread issues for the whole CTA.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The mbarrier receives one arrival once every tcgen05 operation issued so far
+// by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     bar)
+                 : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives row
+// (lane base + t), columns [col, col + 32).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride
+// byte offsets (all >> 4), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;  // descriptor version for sm_100
+    d |= 2ull << 61;  // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor for kind::f16: f32 accumulate, bf16 A and B.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn_major, bool b_mn_major, int m, int n) {
+    return (1u << 4)                         // D format: f32
+           | (1u << 7)                       // A format: bf16
+           | (1u << 10)                      // B format: bf16
+           | ((a_mn_major ? 1u : 0u) << 15)  // A major: 0 = K, 1 = MN
+           | ((b_mn_major ? 1u : 0u) << 16)  // B major
+           | ((uint32_t)(n >> 3) << 17)      // N / 8
+           | ((uint32_t)(m >> 4) << 24);     // M / 16
+}
+
+struct Params {
+    int M, N, K;
+    int64_t ldc;
+    float alpha, beta;
+    __nv_bfloat16 *C;
+    int *status;       // device status word (0 = ok)
+    uint32_t lbo_k;    // leading byte offset used for K-major operands
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int &m_blk, int &n_blk) {
+    const int group_size = GROUP_M * num_n;
+    const int g = tile / group_size;
+    const int first_m = g * GROUP_M;
+    const int gm = min(num_m - first_m, GROUP_M);
+    const int r = tile - g * group_size;
+    m_blk = first_m + r % gm;
+    n_blk = r / gm;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles need 1024-byte alignment.
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem + STAGES * A_TILE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    uint64_t *full_bar = bars;                       // [STAGES] TMA -> MMA
+    uint64_t *empty_bar = bars + STAGES;             // [STAGES] MMA -> TMA
+    uint64_t *tmem_full_bar = bars + 2 * STAGES;     // [2] MMA -> epilogue
+    uint64_t *tmem_empty_bar = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+
+    const int num_m = (p.M + BLOCK_M - 1) / BLOCK_M;
+    const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&tmem_full_bar[s]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[s]), 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_base_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                int m_blk, n_blk;
+                tile_coords(tile, num_m, num_n, m_blk, n_blk);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                        atomicExch(p.status, 101);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&full_bar[stage]);
+                    mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                    const uint32_t a_dst = smem_u32(smem_a + stage * A_TILE_BYTES);
+                    const uint32_t b_dst = smem_u32(smem_b + stage * B_TILE_BYTES);
+                    if (A_MN) {
+#pragma unroll
+                        for (int i = 0; i < BLOCK_M / 64; ++i)
+                            tma_load_2d(a_dst + i * ATOM_BYTES, &tmap_a, bar,
+                                        m_blk * BLOCK_M + i * 64, kb * BLOCK_K);
+                    } else {
+                        tma_load_2d(a_dst, &tmap_a, bar, kb * BLOCK_K, m_blk * BLOCK_M);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int i = 0; i < BLOCK_N / 64; ++i)
+                            tma_load_2d(b_dst + i * ATOM_BYTES, &tmap_b, bar,
+                                        n_blk * BLOCK_N + i * 64, kb * BLOCK_K);
+                    } else {
+                        tma_load_2d(b_dst, &tmap_b, bar, kb * BLOCK_K, n_blk * BLOCK_N);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(A_MN, B_MN, BLOCK_M, BLOCK_N);
+            const uint32_t a_lbo = A_MN ? (uint32_t)ATOM_BYTES : p.lbo_k;
+            const uint32_t b_lbo = B_MN ? (uint32_t)ATOM_BYTES : p.lbo_k;
+            const uint32_t a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;  // bytes per UMMA_K
+            const uint32_t b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag)) {
+                    atomicExch(p.status, 102);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
+                        atomicExch(p.status, 103);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(smem_a + stage * A_TILE_BYTES);
+                    const uint32_t b_base = smem_u32(smem_b + stage * B_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t a_desc = make_smem_desc(a_base + k * a_kstep, a_lbo, 1024);
+                        const uint64_t b_desc = make_smem_desc(b_base + k * b_kstep, b_lbo, 1024);
+                        umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&empty_bar[stage]));  // stage reusable once read
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&tmem_full_bar[acc]));  // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------- epilogue
+        const int quarter = warp % 4;  // TMEM lanes this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            int m_blk, n_blk;
+            tile_coords(tile, num_m, num_n, m_blk, n_blk);
+            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag)) {
+                if (lane == 0) atomicExch(p.status, 104);
+                break;
+            }
+            tc_fence_after();
+            const int row = m_blk * BLOCK_M + quarter * 32 + lane;
+            const uint32_t taddr =
+                tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N);
+            __nv_bfloat16 *crow = p.C + (int64_t)row * p.ldc;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BLOCK_N / 32; ++chunk) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + chunk * 32, r);
+                tmem_ld_wait();
+                const int col0 = n_blk * BLOCK_N + chunk * 32;
+                if (row < p.M && col0 < p.N) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int col = col0 + g * 8;
+                        if (col >= p.N) break;
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = p.alpha * __uint_as_float(r[g * 8 + j]);
+                        if (col + 8 <= p.N) {
+                            uint4 *dst = reinterpret_cast<uint4 *>(crow + col);
+                            if (p.beta != 0.f) {
+                                uint4 old = *dst;
+                                const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    v[2 * j] += p.beta * __uint_as_float(o[j] << 16);
+                                    v[2 * j + 1] += p.beta * __uint_as_float(o[j] & 0xffff0000u);
+                                }
+                            }
+                            uint32_t o[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                o[j] = *reinterpret_cast<uint32_t *>(&h);
+                            }
+                            *dst = make_uint4(o[0], o[1], o[2], o[3]);
+                        } else {
+                            for (int j = 0; j < 8 && col + j < p.N; ++j) {
+                                float x = v[j];
+                                if (p.beta != 0.f) x += p.beta * __bfloat162float(crow[col + j]);
+                                crow[col + j] = __float2bfloat16_rn(x);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    // ------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // Loads that were issued before a wait expired may still be landing in
+        // shared memory: give them time before the CTA's memory is released.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+                cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of
+// outer_stride elements; box = box_inner x box_outer, 128-byte swizzle,
+// out-of-range elements read as zero.
+static int make_tmap(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
+                     uint64_t outer_stride, uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    AG_REQUIRE(fn != nullptr, AG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {outer_stride * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    AG_REQUIRE(r == CUDA_SUCCESS, AG_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)",
+               (int)r);
+    return AG_OK;
+}
+
+static bool tc_enabled() {
+    static int v = []() {
+        const char *e = getenv("AG_TC");
+        return (e && e[0] == '0') ? 0 : 1;
+    }();
+    return v != 0;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+bool gemm_bf16_eligible(int64_t m, int64_t k, int64_t n, const __nv_bfloat16 *a, int64_t rsa,
+                        int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
+                        const __nv_bfloat16 *c, int64_t rsc, int64_t csc) {
+    if (!tc_enabled()) return false;
+    if (m < 128 || n < 128 || k < 64) return false;
+    if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return false;
+    const bool a_k = (csa == 1 && rsa % 8 == 0 && rsa >= k);
+    const bool a_m = (rsa == 1 && csa % 8 == 0 && csa >= m);
+    const bool b_k = (rsb == 1 && csb % 8 == 0 && csb >= k);
+    const bool b_n = (csb == 1 && rsb % 8 == 0 && rsb >= n);
+    if (!(a_k || a_m) || !(b_k || b_n)) return false;
+    if (!(csc == 1 && rsc % 8 == 0 && rsc >= n)) return false;
+    return true;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch(ag_device *dev, const CUtensorMap &ta, const CUtensorMap &tb, const Params &p) {
+    auto kernel = gemm_bf16_tc_kernel<A_MN, B_MN>;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES));
+        configured = true;
+    }
+    const int tiles = (int)(ceil_div(p.M, BLOCK_M) * ceil_div(p.N, BLOCK_N));
+    const int grid = tiles < dev->sm_count ? tiles : dev->sm_count;
+    kernel<<<grid, NUM_THREADS, SMEM_BYTES, dev->stream>>>(ta, tb, p);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloat16 *a,
+              int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
+              float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc) {
+    (void)csc;
+    const bool a_mn = !(csa == 1 && rsa % 8 == 0 && rsa >= k);  // else contiguous along m
+    const bool b_mn = !(rsb == 1 && csb % 8 == 0 && csb >= k);  // else contiguous along n
+    CUtensorMap ta, tb;
+    if (a_mn)
+        AG_TRY(make_tmap(&ta, a, (uint64_t)m, (uint64_t)k, (uint64_t)csa, 64, BLOCK_K));
+    else
+        AG_TRY(make_tmap(&ta, a, (uint64_t)k, (uint64_t)m, (uint64_t)rsa, BLOCK_K, BLOCK_M));
+    if (b_mn)
+        AG_TRY(make_tmap(&tb, b, (uint64_t)n, (uint64_t)k, (uint64_t)rsb, 64, BLOCK_K));
+    else
+        AG_TRY(make_tmap(&tb, b, (uint64_t)k, (uint64_t)n, (uint64_t)csb, BLOCK_K, BLOCK_N));
+    Params p;
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.ldc = rsc;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.C = c;
+    p.status = dev->status_dev;
+    p.lbo_k = 0;
+    if (a_mn && b_mn) return launch<true, true>(dev, ta, tb, p);
+    if (a_mn) return launch<true, false>(dev, ta, tb, p);
+    if (b_mn) return launch<false, true>(dev, ta, tb, p);
+    return launch<false, false>(dev, ta, tb, p);
+}
+
+}  // namespace tc
+}  // namespace ag

@@ -1,0 +1,342 @@
+// C ABI of the host-side neural-network layer: model construction, parameter
+// access, inference and training steps (the counterpart of LeNet5Classifier in
+// benches/neural-network-benches/src/autograph_backend.rs:16-85).
+#include <cmath>
+#include <cuda_bf16.h>
+
+#include "../common.cuh"
+#include "nn.hpp"
+
+using namespace autograph;
+
+struct ag_model {
+    ag_device *dev;
+    ag_dtype dtype;
+    Pool pool;  // declared before every tensor so that it is destroyed last
+    std::vector<std::unique_ptr<Layer>> layers;
+    std::vector<Parameter *> params;
+    std::vector<int64_t> offsets;  // element offset of each parameter in the buckets
+    int64_t bucket_len = 0;
+    Tensor values, grads, velocity;  // flat buckets [bucket_len]
+    bool use_momentum = false;
+    float momentum = 0.f;
+    float grad_scale = 1.f;
+    ag_model(ag_device *d, ag_dtype t) : dev(d), dtype(t), pool(d) {}
+};
+
+namespace {
+
+// splitmix64: the seeded stream behind the default initialiser.
+struct Rng {
+    uint64_t s;
+    uint64_t next() {
+        uint64_t z = (s += 0x9e3779b97f4a7c15ull);
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+        return z ^ (z >> 31);
+    }
+    float uniform(float a) {  // U[-a, a)
+        float u = (float)(next() >> 40) * (1.0f / 16777216.0f);
+        return -a + 2.f * a * u;
+    }
+};
+
+void fill_uniform(ag_model *m, Tensor &dst, float a, Rng &rng) {
+    const int64_t n = dst.len();
+    if (m->dtype == AG_F32) {
+        std::vector<float> h((size_t)n);
+        for (auto &v : h) v = rng.uniform(a);
+        check(ag_upload(m->dev, dst.data(), h.data(), h.size() * 4));
+        check(ag_device_wait(m->dev));
+    } else {
+        std::vector<__nv_bfloat16> h((size_t)n);
+        for (auto &v : h) v = __float2bfloat16_rn(rng.uniform(a));  // bf16::from_f32 of the f32 draw
+        check(ag_upload(m->dev, dst.data(), h.data(), h.size() * 2));
+        check(ag_device_wait(m->dev));
+    }
+}
+
+int64_t round_up(int64_t v, int64_t to) { return (v + to - 1) / to * to; }
+
+void build_model(ag_model *m, const ag_layer_spec *specs, int n, uint64_t seed) {
+    struct Pending {
+        Parameter *p;
+        Shape shape;
+        float a;
+    };
+    std::vector<Pending> pending;
+    for (int i = 0; i < n; ++i) {
+        const ag_layer_spec &s = specs[i];
+        switch (s.kind) {
+            case AG_LAYER_CONV2: {
+                if (s.a <= 0 || s.b <= 0 || s.c <= 0 || s.d <= 0)
+                    throw Error(AG_ERR_INVALID, "Conv2: inputs, outputs and filter must be positive");
+                auto l = std::make_unique<Conv2>();
+                // a = sqrt(2 / (inputs * filter size)) (layer.rs:345-349)
+                float a = std::sqrt(2.f / (float)(s.a * s.c * s.d));
+                l->has_bias = s.bias != 0;
+                pending.push_back({&l->weight, {s.b, s.a, s.c, s.d}, a});
+                if (l->has_bias) pending.push_back({&l->bias, {s.b}, a});
+                m->layers.push_back(std::move(l));
+                break;
+            }
+            case AG_LAYER_DENSE: {
+                if (s.a <= 0 || s.b <= 0)
+                    throw Error(AG_ERR_INVALID, "Dense: inputs and outputs must be positive");
+                auto l = std::make_unique<Dense>();
+                float a = std::sqrt(2.f / (float)s.a);  // layer.rs:463-467
+                l->has_bias = s.bias != 0;
+                pending.push_back({&l->weight, {s.a, s.b}, a});
+                if (l->has_bias) pending.push_back({&l->bias, {s.b}, a});
+                m->layers.push_back(std::move(l));
+                break;
+            }
+            case AG_LAYER_RELU: m->layers.push_back(std::make_unique<Relu>()); break;
+            case AG_LAYER_MAXPOOL2: {
+                if (s.c <= 0 || s.d <= 0) throw Error(AG_ERR_INVALID, "MaxPool2: bad filter");
+                auto l = std::make_unique<MaxPool2>();
+                l->filter[0] = l->stride[0] = s.c;
+                l->filter[1] = l->stride[1] = s.d;
+                m->layers.push_back(std::move(l));
+                break;
+            }
+            case AG_LAYER_FLATTEN: m->layers.push_back(std::make_unique<Flatten>()); break;
+            default: throw Error(AG_ERR_INVALID, "unknown layer kind");
+        }
+    }
+    // Buckets: every parameter starts on a 16-byte boundary.
+    int64_t off = 0;
+    for (auto &p : pending) {
+        m->offsets.push_back(off);
+        off += round_up(numel(p.shape), 8);
+    }
+    m->bucket_len = off;
+    m->values = Tensor::zeros(m->pool, {off}, m->dtype);
+    m->grads = Tensor::zeros(m->pool, {off}, m->dtype);
+    m->velocity = Tensor::zeros(m->pool, {off}, m->dtype);
+    Rng rng{seed};
+    for (size_t i = 0; i < pending.size(); ++i) {
+        Parameter *p = pending[i].p;
+        int64_t len = numel(pending[i].shape);
+        p->value = m->values.narrow0(m->offsets[i], len).into_shape(pending[i].shape);
+        p->grad = m->grads.narrow0(m->offsets[i], len).into_shape(pending[i].shape);
+        p->velocity = m->velocity.narrow0(m->offsets[i], len).into_shape(pending[i].shape);
+        fill_uniform(m, p->value, pending[i].a, rng);
+        m->params.push_back(p);
+    }
+    // A Relu that directly follows a Conv2 can be folded into its epilogue when
+    // no gradient is recorded.
+    for (size_t i = 0; i + 1 < m->layers.size(); ++i) {
+        auto *conv = dynamic_cast<Conv2 *>(m->layers[i].get());
+        if (conv && dynamic_cast<Relu *>(m->layers[i + 1].get())) conv->fuse_relu = true;
+    }
+}
+
+// ≙ the derived Forward: input.forward(&self.f0)?...forward(&self.fN) (autograph_derive/src/lib.rs:291-340)
+Variable forward_chain(ag_model *m, Variable v) {
+    for (size_t i = 0; i < m->layers.size(); ++i) {
+        Layer *l = m->layers[i].get();
+        auto *conv = dynamic_cast<Conv2 *>(l);
+        bool skip_next = conv && conv->relu_was_fused(v);
+        v = l->forward(m->pool, v);
+        if (skip_next) ++i;
+    }
+    return v;
+}
+
+Tensor input_tensor(ag_model *m, const void *x, bool on_host, int64_t bs, int64_t c, int64_t h,
+                    int64_t w) {
+    if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+    if (!x && bs > 0) throw Error(AG_ERR_INVALID, "input pointer is null");
+    Shape shape = {bs, c, h, w};
+    if (on_host) return Tensor::from_host(m->pool, shape, m->dtype, x);
+    return Tensor::external(m->dev, const_cast<void *>(x), shape, m->dtype);
+}
+
+float forward_backward(ag_model *m, const Tensor &x, const Tensor &t) {
+    for (Parameter *p : m->params) p->init_grad();  // ≙ model.init_parameter_grads()
+    Variable y = forward_chain(m, Variable{x, nullptr});
+    Loss loss = cross_entropy_loss(m->pool, y, t);
+    loss.backward();
+    for (Parameter *p : m->params) {
+        if (!p->has_grad()) throw Error(AG_ERR_INVALID, "a parameter received no gradient");
+    }
+    return loss.value;
+}
+
+// ≙ model.update(lr, &sgd) (layer.rs:656-658 -> SGD::update, optimizer.rs:389-428), over the
+// flat buckets: element-wise identical to updating each parameter.
+void apply_update(ag_model *m, float lr) {
+    if (m->grad_scale != 1.f)
+        check(ag_scaled_add(m->dev, m->dtype, m->grad_scale - 1.f, m->grads.data(), m->grads.data(),
+                            m->bucket_len));
+    if (m->use_momentum)
+        check(ag_sgd_update_momentum(m->dev, m->dtype, m->values.data(), m->grads.data(),
+                                     m->velocity.data(), m->bucket_len, lr, m->momentum));
+    else
+        check(ag_sgd_update(m->dev, m->dtype, m->values.data(), m->grads.data(), m->bucket_len, lr));
+    for (Parameter *p : m->params) p->node.reset();  // ≙ take_grad consumed the gradient
+}
+
+}  // namespace
+
+#define AG_HOST_GUARD(body)                                         \
+    try {                                                           \
+        body                                                        \
+    } catch (const Error &e) {                                      \
+        return ::ag::fail(e.status(), "%s", e.what());              \
+    } catch (const std::exception &e) {                             \
+        return ::ag::fail(AG_ERR_INVALID, "%s", e.what());          \
+    }                                                               \
+    return AG_OK;
+
+extern "C" {
+
+int ag_model_create(ag_device *dev, ag_dtype dtype, const ag_layer_spec *layers, int32_t n_layers,
+                    uint64_t seed, ag_model **out) {
+    AG_REQUIRE(dev && layers && out && n_layers > 0, AG_ERR_INVALID, "null or empty argument");
+    AG_REQUIRE(dtype == AG_F32 || dtype == AG_BF16, AG_ERR_DTYPE, "model dtype %d not implemented",
+               (int)dtype);
+    *out = nullptr;
+    ag_model *m = nullptr;
+    try {
+        m = new ag_model(dev, dtype);
+        build_model(m, layers, n_layers, seed);
+    } catch (const Error &e) {
+        delete m;
+        return ::ag::fail(e.status(), "%s", e.what());
+    } catch (const std::exception &e) {
+        delete m;
+        return ::ag::fail(AG_ERR_INVALID, "%s", e.what());
+    }
+    *out = m;
+    return AG_OK;
+}
+
+int ag_model_create_lenet5(ag_device *dev, ag_dtype dtype, uint64_t seed, ag_model **out) {
+    // benches/neural-network-benches/src/autograph_backend.rs:104-163
+    const ag_layer_spec spec[] = {
+        {AG_LAYER_CONV2, 1, 6, 5, 5, 0},   {AG_LAYER_RELU, 0, 0, 0, 0, 0},
+        {AG_LAYER_MAXPOOL2, 0, 0, 2, 2, 0}, {AG_LAYER_CONV2, 6, 16, 5, 5, 0},
+        {AG_LAYER_RELU, 0, 0, 0, 0, 0},    {AG_LAYER_MAXPOOL2, 0, 0, 2, 2, 0},
+        {AG_LAYER_FLATTEN, 0, 0, 0, 0, 0}, {AG_LAYER_DENSE, 256, 128, 0, 0, 0},
+        {AG_LAYER_RELU, 0, 0, 0, 0, 0},    {AG_LAYER_DENSE, 128, 84, 0, 0, 0},
+        {AG_LAYER_RELU, 0, 0, 0, 0, 0},    {AG_LAYER_DENSE, 84, 10, 0, 0, 1},
+    };
+    return ag_model_create(dev, dtype, spec, (int32_t)(sizeof(spec) / sizeof(spec[0])), seed, out);
+}
+
+int ag_model_destroy(ag_model *model) {
+    if (!model) return AG_OK;
+    ag_device_wait(model->dev);
+    delete model;
+    return AG_OK;
+}
+
+int ag_model_parameter_count(ag_model *model, int32_t *count) {
+    AG_REQUIRE(model && count, AG_ERR_INVALID, "null argument");
+    *count = (int32_t)model->params.size();
+    return AG_OK;
+}
+
+int ag_model_parameter_len(ag_model *model, int32_t index, int64_t *len) {
+    AG_REQUIRE(model && len, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(index >= 0 && index < (int32_t)model->params.size(), AG_ERR_INVALID,
+               "parameter index %d out of range", index);
+    *len = model->params[index]->value.len();
+    return AG_OK;
+}
+
+int ag_model_set_parameter(ag_model *model, int32_t index, const void *host) {
+    AG_REQUIRE(model && host, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(index >= 0 && index < (int32_t)model->params.size(), AG_ERR_INVALID,
+               "parameter index %d out of range", index);
+    Tensor &v = model->params[index]->value;
+    AG_TRY(ag_upload(model->dev, v.data(), host, v.nbytes()));
+    return ag_device_wait(model->dev);
+}
+
+int ag_model_get_parameter(ag_model *model, int32_t index, void *host) {
+    AG_REQUIRE(model && host, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(index >= 0 && index < (int32_t)model->params.size(), AG_ERR_INVALID,
+               "parameter index %d out of range", index);
+    Tensor &v = model->params[index]->value;
+    return ag_download(model->dev, host, v.data(), v.nbytes());
+}
+
+int ag_model_get_gradient(ag_model *model, int32_t index, void *host) {
+    AG_REQUIRE(model && host, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(index >= 0 && index < (int32_t)model->params.size(), AG_ERR_INVALID,
+               "parameter index %d out of range", index);
+    Tensor &g = model->params[index]->grad;
+    return ag_download(model->dev, host, g.data(), g.nbytes());
+}
+
+int ag_model_set_sgd(ag_model *model, float momentum) {
+    AG_REQUIRE(model != nullptr, AG_ERR_INVALID, "model is null");
+    model->use_momentum = momentum >= 0.f;
+    model->momentum = momentum >= 0.f ? momentum : 0.f;
+    return ag_fill_zero(model->dev, model->velocity.data(), model->velocity.nbytes());
+}
+
+int ag_model_set_grad_scale(ag_model *model, float scale) {
+    AG_REQUIRE(model != nullptr, AG_ERR_INVALID, "model is null");
+    model->grad_scale = scale;
+    return AG_OK;
+}
+
+int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, int64_t h, int64_t w,
+                   void *logits_host) {
+    AG_REQUIRE(model && logits_host, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({
+        Tensor x = input_tensor(model, x_host, true, bs, c, h, w);
+        Variable y = forward_chain(model, Variable{x, nullptr});
+        y.value.to_host(logits_host);
+    })
+}
+
+int ag_model_forward_device(ag_model *model, const void *x_dev, int64_t bs, int64_t c, int64_t h,
+                            int64_t w, void *logits_dev) {
+    AG_REQUIRE(model && logits_dev, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({
+        Tensor x = input_tensor(model, x_dev, false, bs, c, h, w);
+        Variable y = forward_chain(model, Variable{x, nullptr});
+        check(ag_copy(model->dev, logits_dev, y.value.data(), y.value.nbytes()));
+    })
+}
+
+int ag_model_train_step(ag_model *model, const void *x_host, const uint8_t *t_host, int64_t bs,
+                        int64_t c, int64_t h, int64_t w, float lr, float *loss_host) {
+    AG_REQUIRE(model && t_host && loss_host, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({
+        Tensor x = input_tensor(model, x_host, true, bs, c, h, w);
+        Tensor t = Tensor::from_host(model->pool, {bs}, AG_U8, t_host);
+        *loss_host = forward_backward(model, x, t);
+        apply_update(model, lr);
+    })
+}
+
+int ag_model_train_forward_backward(ag_model *model, const void *x_dev, const uint8_t *t_dev,
+                                    int64_t bs, int64_t c, int64_t h, int64_t w, float *loss_host,
+                                    void **grad_bucket, int64_t *grad_len) {
+    AG_REQUIRE(model && t_dev && loss_host, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({
+        Tensor x = input_tensor(model, x_dev, false, bs, c, h, w);
+        Tensor t = Tensor::external(model->dev, const_cast<uint8_t *>(t_dev), {bs}, AG_U8);
+        *loss_host = forward_backward(model, x, t);
+        if (grad_bucket) *grad_bucket = model->grads.data();
+        if (grad_len) *grad_len = model->bucket_len;
+    })
+}
+
+int ag_model_apply_update(ag_model *model, float lr) {
+    AG_REQUIRE(model != nullptr, AG_ERR_INVALID, "model is null");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({ apply_update(model, lr); })
+}
+
+}  // extern "C"

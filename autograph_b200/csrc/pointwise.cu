@@ -1,0 +1,403 @@
+// Memory-bound operators: relu, max-pool, scaled add, bias add / bias gradient
+// and the SGD updates.  Each kernel moves 16 bytes per thread per access where
+// the layout allows it and is sized as a grid-stride loop over a multiple of
+// the SM count.  Arithmetic is written with explicit round-to-nearest multiply
+// and add (no fused multiply-add) so that results are bit-identical to the
+// reference's host code, which does not contract.
+#include "common.cuh"
+
+namespace ag {
+
+static unsigned grid_for(int64_t items, int threads, int sms) {
+    int64_t blocks = ceil_div(items, threads);
+    int64_t cap = (int64_t)sms * 8;
+    return (unsigned)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+// 16-byte vector of T.
+template <class T>
+struct Vec16 {
+    static constexpr int N = 16 / sizeof(T);
+    uint4 raw;
+    __device__ __forceinline__ float get(int i) const;
+    __device__ __forceinline__ void set(int i, float v);
+};
+template <>
+__device__ __forceinline__ float Vec16<float>::get(int i) const {
+    return __uint_as_float((&raw.x)[i]);
+}
+template <>
+__device__ __forceinline__ void Vec16<float>::set(int i, float v) {
+    (&raw.x)[i] = __float_as_uint(v);
+}
+template <>
+__device__ __forceinline__ float Vec16<__nv_bfloat16>::get(int i) const {
+    uint32_t w = (&raw.x)[i >> 1];
+    return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+}
+template <>
+__device__ __forceinline__ void Vec16<__nv_bfloat16>::set(int i, float v) {
+    __nv_bfloat16 h = __float2bfloat16_rn(v);
+    uint32_t bits = *reinterpret_cast<unsigned short *>(&h);
+    uint32_t &w = (&raw.x)[i >> 1];
+    w = (i & 1) ? ((w & 0x0000ffffu) | (bits << 16)) : ((w & 0xffff0000u) | bits);
+}
+
+template <class T>
+static bool aligned16(const T *p) {
+    return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
+// ---- generic unary / binary / ternary element-wise driver --------------------
+// f(i, in0[i], in1[i]) -> out[i]; vector body when every pointer is 16-byte aligned.
+template <class T, class F>
+__global__ void map2_kernel(const T *a, const T *b, T *out,
+                            int64_t n, bool vec, F f) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    constexpr int V = Vec16<T>::N;
+    int64_t done = 0;
+    if (vec) {
+        const int64_t nv = n / V;
+        for (int64_t i = tid; i < nv; i += stride) {
+            Vec16<T> va, vb, vo;
+            va.raw = reinterpret_cast<const uint4 *>(a)[i];
+            vb.raw = b ? reinterpret_cast<const uint4 *>(b)[i] : va.raw;
+            vo.raw = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < V; ++j) vo.set(j, f(va.get(j), vb.get(j)));
+            reinterpret_cast<uint4 *>(out)[i] = vo.raw;
+        }
+        done = nv * V;
+    }
+    for (int64_t i = done + tid; i < n; i += stride) {
+        float x = to_f32(a[i]);
+        float y = b ? to_f32(b[i]) : x;
+        out[i] = from_f32<T>(f(x, y));
+    }
+}
+
+template <class T, class F>
+static int map2(ag_device *dev, const T *a, const T *b, T *out, int64_t n, F f) {
+    if (n == 0) return AG_OK;
+    const bool vec = aligned16(a) && aligned16(out) && (b == nullptr || aligned16(b));
+    const int threads = 256;
+    const int64_t items = vec ? ceil_div(n, Vec16<T>::N) : n;
+    map2_kernel<T, F><<<grid_for(items, threads, dev->sm_count), threads, 0, dev->stream>>>(
+        a, b, out, n, vec, f);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+struct ReluF {
+    __device__ __forceinline__ float operator()(float x, float) const {
+        return (x >= 0.f) ? x : 0.f;
+    }
+};
+struct ReluBackwardF {  // (x, dy)
+    __device__ __forceinline__ float operator()(float x, float dy) const {
+        return (x >= 0.f) ? dy : 0.f;
+    }
+};
+template <class T>
+struct ScaledAddF {  // (x, y) -> alpha*x + y in T arithmetic
+    float alpha;
+    __device__ __forceinline__ float operator()(float x, float y) const {
+        float p = to_f32(from_f32<T>(__fmul_rn(alpha, x)));
+        return __fadd_rn(p, y);
+    }
+};
+
+// ---- max pool ---------------------------------------------------------------
+template <class T>
+__global__ void max_pool2_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t planes,
+                                 int ih, int iw, int oh, int ow, int h, int w, int sh, int sw) {
+    const int64_t total = planes * oh * ow;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int wid = (int)(i % ow);
+        int64_t t = i / ow;
+        int hid = (int)(t % oh);
+        int64_t plane = t / oh;
+        const T *src = x + (plane * ih + (int64_t)hid * sh) * iw + (int64_t)wid * sw;
+        float m = 0.f;
+        for (int fi = 0; fi < h; ++fi)
+            for (int fj = 0; fj < w; ++fj) {
+                float v = to_f32(src[fi * iw + fj]);
+                if ((fi == 0 && fj == 0) || v > m) m = v;
+            }
+        y[i] = from_f32<T>(m);
+    }
+}
+
+// 2x2 window, stride 2, even width, 16-byte aligned rows: each thread reads two
+// 16-byte row segments and writes V/2 outputs.
+template <class T>
+__global__ void max_pool2_2x2_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t planes,
+                                     int ih, int iw, int oh, int ow) {
+    constexpr int V = Vec16<T>::N;  // inputs per vector
+    const int vec_per_row = iw / V;
+    const int64_t total = planes * oh * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int vx = (int)(i % vec_per_row);
+        int64_t t = i / vec_per_row;
+        int hid = (int)(t % oh);
+        int64_t plane = t / oh;
+        const T *r0 = x + (plane * ih + 2 * (int64_t)hid) * iw + vx * V;
+        Vec16<T> a, b;
+        a.raw = *reinterpret_cast<const uint4 *>(r0);
+        b.raw = *reinterpret_cast<const uint4 *>(r0 + iw);
+        T *dst = y + (plane * oh + hid) * (int64_t)ow + vx * (V / 2);
+#pragma unroll
+        for (int j = 0; j < V / 2; ++j) {
+            float m = a.get(2 * j);
+            float v = a.get(2 * j + 1);
+            if (v > m) m = v;
+            v = b.get(2 * j);
+            if (v > m) m = v;
+            v = b.get(2 * j + 1);
+            if (v > m) m = v;
+            dst[j] = from_f32<T>(m);
+        }
+    }
+}
+
+// One thread per window; windows do not overlap, so no two threads touch the
+// same cell.  dx holds the forward input on entry.
+template <class T>
+__global__ void max_pool2_backward_kernel(T *__restrict__ dx, const T *__restrict__ dy,
+                                          int64_t planes, int ih, int iw, int oh, int ow, int h,
+                                          int w, int sh, int sw) {
+    const int64_t total = planes * oh * ow;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int wid = (int)(i % ow);
+        int64_t t = i / ow;
+        int hid = (int)(t % oh);
+        int64_t plane = t / oh;
+        T *win = dx + (plane * ih + (int64_t)hid * sh) * iw + (int64_t)wid * sw;
+        float m = 0.f;
+        int am = 0;
+        for (int fi = 0; fi < h; ++fi)
+            for (int fj = 0; fj < w; ++fj) {
+                float v = to_f32(win[fi * iw + fj]);
+                if ((fi == 0 && fj == 0) || v > m) {
+                    m = v;
+                    am = fi * iw + fj;
+                }
+                win[fi * iw + fj] = from_f32<T>(0.f);
+            }
+        win[am] = from_f32<T>(__fadd_rn(0.f, to_f32(dy[i])));
+    }
+}
+
+// ---- bias ---------------------------------------------------------------------
+template <class T>
+__global__ void bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias, int64_t total,
+                                int64_t cols, int64_t inner) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t c = (i / inner) % cols;
+        y[i] = from_f32<T>(__fadd_rn(to_f32(y[i]), to_f32(bias[c])));
+    }
+}
+
+// One CTA per channel; fixed-shape tree reduction (deterministic).
+template <class T>
+__global__ void bias_grad_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
+                                 int64_t cols, int64_t inner, float beta) {
+    __shared__ float part[256];
+    const int64_t c = blockIdx.x;
+    const int64_t count = rows * inner;
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
+        int64_t r = i / inner, in = i - r * inner;
+        s += to_f32(x[(r * cols + c) * inner + in]);
+    }
+    part[threadIdx.x] = s;
+    __syncthreads();
+    for (int off = blockDim.x / 2; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) part[threadIdx.x] += part[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        float v = part[0];
+        if (beta != 0.f) v = __fadd_rn(v, __fmul_rn(beta, to_f32(y[c])));
+        y[c] = from_f32<T>(v);
+    }
+}
+
+// ---- SGD ------------------------------------------------------------------------
+template <class T>
+__global__ void sgd_momentum_kernel(T *__restrict__ w, const T *__restrict__ g, T *__restrict__ v,
+                                    int64_t n, float lr, float mom) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        float vv = __fadd_rn(__fmul_rn(mom, to_f32(v[i])), to_f32(g[i]));
+        float ww = __fsub_rn(to_f32(w[i]), __fmul_rn(lr, vv));
+        v[i] = from_f32<T>(vv);
+        w[i] = from_f32<T>(ww);
+    }
+}
+
+template <class T>
+static int pool_forward(ag_device *dev, const T *x, T *y, int64_t planes, int ih, int iw, int oh,
+                        int ow, int h, int w, int sh, int sw) {
+    const int threads = 256;
+    constexpr int V = Vec16<T>::N;
+    if (h == 2 && w == 2 && sh == 2 && sw == 2 && iw % V == 0 && aligned16(x)) {
+        const int64_t items = planes * oh * (iw / V);
+        max_pool2_2x2_kernel<T><<<grid_for(items, threads, dev->sm_count), threads, 0,
+                                  dev->stream>>>(x, y, planes, ih, iw, oh, ow);
+    } else {
+        const int64_t items = planes * oh * ow;
+        max_pool2_kernel<T><<<grid_for(items, threads, dev->sm_count), threads, 0, dev->stream>>>(
+            x, y, planes, ih, iw, oh, ow, h, w, sh, sw);
+    }
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+}  // namespace ag
+
+using namespace ag;
+
+#define AG_DISPATCH_FLOAT(dtype, T, ...)            \
+    do {                                            \
+        if ((dtype) == AG_F32) {                    \
+            using T = float;                        \
+            __VA_ARGS__                             \
+        } else {                                    \
+            using T = __nv_bfloat16;                \
+            __VA_ARGS__                             \
+        }                                           \
+    } while (0)
+
+extern "C" {
+
+int ag_relu(ag_device *dev, ag_dtype dtype, const void *x, void *y, int64_t n) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "relu %d unimplemented", (int)dtype);
+    AG_REQUIRE(n >= 0, AG_ERR_SHAPE, "negative length");
+    if (n == 0) return AG_OK;
+    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    AG_DISPATCH_FLOAT(dtype, T, return map2<T>(dev, (const T *)x, (const T *)nullptr, (T *)y, n, ReluF{}););
+}
+
+int ag_relu_backward(ag_device *dev, ag_dtype dtype, const void *x, const void *dy, void *dx,
+                     int64_t n) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "relu_backward %d unimplemented", (int)dtype);
+    AG_REQUIRE(n >= 0, AG_ERR_SHAPE, "negative length");
+    if (n == 0) return AG_OK;
+    AG_REQUIRE(x && dy && dx, AG_ERR_INVALID, "null tensor pointer");
+    AG_DISPATCH_FLOAT(dtype, T, return map2<T>(dev, (const T *)x, (const T *)dy, (T *)dx, n, ReluBackwardF{}););
+}
+
+int ag_scaled_add(ag_device *dev, ag_dtype dtype, float alpha, const void *x, void *y, int64_t n) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "scaled_add %d unimplemented", (int)dtype);
+    AG_REQUIRE(n >= 0, AG_ERR_SHAPE, "negative length");
+    if (n == 0) return AG_OK;
+    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    if (dtype == AG_F32)
+        return map2<float>(dev, (const float *)x, (const float *)y, (float *)y, n,
+                           ScaledAddF<float>{alpha});
+    // alpha is cast to the element type first (ScalarElem::scalar_cast in the reference).
+    float a = __bfloat162float(__float2bfloat16_rn(alpha));
+    return map2<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, (const __nv_bfloat16 *)y,
+                               (__nv_bfloat16 *)y, n, ScaledAddF<__nv_bfloat16>{a});
+}
+
+int ag_max_pool2(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t c, int64_t ih,
+                 int64_t iw, int32_t h, int32_t w, int32_t sh, int32_t sw, void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "max_pool2 %d unimplemented", (int)dtype);
+    AG_REQUIRE(h > 0 && w > 0 && sh > 0 && sw > 0, AG_ERR_INVALID, "bad pool options");
+    AG_REQUIRE(bs >= 0 && c >= 0 && ih >= h && iw >= w, AG_ERR_SHAPE,
+               "pool window [%d,%d] does not fit input [%lld,%lld]", h, w, (long long)ih,
+               (long long)iw);
+    AG_REQUIRE(ih < (1 << 30) && iw < (1 << 30), AG_ERR_LIMIT, "image too large");
+    const int oh = (int)((ih - h) / sh + 1), ow = (int)((iw - w) / sw + 1);
+    if (bs * c == 0) return AG_OK;
+    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    AG_DISPATCH_FLOAT(dtype, T, return pool_forward<T>(dev, (const T *)x, (T *)y, bs * c, (int)ih, (int)iw, oh, ow, h, w, sh, sw););
+}
+
+int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, int64_t c,
+                          int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh, int32_t sw,
+                          const void *dy) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "max_pool2_backward %d unimplemented",
+               (int)dtype);
+    AG_REQUIRE(h > 0 && w > 0 && sh > 0 && sw > 0, AG_ERR_INVALID, "bad pool options");
+    AG_REQUIRE(sh >= h && sw >= w, AG_ERR_UNSUPPORTED,
+               "max_pool2_backward needs non-overlapping windows (stride >= size)");
+    AG_REQUIRE(bs >= 0 && c >= 0 && ih >= h && iw >= w, AG_ERR_SHAPE,
+               "pool window does not fit input");
+    AG_REQUIRE(ih < (1 << 30) && iw < (1 << 30), AG_ERR_LIMIT, "image too large");
+    const int oh = (int)((ih - h) / sh + 1), ow = (int)((iw - w) / sw + 1);
+    const int64_t planes = bs * c;
+    if (planes == 0) return AG_OK;
+    AG_REQUIRE(dx && dy, AG_ERR_INVALID, "null tensor pointer");
+    const int threads = 256;
+    const unsigned grid = grid_for(planes * oh * ow, threads, dev->sm_count);
+    AG_DISPATCH_FLOAT(dtype, T,
+        max_pool2_backward_kernel<T><<<grid, threads, 0, dev->stream>>>(
+            (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow, h, w, sh, sw););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+int ag_bias_add(ag_device *dev, ag_dtype dtype, void *y, const void *bias, int64_t rows,
+                int64_t cols, int64_t inner) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "add_assign %d unimplemented", (int)dtype);
+    AG_REQUIRE(rows >= 0 && cols >= 0 && inner >= 0, AG_ERR_SHAPE, "negative dimension");
+    const int64_t total = rows * cols * inner;
+    if (total == 0) return AG_OK;
+    AG_REQUIRE(y && bias, AG_ERR_INVALID, "null tensor pointer");
+    const int threads = 256;
+    const unsigned grid = grid_for(total, threads, dev->sm_count);
+    AG_DISPATCH_FLOAT(dtype, T,
+        bias_add_kernel<T><<<grid, threads, 0, dev->stream>>>((T *)y, (const T *)bias, total, cols, inner););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+int ag_bias_grad(ag_device *dev, ag_dtype dtype, const void *x, int64_t rows, int64_t cols,
+                 int64_t inner, float beta, void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "sum_axis %d unimplemented", (int)dtype);
+    AG_REQUIRE(rows >= 0 && cols >= 0 && inner >= 0, AG_ERR_SHAPE, "negative dimension");
+    if (cols == 0) return AG_OK;
+    AG_REQUIRE(y && (rows * inner == 0 || x), AG_ERR_INVALID, "null tensor pointer");
+    AG_REQUIRE(cols < (1ll << 31), AG_ERR_LIMIT, "too many columns");
+    AG_DISPATCH_FLOAT(dtype, T,
+        bias_grad_kernel<T><<<(unsigned)cols, 256, 0, dev->stream>>>((const T *)x, (T *)y, rows, cols, inner, beta););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+int ag_sgd_update(ag_device *dev, ag_dtype dtype, void *w, const void *g, int64_t n, float lr) {
+    // w = cast_T(-lr) * g + w in T arithmetic: the reference routes plain SGD through scaled_add.
+    return ag_scaled_add(dev, dtype, -lr, g, w, n);
+}
+
+int ag_sgd_update_momentum(ag_device *dev, ag_dtype dtype, void *w, const void *g, void *v,
+                           int64_t n, float lr, float momentum) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "SGD %d unimplemented", (int)dtype);
+    AG_REQUIRE(n >= 0, AG_ERR_SHAPE, "negative length");
+    if (n == 0) return AG_OK;
+    AG_REQUIRE(w && g && v, AG_ERR_INVALID, "null tensor pointer");
+    const int threads = 256;
+    const unsigned grid = grid_for(n, threads, dev->sm_count);
+    AG_DISPATCH_FLOAT(dtype, T,
+        sgd_momentum_kernel<T><<<grid, threads, 0, dev->stream>>>((T *)w, (const T *)g, (T *)v, n, lr, momentum););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,306 @@
+/*
+ * autograph_b200 — C ABI of the B200 (sm_100a) backend for autograph's
+ * dense-contraction path.
+ *
+ * Every operator entry point below stands where the reference has one krnl
+ * dispatch site (`kernels::NAME::builder()?.specialize(..).build(device)?.dispatch(..)`).
+ * The comment above each declaration names that site by file:line inside the
+ * reference project.  Arguments mirror what the dispatch site passes: device
+ * pointers to the caller's buffers, element offsets, element strides, sizes
+ * and scalars.
+ *
+ * Conventions
+ *  - Every function returns an ag_status (0 = ok, < 0 = error); the message of
+ *    the most recent error on the calling thread is ag_last_error().  Nothing
+ *    throws, aborts or traps the device.  (The reference returns
+ *    anyhow::Result everywhere and bails on shape / type mismatches.)
+ *  - The caller owns all tensor memory.  The library keeps no pointer after a
+ *    call returns, except its own per-device workspace.
+ *  - Calls on one ag_device run asynchronously, in submission order, on that
+ *    device's CUDA stream (like krnl's device queue).  Only ag_download,
+ *    ag_device_wait and the calls that return a host scalar synchronise.
+ *  - Any host thread may call; calls on one ag_device are serialised inside.
+ *  - dtype is AG_F32 or AG_BF16 for values, AG_U8/U16/U32 for class labels.
+ *  - There is no CPU fallback: without a usable CUDA device every call fails
+ *    with AG_ERR_CUDA.
+ */
+#ifndef AUTOGRAPH_B200_H
+#define AUTOGRAPH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AG_API __attribute__((visibility("default")))
+#else
+#define AG_API
+#endif
+
+typedef struct ag_device ag_device;
+typedef struct ag_model ag_model;
+
+typedef enum ag_dtype { AG_F32 = 0, AG_BF16 = 1, AG_U8 = 2, AG_U16 = 3, AG_U32 = 4 } ag_dtype;
+
+typedef enum ag_status {
+    AG_OK = 0,
+    AG_ERR_INVALID = -1,        /* null pointer, negative size, bad enum */
+    AG_ERR_SHAPE = -2,          /* shape mismatch (reference: bail!("a_rows != c_rows ...")) */
+    AG_ERR_DTYPE = -3,          /* unsupported scalar type */
+    AG_ERR_CUDA = -4,           /* CUDA runtime / driver error, message has the CUDA string */
+    AG_ERR_OOM = -5,            /* device allocation failed */
+    AG_ERR_DEVICE_TIMEOUT = -6, /* a bounded device-side wait gave up */
+    AG_ERR_UNSUPPORTED = -7,    /* valid request this build does not implement */
+    AG_ERR_LIMIT = -8           /* size beyond a documented fixed limit */
+} ag_status;
+
+/* Convolution options; ≙ Im2ColConv2Options / ConvOptions<Ix2> (src/ops.rs:9-39,
+ * src/learn/neural_network/layer.rs:54-145). */
+typedef struct ag_conv2_options {
+    int32_t filter[2];   /* fh, fw */
+    int32_t padding[2];  /* ph, pw */
+    int32_t stride[2];   /* sh, sw */
+    int32_t dilation[2]; /* dh, dw */
+} ag_conv2_options;
+
+/* ---------------------------------------------------------------- runtime */
+
+AG_API const char *ag_last_error(void);
+AG_API const char *ag_version(void);
+
+/* ≙ iterating krnl devices (tests/integration_tests.rs:24-44). */
+AG_API int ag_device_count(int *count);
+/* ≙ Device::builder().index(i).build() (tests/integration_tests.rs:27-30).
+ * Creates a non-blocking stream owned by the device object. */
+AG_API int ag_device_create(int ordinal, ag_device **out);
+/* Same, but work is submitted to a stream the caller owns (cudaStream_t). */
+AG_API int ag_device_create_on_stream(int ordinal, void *cuda_stream, ag_device **out);
+AG_API int ag_device_destroy(ag_device *dev);
+/* ≙ device.wait() (src/tensor/linalg.rs:549). Also reports a device-side timeout flag. */
+AG_API int ag_device_wait(ag_device *dev);
+AG_API void *ag_device_stream(ag_device *dev);
+AG_API int ag_device_ordinal(ag_device *dev);
+
+/* ≙ Buffer allocation / transfer behind Tensor::into_device and into_array
+ * (src/tensor.rs:1819-1833, 1923-1945). ag_upload is asynchronous with respect
+ * to the host only when `host` is pinned memory; ag_download blocks until the
+ * data is on the host. */
+AG_API int ag_alloc(ag_device *dev, size_t bytes, void **dptr);
+AG_API int ag_free(ag_device *dev, void *dptr);
+AG_API int ag_host_alloc(size_t bytes, void **hptr); /* pinned host memory */
+AG_API int ag_host_free(void *hptr);
+AG_API int ag_upload(ag_device *dev, void *dptr, const void *host, size_t bytes);
+AG_API int ag_download(ag_device *dev, void *host, const void *dptr, size_t bytes);
+AG_API int ag_copy(ag_device *dev, void *dst, const void *src, size_t bytes);
+AG_API int ag_fill_zero(ag_device *dev, void *dptr, size_t bytes);
+
+/* ----------------------------------------------------------------- linalg */
+
+/* C = alpha * A.B + beta * C.  ≙ fn gemm + kernels::gemm_<T>
+ * (src/tensor/linalg.rs:249-360, 30-246), reached from Dot for TensorBase /
+ * ScalarTensorBase (:362-468) and Variable2::dot (autograd.rs:607-627).
+ * A is m x k, B is k x n, C is m x n; off_* are element offsets into the
+ * buffers, rs* / cs* are row / column strides in elements (may describe a
+ * transposed view; never a copy).  bf16 inputs are multiplied and accumulated
+ * in f32 and the result is rounded once (linalg.rs:244).  beta == 0 never
+ * reads C.  Large-k, small-output products are split along k with f32 partial
+ * sums and a fixed reduction order (deterministic). */
+AG_API int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t n, float alpha,
+                   const void *a, int64_t off_a, int64_t rsa, int64_t csa,
+                   const void *b, int64_t off_b, int64_t rsb, int64_t csb,
+                   float beta, void *c, int64_t off_c, int64_t rsc, int64_t csc);
+
+/* ------------------------------------------------------------ convolution */
+
+/* y = conv2(x, w) (+ bias) (then relu when fuse_relu != 0), NCHW.
+ * Replaces the sequence im2col_conv2 -> dot(Wmat^T) -> permute to NCHW ->
+ * bias add of conv2 / conv2_im2col (src/learn/neural_network/layer.rs:930-1005);
+ * fuse_relu folds the following Relu::forward (layer.rs:1254-1267).
+ * x [bs,ic,ih,iw], w [oc,ic,fh,fw], bias [oc] or NULL, y [bs,oc,oh,ow] with
+ * oh, ow from ag_conv2_output_shape. All tensors contiguous. */
+AG_API int ag_conv2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t ic,
+                            int64_t ih, int64_t iw, const void *w, int64_t oc, const void *bias,
+                            const ag_conv2_options *opt, int fuse_relu, void *y);
+
+/* dx = col2im(dy . Wmat): replaces the input edge of conv2_im2col
+ * (layer.rs:976-988) = dot + kernels::col2im_conv2_<T> (src/tensor/ops.rs:1602-1667).
+ * dy [bs,oc,oh,ow] (NCHW, as the autograd edge receives it), dx [bs,ic,ih,iw]. */
+AG_API int ag_conv2_backward_input(ag_device *dev, ag_dtype dtype, const void *w, int64_t oc,
+                                   int64_t ic, const void *dy, int64_t bs, int64_t ih, int64_t iw,
+                                   const ag_conv2_options *opt, void *dx);
+
+/* dw = dy^T . im2col(x): replaces the weight edge of conv2_im2col (layer.rs:989-997).
+ * dw [oc,ic,fh,fw] = beta * dw + gradient (beta = 1 accumulates, as
+ * Node::backward_grad does for a second edge, autograd.rs:126-131). */
+AG_API int ag_conv2_backward_weight(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                    int64_t ic, int64_t ih, int64_t iw, const void *dy, int64_t oc,
+                                    const ag_conv2_options *opt, float beta, void *dw);
+
+/* Output size (i + 2p - d(f-1) - 1)/s + 1 (src/ops.rs:28-38). Fails with
+ * AG_ERR_SHAPE when it is not positive. */
+AG_API int ag_conv2_output_shape(int64_t ih, int64_t iw, const ag_conv2_options *opt, int64_t *oh,
+                                 int64_t *ow);
+
+/* ≙ kernels::im2col_conv2_<T> (src/tensor/ops.rs:831-888, 1536-1599).
+ * x [bs,c,ih,iw] -> y [bs*oh*ow, c*fh*fw]; kept for trait / test parity. */
+AG_API int ag_im2col_conv2(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t c,
+                           int64_t ih, int64_t iw, const ag_conv2_options *opt, void *y);
+
+/* ≙ kernels::col2im_conv2_<T> (src/tensor/ops.rs:982-1037, 1602-1667).
+ * x [bs*gh*gw, c*fh*fw] -> y [bs,c,oh,ow]; (gh, gw) is Col2ImConv2Options::shape
+ * and the image size is (g-1)*s + d*(f-1) + 1 - 2p (src/ops.rs:67-78). Sums in f32. */
+AG_API int ag_col2im_conv2(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t c,
+                           int64_t gh, int64_t gw, const ag_conv2_options *opt, void *y);
+
+/* ---------------------------------------------------------------- pooling */
+
+/* ≙ kernels::max_pool2_<T> (src/tensor/ops.rs:1106-1141, 1670-1702); host
+ * semantics of :1040-1088 (first maximum wins). x [bs,c,ih,iw] ->
+ * y [bs,c,(ih-h)/sh+1,(iw-w)/sw+1]. */
+AG_API int ag_max_pool2(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t c,
+                        int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh, int32_t sw,
+                        void *y);
+
+/* ≙ kernels::max_pool2_backward_<T> (src/tensor/ops.rs:1228-1275, 1705-1744)
+ * with the host semantics of :1144-1207: dx must arrive holding a copy of the
+ * forward input (layer.rs:1203-1212); each window is zeroed and receives dy at
+ * its first maximum; cells no window covers keep their value.  Requires
+ * non-overlapping windows (sh >= h and sw >= w), as in every use by the reference. */
+AG_API int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, int64_t c,
+                                 int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh,
+                                 int32_t sw, const void *dy);
+
+/* ------------------------------------------------------------------- relu */
+
+/* ≙ kernels::relu_<T> / relu_mut_<T> (layer.rs:1300-1369, 1546-1553): y = x >= 0 ? x : 0.
+ * y may alias x (relu_mut). */
+AG_API int ag_relu(ag_device *dev, ag_dtype dtype, const void *x, void *y, int64_t n);
+/* ≙ kernels::relu_backward_<T> / relu_backward_mut_<T> (layer.rs:1413-1510, 1555-1563):
+ * dx = x >= 0 ? dy : 0, x is the layer input. dx may alias dy. */
+AG_API int ag_relu_backward(ag_device *dev, ag_dtype dtype, const void *x, const void *dy,
+                            void *dx, int64_t n);
+
+/* ------------------------------------------------------------ elementwise */
+
+/* y = alpha * x + y, computed in the element type.
+ * ≙ scaled_add -> kernels::assign_<X>_<Y> with BinaryOp::Add, contiguous case
+ * (src/tensor/ops.rs:257-318, 1357-1400). */
+AG_API int ag_scaled_add(ag_device *dev, ag_dtype dtype, float alpha, const void *x, void *y,
+                         int64_t n);
+
+/* y[r, c, i] += bias[c] for y viewed as [rows, cols, inner]; the broadcast
+ * scaled_add behind Variable::add_assign (autograd.rs:571-599 -> ops.rs strided
+ * assign kernels :1403-1490). inner = 1 for Dense, oh*ow for Conv2 (NCHW). */
+AG_API int ag_bias_add(ag_device *dev, ag_dtype dtype, void *y, const void *bias, int64_t rows,
+                       int64_t cols, int64_t inner);
+
+/* y[c] = beta * y[c] + sum over r, i of x[r, c, i] for x viewed as [rows, cols, inner].
+ * ≙ broadcast_backward -> sum_axis -> kernels::sum_axis<N>_<T>
+ * (autograd.rs:490-542, src/tensor/reduce.rs:59-404, 578-833). f32 accumulation. */
+AG_API int ag_bias_grad(ag_device *dev, ag_dtype dtype, const void *x, int64_t rows, int64_t cols,
+                        int64_t inner, float beta, void *y);
+
+/* -------------------------------------------------------------- criterion */
+
+/* ≙ cross_entropy_loss_device + kernels::cross_entropy_loss_<X>_<T> + sum
+ * (src/learn/criterion.rs:229-254, 299-324). x [bs,classes], t [bs] labels.
+ * *loss_host receives the SUM over the batch (synchronises). */
+AG_API int ag_cross_entropy_loss(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
+                                 const void *x, const void *t, int64_t bs, int64_t classes,
+                                 float *loss_host);
+
+/* ≙ kernels::cross_entropy_loss_backward_<X>_<T>
+ * (src/learn/neural_network/criterion.rs:79-137, 154-184):
+ * dx = (dy / bs) * (softmax(x) - onehot(t)). */
+AG_API int ag_cross_entropy_loss_backward(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
+                                          const void *x, const void *t, int64_t bs,
+                                          int64_t classes, float dy, void *dx);
+
+/* ≙ kernels::accuracy_<X>_<T> + sum (src/learn/criterion.rs:100-128, 271-296):
+ * counts rows whose target logit is strictly greater than every other logit
+ * (synchronises). */
+AG_API int ag_accuracy(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype, const void *x,
+                       const void *t, int64_t bs, int64_t classes, uint64_t *correct_host);
+
+/* -------------------------------------------------------------- optimizer */
+
+/* ≙ SGD::update without momentum (optimizer.rs:419-424): w = cast_T(-lr) * g + w in T. */
+AG_API int ag_sgd_update(ag_device *dev, ag_dtype dtype, void *w, const void *g, int64_t n,
+                         float lr);
+/* ≙ kernels::sgd_update_with_momentum_<T> (optimizer.rs:430-500, 509-545):
+ * v = m*v + g; w -= lr*v in f32, stored back in T. */
+AG_API int ag_sgd_update_momentum(ag_device *dev, ag_dtype dtype, void *w, const void *g, void *v,
+                                  int64_t n, float lr, float momentum);
+
+/* --------------------------------------------------- neural-network layer
+ * Host-side mirror of the reference's Layer / Forward objects for the
+ * benchmark networks (benches/neural-network-benches/src/autograph_backend.rs:16-163):
+ * a model is a chain of Conv2 / Relu / MaxPool2 / Flatten / Dense layers with
+ * resident parameters, run through define-by-run autograd on the device. */
+
+typedef enum ag_layer_kind {
+    AG_LAYER_CONV2 = 0,   /* a = inputs, b = outputs, c = fh, d = fw, bias */
+    AG_LAYER_RELU = 1,
+    AG_LAYER_MAXPOOL2 = 2, /* c = h, d = w (stride = filter, layer.rs:535-539) */
+    AG_LAYER_FLATTEN = 3,
+    AG_LAYER_DENSE = 4    /* a = inputs, b = outputs, bias */
+} ag_layer_kind;
+
+typedef struct ag_layer_spec {
+    int32_t kind;
+    int32_t a, b, c, d;
+    int32_t bias;
+} ag_layer_spec;
+
+/* ≙ LeNet5::new / the layer builders (autograph_backend.rs:104-163,
+ * layer.rs:330-397, 452-504). Parameters are drawn from U(-a, a),
+ * a = sqrt(2 / fan_in), from a generator seeded with `seed`. */
+AG_API int ag_model_create(ag_device *dev, ag_dtype dtype, const ag_layer_spec *layers,
+                           int32_t n_layers, uint64_t seed, ag_model **out);
+AG_API int ag_model_create_lenet5(ag_device *dev, ag_dtype dtype, uint64_t seed, ag_model **out);
+AG_API int ag_model_destroy(ag_model *model);
+/* ≙ Layer::try_for_each_parameter (layer.rs:597-640): number of parameter
+ * tensors, and the element count of each. */
+AG_API int ag_model_parameter_count(ag_model *model, int32_t *count);
+AG_API int ag_model_parameter_len(ag_model *model, int32_t index, int64_t *len);
+/* Copy one parameter tensor from / to host memory holding `dtype` elements. */
+AG_API int ag_model_set_parameter(ag_model *model, int32_t index, const void *host);
+AG_API int ag_model_get_parameter(ag_model *model, int32_t index, void *host);
+/* Gradient of the last training step (before the update consumed it). */
+AG_API int ag_model_get_gradient(ag_model *model, int32_t index, void *host);
+/* ≙ SGD::builder().momentum(m).build() (optimizer.rs:353-357); momentum < 0 = plain SGD. */
+AG_API int ag_model_set_sgd(ag_model *model, float momentum);
+/* Scale applied to gradients before the update (1/world for data parallel). */
+AG_API int ag_model_set_grad_scale(ag_model *model, float scale);
+
+/* ≙ LeNet5Classifier::infer (autograph_backend.rs:44-69): host input
+ * [bs, c, h, w] of `dtype` elements -> device, forward, logits back to host
+ * (blocking). */
+AG_API int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, int64_t h,
+                          int64_t w, void *logits_host);
+/* Forward only, device-resident input and output (no host copies, no sync). */
+AG_API int ag_model_forward_device(ag_model *model, const void *x_dev, int64_t bs, int64_t c,
+                                   int64_t h, int64_t w, void *logits_dev);
+/* ≙ LeNet5Classifier::train (autograph_backend.rs:70-85): init grads, forward,
+ * cross_entropy_loss, backward, optimizer update. Labels are u8. *loss_host =
+ * summed loss of the batch. */
+AG_API int ag_model_train_step(ag_model *model, const void *x_host, const uint8_t *t_host,
+                               int64_t bs, int64_t c, int64_t h, int64_t w, float lr,
+                               float *loss_host);
+/* The same step split in two for data-parallel training: gradients of this
+ * rank's shard are left in one flat f32/bf16 bucket (device pointer and
+ * element count returned) so that the caller can all-reduce it; apply then
+ * runs the optimizer over the bucket. */
+AG_API int ag_model_train_forward_backward(ag_model *model, const void *x_dev,
+                                           const uint8_t *t_dev, int64_t bs, int64_t c, int64_t h,
+                                           int64_t w, float *loss_host, void **grad_bucket,
+                                           int64_t *grad_len);
+AG_API int ag_model_apply_update(ag_model *model, float lr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AUTOGRAPH_B200_H */

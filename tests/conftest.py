@@ -1,0 +1,44 @@
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu)")
+
+
+class Golden:
+    """Committed vectors built from the reference's test generators
+    (tests/golden/gen_golden.py)."""
+
+    def __init__(self):
+        self.z = np.load(ROOT / "tests" / "golden" / "golden_vectors.npz")
+        self.meta = json.loads(bytes(self.z["meta"]).decode())
+
+    def __getitem__(self, name):
+        return self.z[name]
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return Golden()
+
+
+@pytest.fixture(scope="session")
+def dev():
+    """One library device on cuda:0 (no CPU fallback: fails without a GPU)."""
+    import autograph_b200 as ag
+    d = ag.Device(0)
+    yield d
+    d.wait()
+
+
+def cycle(lo, hi, n):
+    return (np.arange(n) % (hi - lo) + lo).astype(np.float32)
