@@ -51,6 +51,13 @@ def _conv_options(filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
     return o
 
 
+def kernel_launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    n = ctypes.c_uint64()
+    _capi.check(lib().ag_kernel_launch_count(ctypes.byref(n)))
+    return n.value
+
+
 class Device:
     """≙ ``Device::builder().index(i).build()``.  Work is submitted to a CUDA
     stream: by default a torch stream created here, which also becomes torch's

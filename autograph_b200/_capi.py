@@ -45,6 +45,7 @@ _P = c_void_p
 _SIGNATURES = {
     "ag_last_error": (c_char_p, []),
     "ag_version": (c_char_p, []),
+    "ag_kernel_launch_count": (c_int, [POINTER(c_uint64)]),
     "ag_device_count": (c_int, [POINTER(c_int)]),
     "ag_device_create": (c_int, [c_int, POINTER(_P)]),
     "ag_device_create_on_stream": (c_int, [c_int, _P, POINTER(_P)]),

@@ -38,8 +38,15 @@ int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)))
         if (!(cond)) return ::ag::fail(status, __VA_ARGS__); \
     } while (0)
 
+// Counts kernel launches enqueued by the library (ag_kernel_launch_count).
+void count_launch();
+
 // Checks the launch that was just enqueued.
-#define AG_CHECK_LAUNCH() AG_CUDA_TRY(cudaGetLastError())
+#define AG_CHECK_LAUNCH()                  \
+    do {                                   \
+        ::ag::count_launch();              \
+        AG_CUDA_TRY(cudaGetLastError());   \
+    } while (0)
 
 }  // namespace ag
 

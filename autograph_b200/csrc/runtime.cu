@@ -1,4 +1,5 @@
 // Device objects, memory, transfers and error reporting of the C ABI.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -17,6 +18,10 @@ int fail(int status, const char *fmt, ...) {
     va_end(ap);
     return status;
 }
+
+static std::atomic<uint64_t> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int workspace(ag_device *dev, size_t bytes, void **out) {
     if (bytes > dev->workspace_bytes) {
@@ -81,6 +86,12 @@ extern "C" {
 const char *ag_last_error(void) { return error_buffer(); }
 
 const char *ag_version(void) { return "autograph_b200 0.1 (sm_100a)"; }
+
+int ag_kernel_launch_count(uint64_t *count) {
+    AG_REQUIRE(count != nullptr, AG_ERR_INVALID, "count is null");
+    *count = g_launches.load(std::memory_order_relaxed);
+    return AG_OK;
+}
 
 int ag_device_count(int *count) {
     AG_REQUIRE(count != nullptr, AG_ERR_INVALID, "count is null");

@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction path: LeNet5 inference images/s and GEMM TFLOP/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--quick]
+
+A step is one LeNet5 forward pass over one batch of 1000 synthetic images in f32
+(BASELINE configs[0], the configuration the metric "LeNet5 infer img/s (bs1000)" is
+quoted on).  With N > 1 every rank (one process per GPU, launched by torchrun) runs the
+same step on its own 1000-image shard: inference shards by batch with no collective, so
+scaling is weak and `value` is the images all ranks processed divided by the slowest
+rank's device time.
+
+One JSON line is printed by rank 0.  Besides the contract keys it carries
+  roofline      dominant kernel of the timed step against the measured HBM peak
+  gemm          the standalone dot sweep (configs[1]) in TFLOP/s, with `gemm_roofline`
+                for the 4096^3 bf16 dot against the measured bf16 tensor peak
+  cpu_baseline  the CPU oracle (a port of the reference's host path) on this box's cores
+  extras        bf16 inference, the 65536-image batch of configs[4], the training step
+
+`--impl reference` times the CPU restatement of the reference's host path instead
+(the reference is Rust; no Rust toolchain exists on these machines).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "lenet5_infer_img_per_s"
+UNIT = "img/s"
+BATCH = 1000
+FLOPS_PER_IMG = 568720            # 2*(576*25*6 + 64*150*16 + 256*128 + 128*84 + 84*10)
+ROTATE = 64                       # distinct input batches: 64 * 3.136 MB = 200 MB > 126 MB L2
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained"), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        self.marks = []
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu=timestamp,{self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(gpu_index), "-lms", "50"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def mark(self, t0, t1):
+        self.marks.append((t0, t1))
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0, samples_in_timed_regions=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = []
+        import datetime
+        for line in Path(self.file.name).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 10:
+                continue
+            try:
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[2]), float(parts[3]), float(parts[4]), parts[5:]))
+            except ValueError:
+                continue
+        os.unlink(self.file.name)
+        if not rows:
+            return out
+        timed = [r for r in rows if any(a - 0.05 <= r[0] <= b + 0.05 for a, b in self.marks)]
+        busy = timed or [r for r in rows if r[3] > 250.0] or rows
+        out["samples"] = len(rows)
+        out["samples_in_timed_regions"] = len(timed)
+        out["sm_mhz"] = float(np.median([r[1] for r in busy]))
+        out["sm_max_mhz"] = max(r[2] for r in rows)
+        out["power_w_max"] = max(r[3] for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        seen = set()
+        for r in busy:
+            flags = r[4]
+            for name, val in zip(names, flags[1:5]):
+                if val.lower().startswith("active"):
+                    seen.add(name)
+        out["reasons"] = sorted(seen)
+        return out
+
+
+# ------------------------------------------------------------- CPU baseline
+def cpu_forward_rate(seconds: float, min_steps: int = 2):
+    """Images/s of the oracle's LeNet5 forward (direct f32 conv restating conv_direct.rs,
+    threaded GEMM) on all host cores, on batches of 1000 for about `seconds`."""
+    import oracle
+    from oracle import models
+    P = models.init_params(models.LENET5, 2000)
+    x = np.random.default_rng(1000).uniform(0, 1, (BATCH, 1, 28, 28)).astype(np.float32)
+    models.forward(models.LENET5, P, x, fast=True)  # warm-up
+    n, t0 = 0, time.perf_counter()
+    while True:
+        models.forward(models.LENET5, P, x, fast=True)
+        n += 1
+        dt = time.perf_counter() - t0
+        if n >= min_steps and dt >= seconds:
+            break
+    return n * BATCH / dt, oracle.num_threads(), n, dt
+
+
+def run_reference(args):
+    """The reference arm: the reference's host path, restated in C (oracle/), timed on the
+    host cores with all threads; K steps of one 1000-image forward each."""
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    import oracle
+    from oracle import models
+    P = models.init_params(models.LENET5, 2000)
+    x = np.random.default_rng(1000).uniform(0, 1, (BATCH, 1, 28, 28)).astype(np.float32)
+    for _ in range(max(args.warmup, 1)):
+        models.forward(models.LENET5, P, x, fast=True)
+    steps = min(args.steps, 2000)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        models.forward(models.LENET5, P, x, fast=True)
+    dt = time.perf_counter() - t0
+    value = steps * BATCH / dt
+    cores = oracle.num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "LeNet5 inference f32, batch 1000 per step (BASELINE configs[0])",
+                   "note": "CPU restatement of the reference's host path (oracle/); the reference "
+                           "itself is Rust and cannot be built on this box"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{steps} forward passes of 1000 images"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm
+def event_time_ms(torch, fn, iters, stream):
+    """Total device time of `iters` calls of fn, CUDA events on the launching stream."""
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(iters):
+        fn(i)
+    end.record(stream)
+    end.synchronize()
+    return start.elapsed_time(end)
+
+
+def run_gpu(args):
+    import torch
+    import autograph_b200 as ag
+    from autograph_b200 import data_parallel as dp
+
+    rank, local_rank, world = dp.env_world()
+    if world > 1:
+        dist = dp.init_process_group("nccl")
+    torch.cuda.set_device(local_rank)
+    dev = ag.Device(local_rank)
+    stream = dev.stream
+    peaks = measured_peaks()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev.torch_device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    K, W = args.steps, max(args.warmup, 3)
+    # Random-init weights of the architecture: the library's seeded default initialiser.
+    model = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)
+
+    # Device-resident inputs, rotated so that every step reads its images from HBM.
+    gen = torch.Generator(device=dev.torch_device).manual_seed(1000 + rank)
+    xs = torch.rand((ROTATE, BATCH, 1, 28, 28), generator=gen, device=dev.torch_device)
+    out = dev.empty((BATCH, 10), torch.float32)
+
+    def step(i):
+        model.forward_device(xs[i % ROTATE], out)
+
+    for i in range(W):
+        step(i)
+    barrier()
+    launches0 = ag.kernel_launch_count()
+    t_wall0 = time.time()
+    ms = event_time_ms(torch, step, K, stream)
+    t_wall1 = time.time()
+    launches = ag.kernel_launch_count() - launches0
+    barrier()
+    if sampler:
+        sampler.mark(t_wall0, t_wall1)
+    ms = max_over_ranks(ms)
+    value = world * BATCH * K / (ms * 1e-3)
+
+    # End to end through the public call with host buffers (pinned): H2D of the images and
+    # D2H of the logits inside the timed region.
+    xh = [torch.rand((BATCH, 1, 28, 28)).pin_memory() for _ in range(4)]
+    oh = torch.empty((BATCH, 10), dtype=torch.float32).pin_memory()
+    for i in range(W):
+        model.infer(xh[i % 4], oh)
+    barrier()
+    Ke = max(min(K, 2000), 10)
+    t0 = time.time()
+    ms_e2e = event_time_ms(torch, lambda i: model.infer(xh[i % 4], oh), Ke, stream)
+    if sampler:
+        sampler.mark(t0, time.time())
+    barrier()
+    ms_e2e = max_over_ranks(ms_e2e)
+    e2e = {"value": world * BATCH * Ke / (ms_e2e * 1e-3), "unit": UNIT,
+           "h2d_bytes_per_step": BATCH * 784 * 4, "d2h_bytes_per_step": BATCH * 10 * 4,
+           "steps": Ke, "ms_per_step": ms_e2e / Ke}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "LeNet5 inference f32, batch 1000 per step per GPU (BASELINE configs[0])",
+                   "global_batch": BATCH * world, "parallelism": f"dp{world} (batch shards, no collective)",
+                   "l2": f"inputs rotate over {ROTATE} batches (200 MB > 126 MB L2)",
+                   "peaks": peaks["source"]},
+        "e2e": e2e, "gpu_launches": int(launches),
+    }
+
+    if rank == 0:
+        line["roofline"], line["stages"] = lenet5_roofline(torch, ag, dev, model, xs, K, peaks)
+        if not args.quick:
+            line["gemm"], line["gemm_roofline"] = gemm_sweep(torch, ag, dev, peaks, sampler)
+            line["extras"] = extras(torch, ag, dev, peaks, world)
+    barrier()
+    if rank == 0:
+        line["clocks"] = sampler.stop()
+        if world == 1 or True:
+            secs = 3.0 if args.quick else 12.0
+            rate, cores, n, dt = cpu_forward_rate(secs)
+            line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"{n} forward passes of 1000 images in {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):
+    """Times each stage of the f32 forward alone (CUDA events, rotating inputs) and reports
+    the dominant kernel against the measured HBM peak; the FP32-pipe view is added because
+    the convolution kernels are FFMA-bound, which the hbm / tensor choice cannot express."""
+    shapes = [(6, 1, 5, 5), (16, 6, 5, 5), (256, 128), (128, 84), (84, 10), (10,)]
+    P = [dev.tensor(model.get_parameter(i).reshape(shp)) for i, shp in enumerate(shapes)]
+    B = BATCH
+    x0 = xs[:, :, :, :, :]
+    c1 = dev.conv2_forward(xs[0], P[0], relu=True)
+    p1 = dev.max_pool2(c1)
+    p1s = torch.stack([p1 + 0.001 * i for i in range(16)])           # 16 * 3.5 MB
+    c2 = dev.conv2_forward(p1, P[1], relu=True)
+    p2 = dev.max_pool2(c2)
+    f = p2.reshape(B, 256)
+    d1 = dev.dot(f, P[2])
+    iters = max(min(K, 500), 20)
+    stages = {}
+
+    def timeit(name, fn, flops, bytes_):
+        for i in range(3):
+            fn(i)
+        ms = event_time_ms(torch, fn, iters, dev.stream) / iters
+        stages[name] = {"us": ms * 1e3, "gflops": flops / ms * 1e-6, "gbs": bytes_ / ms * 1e-6,
+                        "alg_bytes": bytes_, "alg_flops": flops}
+
+    s = 4
+    timeit("conv1+relu (gemm_simt_kernel, implicit GEMM 576000x25x6)",
+           lambda i: dev.conv2_forward(x0[i % ROTATE], P[0], relu=True),
+           2 * B * 576 * 25 * 6, (B * 784 + 150 + B * 6 * 576) * s)
+    timeit("pool1 (max_pool2_2x2_kernel)", lambda i: dev.max_pool2(c1),
+           0, (B * 6 * 576 + B * 6 * 144) * s)
+    timeit("conv2+relu (gemm_simt_kernel, implicit GEMM 64000x150x16)",
+           lambda i: dev.conv2_forward(p1s[i % 16], P[1], relu=True),
+           2 * B * 64 * 150 * 16, (B * 6 * 144 + 2400 + B * 16 * 64) * s)
+    timeit("pool2 (max_pool2_2x2_kernel)", lambda i: dev.max_pool2(c2), 0,
+           (B * 16 * 64 + B * 256) * s)
+    timeit("dense1 (gemm_simt_kernel 1000x256x128)", lambda i: dev.dot(f, P[2]),
+           2 * B * 256 * 128, (B * 256 + 256 * 128 + B * 128) * s)
+    timeit("dense2 (gemm_simt_kernel 1000x128x84)", lambda i: dev.dot(d1, P[3]),
+           2 * B * 128 * 84, (B * 128 + 128 * 84 + B * 84) * s)
+    name = max(stages, key=lambda k: stages[k]["us"])
+    st = stages[name]
+    clock_ghz = 1.965
+    fp32_peak = 148 * 128 * 2 * clock_ghz * 1e-3  # TFLOP/s at the maximum SM clock
+    roof = {"bound": "hbm", "kernel": name, "achieved": st["gbs"], "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": st["gbs"] / peaks["hbm_gbs"], "traffic": None,
+            "peak_source": peaks["source"], "us_per_launch": st["us"],
+            "algorithmic_bytes_per_launch": st["alg_bytes"],
+            "fp32_pipe": {"achieved_tflops": st["gflops"] * 1e-3, "peak_tflops": fp32_peak,
+                          "frac": st["gflops"] * 1e-3 / fp32_peak,
+                          "note": "148 SMs x 128 lanes x 2 x 1.965 GHz; this kernel is FFMA-bound"}}
+    return roof, stages
+
+
+def gemm_sweep(torch, ag, dev, peaks, sampler):
+    """configs[1]: square dot products, f32 (SIMT) and bf16 (tcgen05), NN / TN / NT."""
+    results = []
+    roof = None
+    for dtype, name in [(torch.bfloat16, "bf16"), (torch.float32, "f32")]:
+        for n in [1024, 4096, 8192]:
+            layouts = ["nn", "tn", "nt"] if n == 4096 else ["nn"]
+            a = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
+            b = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
+            c = dev.empty((n, n), dtype)
+            for layout in layouts:
+                av = a.t() if layout[0] == "t" else a
+                bv = b.t() if layout[1] == "t" else b
+                iters = 20 if n <= 4096 else (10 if name == "bf16" else 4)
+                fn = lambda i: dev.gemm(1.0, av, bv, 0.0, c)
+                for i in range(3):
+                    fn(i)
+                t0 = time.time()
+                ms = event_time_ms(torch, fn, iters, dev.stream) / iters
+                if sampler:
+                    sampler.mark(t0, time.time())
+                tf = 2.0 * n ** 3 / ms * 1e-9
+                entry = {"dtype": name, "n": n, "layout": layout, "ms": ms, "tflops": tf}
+                if name == "bf16":
+                    entry["frac_of_measured_bf16_peak"] = tf / peaks["bf16_tflops"]
+                else:
+                    entry["frac_of_fp32_pipe_peak_at_max_clock"] = tf / (148 * 128 * 2 * 1.965e-3)
+                results.append(entry)
+                if name == "bf16" and n == 4096 and layout == "nn":
+                    roof = {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel (tcgen05), 4096^3 nn",
+                            "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                            "frac": tf / peaks["bf16_tflops"], "traffic": None,
+                            "peak_source": peaks["source"] + " (burst: kernel timed alone)"}
+            del a, b, c
+    return results, roof
+
+
+def extras(torch, ag, dev, peaks, world):
+    """bf16 inference, the 65536-image batch of configs[4] and the configs[2] training step."""
+    out = {}
+    # bf16 LeNet5 inference, batch 1000
+    mb = ag.Model(dev, ag.LENET5_SPEC, torch.bfloat16, seed=2000)
+    xb = torch.rand((ROTATE, BATCH, 1, 28, 28), device=dev.torch_device).to(torch.bfloat16)
+    ob = dev.empty((BATCH, 10), torch.bfloat16)
+    fn = lambda i: mb.forward_device(xb[i % ROTATE], ob)
+    for i in range(5):
+        fn(i)
+    ms = event_time_ms(torch, fn, 200, dev.stream) / 200
+    out["lenet5_infer_bf16_bs1000"] = {"img_per_s": BATCH / ms * 1e3, "ms": ms}
+    mb.close()
+    del xb
+    # configs[4a]: 65536 images in one pass (input 205 MB > L2)
+    m = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)
+    n_big = 65536 // world
+    xl = torch.rand((n_big, 1, 28, 28), device=dev.torch_device)
+    ol = dev.empty((n_big, 10), torch.float32)
+    fn = lambda i: m.forward_device(xl, ol)
+    for i in range(3):
+        fn(i)
+    ms = event_time_ms(torch, fn, 10, dev.stream) / 10
+    out["lenet5_infer_f32_bs65536"] = {
+        "img_per_s": n_big / ms * 1e3, "ms": ms,
+        "tflops": n_big * FLOPS_PER_IMG / ms * 1e-9,
+        "hbm_gbs_algorithmic": n_big * (784 + 10) * 4 / ms * 1e-6}
+    del xl, ol
+    # configs[2]: training step, batch 100, host buffers, plain SGD lr 0.01
+    xt = torch.rand((100, 1, 28, 28)).pin_memory()
+    tt = torch.randint(0, 10, (100,), dtype=torch.uint8).pin_memory()
+    for i in range(5):
+        m.train_step(xt, tt, 0.01)
+    ms = event_time_ms(torch, lambda i: m.train_step(xt, tt, 0.01), 100, dev.stream) / 100
+    out["lenet5_train_f32_bs100"] = {"ms_per_step": ms, "img_per_s": 100 / ms * 1e3}
+    m.close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--quick", action="store_true", help="skip the GEMM sweep and extras")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

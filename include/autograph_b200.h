@@ -70,6 +70,9 @@ typedef struct ag_conv2_options {
 
 AG_API const char *ag_last_error(void);
 AG_API const char *ag_version(void);
+/* Diagnostic with no counterpart in the reference: number of GPU kernels this
+ * library has launched in the calling process since it was loaded. */
+AG_API int ag_kernel_launch_count(uint64_t *count);
 
 /* ≙ iterating krnl devices (tests/integration_tests.rs:24-44). */
 AG_API int ag_device_count(int *count);

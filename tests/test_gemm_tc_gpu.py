@@ -1,0 +1,84 @@
+"""GPU: the tcgen05 bf16 GEMM (shapes large and aligned enough for the tensor-core path)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _views(a, b, layout):
+    return (a.T if layout[0] == "t" else a), (b.T if layout[1] == "t" else b)
+
+
+def _operands(rng, m, k, n, layout):
+    a = rng.uniform(-1, 1, (m, k) if layout[0] == "n" else (k, m)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n) if layout[1] == "n" else (n, k)).astype(np.float32)
+    return oracle.round_bf16(a), oracle.round_bf16(b)
+
+
+def _check(c, ref, tol=1e-2):
+    # bf16 result within 1e-2 relative (to max|C|) of the f64 product; the rounding
+    # of one bf16 store alone is 2^-9 = 2e-3 relative to the element.
+    err = np.abs(c.astype(np.float64) - ref).max() / np.abs(ref).max()
+    assert err <= tol, err
+    # and element-wise: within bf16 half-ulp of the f64 value plus accumulation noise
+    bound = np.abs(ref) * 2.0 ** -8 + 1e-3 * np.abs(ref).max()
+    assert (np.abs(c.astype(np.float64) - ref) <= bound).all()
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn", "tt"])
+@pytest.mark.parametrize("shape", [(128, 64, 256), (256, 256, 256), (384, 200, 520),
+                                   (1024, 1024, 1024)])
+def test_bf16_vs_f64(dev, layout, shape):
+    m, k, n = shape
+    rng = np.random.default_rng(3000 + m + k)
+    a, b = _operands(rng, m, k, n, layout)
+    av, bv = _views(a, b, layout)
+    ref = av.astype(np.float64) @ bv.astype(np.float64)
+    ad, bd = dev.tensor(a, torch.bfloat16), dev.tensor(b, torch.bfloat16)
+    c = dev.dot(*_views(ad, bd, layout)).float().cpu().numpy()
+    dev.wait()
+    _check(c, ref)
+
+
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_bf16_identity_exact(dev, layout):
+    """A . I = A exactly: catches any mis-addressed tile or swizzle error."""
+    m, k = 256, 512
+    rng = np.random.default_rng(11)
+    a = oracle.round_bf16(rng.uniform(-1, 1, (m, k) if layout[0] == "n" else (k, m)).astype(np.float32))
+    eye = np.eye(k, dtype=np.float32)
+    ad, bd = dev.tensor(a, torch.bfloat16), dev.tensor(eye, torch.bfloat16)
+    av, bv = _views(ad, bd, layout)
+    c = dev.dot(av, bv).float().cpu().numpy()
+    assert np.array_equal(c, a if layout[0] == "n" else a.T)
+
+
+def test_bf16_alpha_beta(dev):
+    m, k, n = 256, 128, 512
+    rng = np.random.default_rng(12)
+    a = rng.integers(-2, 3, (m, k)).astype(np.float32)
+    b = rng.integers(-2, 3, (k, n)).astype(np.float32)
+    c0 = rng.integers(-4, 5, (m, n)).astype(np.float32)
+    ad, bd, cd = (dev.tensor(v, torch.bfloat16) for v in (a, b, c0))
+    dev.gemm(0.5, ad, bd, 2.0, cd)
+    want = oracle.round_bf16((0.5 * (a @ b) + 2.0 * c0).astype(np.float32))
+    assert np.array_equal(cd.float().cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+def test_bf16_4096_sampled(dev, layout):
+    n = 4096
+    rng = np.random.default_rng(3012)
+    a, b = _operands(rng, n, n, n, layout)
+    av, bv = _views(a, b, layout)
+    ad, bd = dev.tensor(a, torch.bfloat16), dev.tensor(b, torch.bfloat16)
+    c = dev.dot(*_views(ad, bd, layout)).float().cpu().numpy()
+    rows = rng.choice(n, 32, replace=False)
+    ref = av[rows].astype(np.float64) @ bv.astype(np.float64)
+    _check(c[rows], ref)
+    cols = rng.choice(n, 32, replace=False)
+    ref = av.astype(np.float64) @ bv[:, cols].astype(np.float64)
+    _check(c[:, cols], ref)

@@ -1,0 +1,154 @@
+"""GPU: the layer chain (LeNet5 and the wider conv stack) against the oracle composition:
+inference logits + argmax, and a full training step (loss, every gradient, every update)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import models
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(spec, seed, bf16):
+    return models.init_params(spec, seed, bf16=bf16)
+
+
+def _rel(got, ref):
+    return float(np.abs(got.astype(np.float64) - ref.astype(np.float64)).max() /
+                 max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_lenet5_inference_bs1000(dev, dtype):
+    """BASELINE config 0: x [1000,1,28,28] U[0,1) seed 1000, default-init weights seed 2000."""
+    import autograph_b200 as ag
+    bf = dtype == torch.bfloat16
+    P = _params(models.LENET5, 2000, bf)
+    x = np.random.default_rng(1000).uniform(0, 1, (1000, 1, 28, 28)).astype(np.float32)
+    if bf:
+        x = oracle.round_bf16(x)
+    model = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=1)
+    model.set_parameters(P)
+    xh = torch.from_numpy(x).to(dtype).pin_memory()
+    logits = model.infer(xh).float().numpy()
+    ref64 = models.forward(models.LENET5, P, x, acc="f64")           # f64 accumulation, f32 stores
+    if bf:
+        assert _rel(logits, ref64) <= 1e-2 * 4                        # 5 layers of bf16 stores
+        ref_bf = models.forward(models.LENET5, P, x, acc="f64", bf16=True)
+        assert _rel(logits, ref_bf) <= 1e-2
+        # argmax must match wherever the top-2 margin exceeds the bf16 resolution
+        top2 = np.sort(ref_bf, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 2e-2 * np.abs(ref_bf).max()
+        assert (logits.argmax(1) == ref_bf.argmax(1))[clear].all()
+        assert (logits.argmax(1) == ref_bf.argmax(1)).mean() > 0.97
+    else:
+        ref32 = models.forward(models.LENET5, P, x)                    # the reference's host arithmetic
+        assert _rel(logits, ref64) <= 1e-5 * np.sqrt(256)
+        assert _rel(logits, ref32) <= 1e-5 * np.sqrt(256)
+        assert np.array_equal(logits.argmax(1), ref64.argmax(1))       # all 1000 rows
+        assert np.array_equal(logits.argmax(1), ref32.argmax(1))
+    # device-resident path gives the same bits as the host-buffer path
+    out = model.forward_device(xh.to(dev.torch_device)).float().cpu().numpy()
+    assert np.array_equal(out, logits)
+    # batch independence: the first 10 rows alone give the same logits
+    small = model.infer(xh[:10].contiguous()).float().numpy()
+    assert _rel(small, logits[:10]) <= (1e-2 if bf else 1e-6)
+    model.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("momentum", [None, 0.01])
+def test_lenet5_train_step_bs100(dev, dtype, momentum):
+    """BASELINE config 2: x [100,1,28,28] seed 4000, labels seed 4001, lr 0.01."""
+    import autograph_b200 as ag
+    bf = dtype == torch.bfloat16
+    P = _params(models.LENET5, 2000, bf)
+    x = np.random.default_rng(4000).uniform(0, 1, (100, 1, 28, 28)).astype(np.float32)
+    if bf:
+        x = oracle.round_bf16(x)
+    t = np.random.default_rng(4001).integers(0, 10, 100).astype(np.uint8)
+    model = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=1)
+    model.set_parameters(P)
+    model.set_sgd(momentum)
+    xh = torch.from_numpy(x).to(dtype).pin_memory()
+    th = torch.from_numpy(t).pin_memory()
+    loss = model.train_step(xh, th, 0.01)
+    ref_loss, grads, new_p, vel = models.train_step(models.LENET5, P, x, t.astype(np.uint32), 0.01,
+                                                    momentum=momentum, acc="f64", bf16=bf)
+    assert abs(loss - ref_loss) <= (2e-2 if bf else 1e-4) * abs(ref_loss)
+    for i, (g, w) in enumerate(zip(grads, new_p)):
+        got_g = model.get_gradient(i)
+        got_w = model.get_parameter(i)
+        gtol = 3e-2 if bf else 1e-4
+        assert _rel(got_g, g.ravel()) <= gtol, (i, _rel(got_g, g.ravel()))
+        assert _rel(got_w, w.ravel()) <= (1e-2 if bf else 1e-6), i
+        if not bf:
+            # the update itself is exact given the device's own gradient
+            if momentum is None:
+                assert np.array_equal(got_w, oracle.sgd_update(P[i].ravel(), got_g, 0.01))
+    # a second step runs on the updated parameters and lowers the loss on the same batch
+    loss2 = model.train_step(xh, th, 0.01)
+    assert loss2 < loss
+    model.close()
+
+
+def test_wide_stack_bf16_forward_backward(dev):
+    """BASELINE config 3 at batch 8 (the oracle's naive loops finish in seconds), bf16."""
+    import autograph_b200 as ag
+    dtype = torch.bfloat16
+    P = _params(models.WIDE_STACK, 5100, True)
+    bs = 8
+    x = oracle.round_bf16(np.random.default_rng(5000).standard_normal((bs, 3, 64, 64)).astype(np.float32))
+    t = np.random.default_rng(5001).integers(0, 10, bs).astype(np.uint8)
+    model = ag.Model(dev, ag.WIDE_STACK_SPEC, dtype, seed=1)
+    model.set_parameters(P)
+    xh = torch.from_numpy(x).to(dtype).pin_memory()
+    logits = model.infer(xh).float().numpy()
+    ref = models.forward(models.WIDE_STACK, P, x, acc="f64", bf16=True)
+    assert _rel(logits, ref) <= 2e-2
+    loss = model.train_step(xh, torch.from_numpy(t).pin_memory(), 0.01)
+    ref_loss, grads, new_p, _ = models.train_step(models.WIDE_STACK, P, x, t.astype(np.uint32), 0.01,
+                                                  acc="f64", bf16=True)
+    assert abs(loss - ref_loss) <= 3e-2 * abs(ref_loss)
+    for i, g in enumerate(grads):
+        assert _rel(model.get_gradient(i), g.ravel()) <= 5e-2, i
+    model.close()
+
+
+def test_wide_stack_full_batch_properties(dev):
+    """Config 3 at its full batch 256: rows are independent, so the first 8 rows of the
+    batch-256 forward equal the batch-8 forward."""
+    import autograph_b200 as ag
+    dtype = torch.bfloat16
+    P = _params(models.WIDE_STACK, 5100, True)
+    x = np.random.default_rng(5000).standard_normal((256, 3, 64, 64)).astype(np.float32)
+    model = ag.Model(dev, ag.WIDE_STACK_SPEC, dtype, seed=1)
+    model.set_parameters(P)
+    xh = torch.from_numpy(x).to(dtype).pin_memory()
+    full = model.infer(xh).float().numpy()
+    part = model.infer(xh[:8].contiguous()).float().numpy()
+    assert np.isfinite(full).all()
+    assert _rel(full[:8], part) <= 1e-2
+    loss = model.train_step(xh, torch.zeros(256, dtype=torch.uint8).pin_memory(), 0.01)
+    assert np.isfinite(loss) and loss > 0
+    model.close()
+
+
+def test_default_initialiser_distribution(dev):
+    """Parameters are U(-a, a), a = sqrt(2/fan_in) (layer.rs:345-389, 463-503); seeded."""
+    import autograph_b200 as ag
+    m1 = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=42)
+    m2 = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=42)
+    m3 = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=43)
+    assert m1.parameter_lens == [150, 2400, 32768, 10752, 840, 10]
+    fan_in = [25, 150, 256, 128, 84, 84]
+    for i, f in enumerate(fan_in):
+        w = m1.get_parameter(i)
+        a = np.sqrt(2.0 / f)
+        assert np.abs(w).max() <= a and np.array_equal(w, m2.get_parameter(i))
+        assert not np.array_equal(w, m3.get_parameter(i))
+        if w.size > 1000:
+            assert abs(w.mean()) < 0.05 * a and abs(w.std() - a / np.sqrt(3)) < 0.05 * a
+    for m in (m1, m2, m3):
+        m.close()
