@@ -236,7 +236,7 @@ __device__ __forceinline__ void store_tile(const Op &op, float *S, int tid,
     }
 }
 
-// grid = (ceil(N/BN), ceil(M/BM), splits); blockIdx.z works on k in
+// grid = (ceil(M/BM), ceil(N/BN), splits); blockIdx.z works on k in
 // [z*k_chunk, min(K, (z+1)*k_chunk)), k_chunk a multiple of BK.
 template <class Cfg, class AOp, class BOp, class Epi>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_BLOCKS)
@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_BLOCKS)
 
     const int tid = threadIdx.x;
     const int tx = tid % Cfg::TX, ty = tid / Cfg::TX;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int k_begin = blockIdx.z * k_chunk;
     const int k_end = min(K, k_begin + k_chunk);
     const int tiles = (k_end - k_begin + BK - 1) / BK;

@@ -9,9 +9,10 @@ namespace simt {
 template <class Cfg, class AOp, class BOp, class Epi>
 int launch_cfg(ag_device *dev, int M, int N, int K, int splits, int k_chunk, const AOp &A,
                const BOp &B, const Epi &E) {
-    dim3 grid((unsigned)ceil_div(N, Cfg::BN), (unsigned)ceil_div(M, Cfg::BM), (unsigned)splits);
+    // m tiles on grid.x (up to 2^31 - 1), n tiles on grid.y.
+    dim3 grid((unsigned)ceil_div(M, Cfg::BM), (unsigned)ceil_div(N, Cfg::BN), (unsigned)splits);
     AG_REQUIRE(grid.y <= 65535u && grid.z <= 65535u, AG_ERR_LIMIT,
-               "problem too large for one launch (m tiles %u, splits %u)", grid.y, grid.z);
+               "problem too large for one launch (n tiles %u, splits %u)", grid.y, grid.z);
     gemm_simt_kernel<Cfg, AOp, BOp, Epi>
         <<<grid, Cfg::THREADS, 0, dev->stream>>>(M, N, K, k_chunk, A, B, E);
     AG_CHECK_LAUNCH();

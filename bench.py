@@ -265,8 +265,16 @@ def run_gpu(args):
     if rank == 0:
         line["roofline"], line["stages"] = lenet5_roofline(torch, ag, dev, model, xs, K, peaks)
         if not args.quick:
-            line["gemm"], line["gemm_roofline"] = gemm_sweep(torch, ag, dev, peaks, sampler)
-            line["extras"] = extras(torch, ag, dev, peaks, world)
+            for key, fn in (("gemm", lambda: gemm_sweep(torch, ag, dev, peaks, sampler)),
+                            ("extras", lambda: extras(torch, ag, dev, peaks, world))):
+                try:
+                    res = fn()
+                    if key == "gemm":
+                        line["gemm"], line["gemm_roofline"] = res
+                    else:
+                        line[key] = res
+                except Exception as exc:  # the headline numbers above are still reported
+                    line[key + "_error"] = repr(exc)
     barrier()
     if rank == 0:
         line["clocks"] = sampler.stop()
@@ -412,6 +420,44 @@ def extras(torch, ag, dev, peaks, world):
     return out
 
 
+def run_probe(args):
+    """Runs one kernel family alone, for profiler captures:
+    gemm:<f32|bf16>:<n>:<nn|tn|nt|tt>, infer:<f32|bf16>:<batch>, train:<f32|bf16>:<batch>."""
+    import torch
+    import autograph_b200 as ag
+    dev = ag.Device(0)
+    parts = args.probe.split(":")
+    dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[parts[1]]
+    K, W = args.steps, args.warmup
+    if parts[0] == "gemm":
+        n, layout = int(parts[2]), parts[3]
+        a = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
+        b = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
+        c = dev.empty((n, n), dtype)
+        av = a.t() if layout[0] == "t" else a
+        bv = b.t() if layout[1] == "t" else b
+        fn = lambda i: dev.gemm(1.0, av, bv, 0.0, c)
+        work, unit = 2.0 * n ** 3 * 1e-12, "TFLOP/s"
+    else:
+        bs = int(parts[2])
+        model = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=2000)
+        if parts[0] == "infer":
+            x = torch.rand((bs, 1, 28, 28), device=dev.torch_device).to(dtype)
+            out = dev.empty((bs, 10), dtype)
+            fn = lambda i: model.forward_device(x, out)
+        else:
+            xh = torch.rand((bs, 1, 28, 28)).to(dtype).pin_memory()
+            th = torch.randint(0, 10, (bs,), dtype=torch.uint8).pin_memory()
+            fn = lambda i: model.train_step(xh, th, 0.01)
+        work, unit = float(bs), "img/s"
+    for i in range(W):
+        fn(i)
+    torch.cuda.synchronize()
+    ms = event_time_ms(torch, fn, K, dev.stream) / K
+    print(json.dumps({"probe": args.probe, "ms": ms, "rate": work / (ms * 1e-3), "unit": unit}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -419,8 +465,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="skip the GEMM sweep and extras")
+    ap.add_argument("--probe", default=None,
+                    help="run one kernel family alone (for profiler captures), e.g. gemm:bf16:4096:nn")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.probe:
+        run_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
