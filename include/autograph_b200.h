@@ -116,6 +116,25 @@ AG_API int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t
                    const void *b, int64_t off_b, int64_t rsb, int64_t csb,
                    float beta, void *c, int64_t off_c, int64_t rsc, int64_t csc);
 
+/* The same product as ag_gemm for callers that cannot allocate device memory
+ * (it has no counterpart in the reference).  Some hosts own all of a GPU's
+ * memory themselves, or forbid driver allocations after start-up; ag_gemm does
+ * not suit them because a product that is split along k keeps its partial sums
+ * in a workspace grown with cudaMalloc, and creating an ag_device allocates too.
+ * This entry point takes a device ordinal and a cudaStream_t instead of an
+ * ag_device, keeps the partial sums in a fixed 4 MiB array inside the library
+ * image (held by every GPU that loads the library, until the process exits) and
+ * calls no allocating routine.  Limit: m * n <= 524288 output elements, else
+ * AG_ERR_LIMIT.  The first call on a GPU looks up the array's device address;
+ * make that first call before any stream capture.  All calls on a GPU share the
+ * array: calls that overlap on the GPU (different streams, no ordering) race.
+ * Always runs the SIMT engine (f32 accumulation; bf16 inputs allowed). */
+AG_API int ag_gemm_static_scratch(int ordinal, void *cuda_stream, ag_dtype dtype, int64_t m,
+                                  int64_t k, int64_t n, float alpha, const void *a, int64_t off_a,
+                                  int64_t rsa, int64_t csa, const void *b, int64_t off_b,
+                                  int64_t rsb, int64_t csb, float beta, void *c, int64_t off_c,
+                                  int64_t rsc, int64_t csc);
+
 /* ------------------------------------------------------------ convolution */
 
 /* y = conv2(x, w) (+ bias) (then relu when fuse_relu != 0), NCHW.

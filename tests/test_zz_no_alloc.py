@@ -1,0 +1,75 @@
+"""GPU: ag_gemm_static_scratch, the split-k product for callers that may not allocate.
+
+Some users of the library run where device memory cannot be requested after start-up
+(the host application owns the whole GPU through its own arena, or forbids driver
+allocations on its worker threads).  They call this entry point with a device ordinal
+and a stream; its partial sums live in a fixed array inside the library.  The test
+checks it against ag_gemm on shapes that are split along k, twice in a row (the
+array keeps the previous call's contents), and checks the size limit.
+This file sorts last so that a failure here cannot hide any other test.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _call(lib, stream, a, b, c, alpha=1.0, beta=0.0):
+    code = {torch.float32: 0, torch.bfloat16: 1}[a.dtype]
+    m, k = a.shape
+    n = b.shape[1]
+    return lib.ag_gemm_static_scratch(
+        0, ctypes.c_void_p(stream), code, m, k, n, ctypes.c_float(alpha),
+        ctypes.c_void_p(a.data_ptr()), 0, a.stride(0), a.stride(1),
+        ctypes.c_void_p(b.data_ptr()), 0, b.stride(0), b.stride(1),
+        ctypes.c_float(beta), ctypes.c_void_p(c.data_ptr()), 0, c.stride(0), c.stride(1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_static_scratch_matches_ag_gemm(dev, dtype):
+    import autograph_b200 as ag
+    lib = ag.lib()
+    stream = dev.stream.cuda_stream
+    rng = np.random.default_rng(21)
+    # (m, k, n, layout): products the SIMT engine splits along k, in the layouts backward uses
+    shapes = [(16, 6400, 150, "tn"), (6, 57600, 25, "tn"), (64, 4096, 64, "nn"),
+              (100, 3000, 10, "nt"), (33, 1000, 7, "nn")]
+    for rep in range(2):  # two calls in a row share the array
+        for m, k, n, layout in shapes:
+            a = rng.uniform(-1, 1, (m, k) if layout[0] == "n" else (k, m)).astype(np.float32)
+            b = rng.uniform(-1, 1, (k, n) if layout[1] == "n" else (n, k)).astype(np.float32)
+            ad, bd = dev.tensor(a, dtype), dev.tensor(b, dtype)
+            av = ad.t() if layout[0] == "t" else ad
+            bv = bd.t() if layout[1] == "t" else bd
+            c0 = dev.tensor(rng.uniform(-1, 1, (m, n)).astype(np.float32), dtype)
+            want = dev.gemm(0.5, av, bv, 2.0, c0.clone())
+            got = c0.clone()
+            assert _call(lib, stream, av, bv, got, 0.5, 2.0) == 0, lib.ag_last_error()
+            torch.cuda.synchronize()
+            ref = 0.5 * (av.double() @ bv.double()) + 2.0 * c0.double()
+            tol = 1e-5 * np.sqrt(k) if dtype == torch.float32 else 1e-2
+            scale = ref.abs().max().item()
+            assert (got.double() - ref).abs().max().item() <= tol * scale
+            assert (got.double() - want.double()).abs().max().item() <= tol * scale
+
+
+def test_static_scratch_limits_and_errors(dev):
+    import autograph_b200 as ag
+    lib = ag.lib()
+    stream = dev.stream.cuda_stream
+    a = dev.empty((1024, 8), torch.float32)
+    b = dev.empty((8, 1024), torch.float32)
+    c = dev.empty((1024, 1024), torch.float32)
+    assert _call(lib, stream, a, b, c) == ag._capi.AG_ERR_LIMIT
+    assert b"static scratch limit" in lib.ag_last_error()
+    small = dev.empty((4, 8), torch.float32)
+    bad_dtype = lib.ag_gemm_static_scratch(
+        0, ctypes.c_void_p(stream), 3, 4, 8, 4, ctypes.c_float(1.0),
+        ctypes.c_void_p(small.data_ptr()), 0, 8, 1, ctypes.c_void_p(small.data_ptr()), 0, 1, 8,
+        ctypes.c_float(0.0), ctypes.c_void_p(small.data_ptr()), 0, 4, 1)
+    assert bad_dtype == ag._capi.AG_ERR_DTYPE
+    e = dev.empty((0, 8), torch.float32)
+    assert _call(lib, stream, e, b[:, :4], dev.empty((0, 4), torch.float32)) == 0
