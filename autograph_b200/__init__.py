@@ -169,6 +169,39 @@ class Device:
                                            ctypes.byref(o), int(relu), _ptr(y)))
         return y
 
+    def conv2_relu_max_pool2(self, x, w, bias=None, padding=(0, 0), stride=(1, 1), dilation=(1, 1),
+                             relu=True, pool=(2, 2)):
+        """Conv2 -> Relu -> MaxPool2 (window = stride) in one call (inference fusion)."""
+        bs, ic, ih, iw = x.shape
+        oc, ic2, fh, fw = w.shape
+        if ic != ic2:
+            raise AgError(_capi.AG_ERR_SHAPE, "input channels do not match the weight")
+        o = _conv_options((fh, fw), padding, stride, dilation)
+        oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
+        if oh < pool[0] or ow < pool[1]:
+            raise AgError(_capi.AG_ERR_SHAPE, "pool window does not fit the convolution output")
+        y = self.empty((bs, oc, (oh - pool[0]) // pool[0] + 1, (ow - pool[1]) // pool[1] + 1),
+                       x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_conv2_relu_max_pool2_forward(
+            self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw,
+            _ptr(w.contiguous()), oc, _ptr(bias), ctypes.byref(o), int(relu), pool[0], pool[1],
+            _ptr(y)))
+        return y
+
+    def dense_forward(self, x, w, bias=None, relu=False):
+        """≙ Dense::forward (x.dot(w) + bias) with an optional following Relu folded in."""
+        if x.dtype != w.dtype:
+            raise AgError(_capi.AG_ERR_DTYPE, "Can not dot tensors of different types")
+        if x.shape[1] != w.shape[0]:
+            raise AgError(_capi.AG_ERR_SHAPE, f"a_cols != b_rows, {x.shape[1]} != {w.shape[0]}")
+        y = self.empty((x.shape[0], w.shape[1]), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_dense_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()),
+                                           x.shape[0], x.shape[1], _ptr(w.contiguous()),
+                                           w.shape[1], _ptr(bias), int(relu), _ptr(y)))
+        return y
+
     def conv2_backward_input(self, w, dy, input_hw, padding=(0, 0), stride=(1, 1),
                              dilation=(1, 1)):
         oc, ic, fh, fw = w.shape

@@ -67,6 +67,10 @@ _SIGNATURES = {
     "ag_gemm_static_scratch": (c_int, [c_int, _P, c_int, c_int64, c_int64, c_int64, c_float, _P,
                                        c_int64, c_int64, c_int64, _P, c_int64, c_int64, c_int64,
                                        c_float, _P, c_int64, c_int64, c_int64]),
+    "ag_dense_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, _P, c_int64, _P, c_int, _P]),
+    "ag_conv2_relu_max_pool2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
+                                                _P, c_int64, _P, POINTER(ConvOptions), c_int,
+                                                c_int32, c_int32, _P]),
     "ag_conv2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int64,
                                  _P, POINTER(ConvOptions), c_int, _P]),
     "ag_conv2_backward_input": (c_int, [_P, c_int, _P, c_int64, c_int64, _P, c_int64, c_int64,

@@ -1,6 +1,7 @@
 // Convolution entry points: implicit-GEMM forward / backward-input /
 // backward-weight on the SIMT tile engine (the patch matrix is never written to
 // memory), plus the stand-alone im2col / col2im kernels.
+#include "conv2_direct.cuh"
 #include "gemm_simt_launch.cuh"
 
 namespace ag {
@@ -285,6 +286,16 @@ int ag_conv2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, 
     AG_REQUIRE(oc >= 0 && oc < (1 << 30), AG_ERR_SHAPE, "bad output channel count");
     if (bs == 0 || oc == 0) return AG_OK;
     AG_REQUIRE(x && w && y, AG_ERR_INVALID, "null tensor pointer");
+    if (direct::eligible(bs, ic, ih, iw, oc, opt)) {
+        if (dtype == AG_F32)
+            return direct::forward<float>(dev, (const float *)x, bs, ic, ih, iw, (const float *)w,
+                                          oc, (const float *)bias, opt, fuse_relu != 0, false,
+                                          (float *)y);
+        return direct::forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw,
+                                              (const __nv_bfloat16 *)w, oc,
+                                              (const __nv_bfloat16 *)bias, opt, fuse_relu != 0,
+                                              false, (__nv_bfloat16 *)y);
+    }
     if (dtype == AG_F32)
         return conv2_forward_t<float>(dev, g, (const float *)x, (const float *)w, (int)oc,
                                       (const float *)bias, fuse_relu != 0, (float *)y);
@@ -292,6 +303,38 @@ int ag_conv2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, 
                                           (const __nv_bfloat16 *)w, (int)oc,
                                           (const __nv_bfloat16 *)bias, fuse_relu != 0,
                                           (__nv_bfloat16 *)y);
+}
+
+int ag_conv2_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                    int64_t ic, int64_t ih, int64_t iw, const void *w, int64_t oc,
+                                    const void *bias, const ag_conv2_options *opt, int fuse_relu,
+                                    int32_t pool_h, int32_t pool_w, void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "Conv %d not implemented", (int)dtype);
+    AG_REQUIRE(pool_h > 0 && pool_w > 0, AG_ERR_INVALID, "bad pool window");
+    ConvGeom g;
+    AG_TRY(make_geom(bs, ic, ih, iw, opt, &g));
+    AG_REQUIRE(g.oh >= pool_h && g.ow >= pool_w, AG_ERR_SHAPE,
+               "pool window [%d,%d] does not fit the convolution output [%d,%d]", pool_h, pool_w,
+               g.oh, g.ow);
+    if (bs == 0 || oc == 0) return AG_OK;
+    AG_REQUIRE(x && w && y, AG_ERR_INVALID, "null tensor pointer");
+    if (pool_h == 2 && pool_w == 2 && direct::eligible(bs, ic, ih, iw, oc, opt)) {
+        if (dtype == AG_F32)
+            return direct::forward<float>(dev, (const float *)x, bs, ic, ih, iw, (const float *)w,
+                                          oc, (const float *)bias, opt, fuse_relu != 0, true,
+                                          (float *)y);
+        return direct::forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw,
+                                              (const __nv_bfloat16 *)w, oc,
+                                              (const __nv_bfloat16 *)bias, opt, fuse_relu != 0,
+                                              true, (__nv_bfloat16 *)y);
+    }
+    // General shapes: convolution into the device workspace, then the pool kernel.
+    // (neither of the two kernels below uses the workspace itself)
+    void *tmp = nullptr;
+    AG_TRY(workspace(dev, (size_t)bs * oc * g.oh * g.ow * dtype_size(dtype), &tmp));
+    AG_TRY(ag_conv2_forward(dev, dtype, x, bs, ic, ih, iw, w, oc, bias, opt, fuse_relu, tmp));
+    return ag_max_pool2(dev, dtype, tmp, bs, oc, g.oh, g.ow, pool_h, pool_w, pool_h, pool_w, y);
 }
 
 int ag_conv2_backward_input(ag_device *dev, ag_dtype dtype, const void *w, int64_t oc, int64_t ic,

@@ -49,9 +49,49 @@ static int gemm_simt_dispatch(ag_device *dev, int m, int k, int n, float alpha, 
                                             rsc, csc);
 }
 
+template <class T>
+static int dense_forward_simt(ag_device *dev, const T *x, int bs, int inputs, const T *w,
+                              int outputs, const T *bias, bool relu, T *y) {
+    simt::StridedOperand<T, true> A{x, (int64_t)inputs, 1, bs, inputs, false};
+    A.vec = (inputs % 4 == 0 || bs == 1) && aligned_for_vec(x);
+    simt::StridedOperand<T, false> B{w, 1, (int64_t)outputs, outputs, inputs, false};
+    B.vec = (outputs % 4 == 0 || inputs == 1) && aligned_for_vec(w);
+    simt::BiasReluEpilogue<T> E{y, (int64_t)outputs, bias, relu};
+    return simt::gemm(dev, bs, outputs, inputs, A, B, E, /*allow_split=*/true);
+}
+
 }  // namespace ag
 
 using namespace ag;
+
+extern "C" int ag_dense_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                int64_t inputs, const void *w, int64_t outputs, const void *bias,
+                                int fuse_relu, void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(dtype == AG_F32 || dtype == AG_BF16, AG_ERR_DTYPE, "Dense %d not implemented",
+               (int)dtype);
+    AG_REQUIRE(bs >= 0 && inputs >= 0 && outputs >= 0, AG_ERR_SHAPE, "negative dimension");
+    AG_REQUIRE(bs < (1ll << 31) && inputs < (1ll << 31) && outputs < (1ll << 31), AG_ERR_LIMIT,
+               "dimension beyond 2^31");
+    if (bs == 0 || outputs == 0) return AG_OK;
+    AG_REQUIRE(y && (inputs == 0 || (x && w)), AG_ERR_INVALID, "null tensor pointer");
+    if (dtype == AG_F32)
+        return dense_forward_simt<float>(dev, (const float *)x, (int)bs, (int)inputs,
+                                         (const float *)w, (int)outputs, (const float *)bias,
+                                         fuse_relu != 0, (float *)y);
+    const __nv_bfloat16 *px = (const __nv_bfloat16 *)x, *pw = (const __nv_bfloat16 *)w;
+    __nv_bfloat16 *py = (__nv_bfloat16 *)y;
+    if (tc::gemm_bf16_eligible(bs, inputs, outputs, px, inputs, 1, pw, outputs, 1, py, outputs, 1)) {
+        // Large products go to the tensor cores; bias and relu follow as separate passes.
+        AG_TRY(tc::gemm_bf16(dev, (int)bs, (int)inputs, (int)outputs, 1.f, px, inputs, 1, pw,
+                             outputs, 1, 0.f, py, outputs, 1));
+        if (bias) AG_TRY(ag_bias_add(dev, dtype, y, bias, bs, outputs, 1));
+        if (fuse_relu) AG_TRY(ag_relu(dev, dtype, y, y, bs * outputs));
+        return AG_OK;
+    }
+    return dense_forward_simt<__nv_bfloat16>(dev, px, (int)bs, (int)inputs, pw, (int)outputs,
+                                             (const __nv_bfloat16 *)bias, fuse_relu != 0, py);
+}
 
 extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t n,
                        float alpha, const void *a, int64_t off_a, int64_t rsa, int64_t csa,

@@ -29,6 +29,7 @@ struct TileCfg {
 
 using CfgL = TileCfg<128, 128, 16, 8, 8, 2>;  // 256 threads, large problems
 using CfgM = TileCfg<64, 64, 16, 4, 4, 3>;   // 256 threads, medium problems
+using CfgXS = TileCfg<32, 32, 16, 4, 4, 8>;   // 64 threads, small problems (more CTAs)
 using CfgS16 = TileCfg<128, 16, 16, 4, 4, 4>;  // 128 threads, n <= 16
 using CfgS8 = TileCfg<256, 8, 16, 4, 4, 4>;    // 128 threads, n <= 8
 
@@ -130,6 +131,25 @@ __device__ __forceinline__ void StridedEpilogue<__nv_bfloat16>::store4(int m, in
     out.y = *reinterpret_cast<uint32_t *>(&hi);
     *q = out;
 }
+
+// Row-major y = acc (+ bias[n]) (relu): the Dense layer.  The accumulator is
+// rounded to T before the bias is added and again after, so the result equals
+// the reference's unfused sequence dot -> add_assign(bias) -> relu bit for bit.
+template <class T>
+struct BiasReluEpilogue {
+    T *c;
+    int64_t rs;
+    const T *bias;
+    bool relu;
+    __device__ __forceinline__ void store(int m, int n, float acc) const {
+        float v = to_f32(from_f32<T>(acc));
+        if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[n]))));
+        if (relu) v = (v >= 0.f) ? v : 0.f;
+        c[(int64_t)m * rs + n] = from_f32<T>(v);
+    }
+    __device__ __forceinline__ bool can4(int, int) const { return false; }
+    __device__ __forceinline__ void store4(int, int, const float (&)[4]) const {}
+};
 
 // Split-k partial sums: plane blockIdx.z of a [splits][M*N] f32 workspace.
 struct PartialEpilogue {

@@ -19,20 +19,23 @@ int launch_cfg(ag_device *dev, int M, int N, int K, int splits, int k_chunk, con
     return AG_OK;
 }
 
-enum CfgId { kCfgL, kCfgM, kCfgS16, kCfgS8 };
+enum CfgId { kCfgL, kCfgM, kCfgXS, kCfgS16, kCfgS8 };
 
 inline CfgId pick_cfg(int M, int N, int sms) {
     if (N <= 8) return kCfgS8;
     if (N <= 16) return kCfgS16;
     int64_t tiles_l = ceil_div(M, 128) * ceil_div(N, 128);
     if (tiles_l >= sms) return kCfgL;
-    return kCfgM;
+    int64_t tiles_m = ceil_div(M, 64) * ceil_div(N, 64);
+    if (tiles_m * 2 >= sms) return kCfgM;
+    return kCfgXS;
 }
 
 inline void cfg_dims(CfgId id, int &bm, int &bn) {
     switch (id) {
         case kCfgL: bm = 128; bn = 128; break;
         case kCfgM: bm = 64; bn = 64; break;
+        case kCfgXS: bm = 32; bn = 32; break;
         case kCfgS16: bm = 128; bn = 16; break;
         default: bm = 256; bn = 8; break;
     }
@@ -44,6 +47,7 @@ int launch_any(ag_device *dev, CfgId id, int M, int N, int K, int splits, int k_
     switch (id) {
         case kCfgL: return launch_cfg<CfgL>(dev, M, N, K, splits, k_chunk, A, B, E);
         case kCfgM: return launch_cfg<CfgM>(dev, M, N, K, splits, k_chunk, A, B, E);
+        case kCfgXS: return launch_cfg<CfgXS>(dev, M, N, K, splits, k_chunk, A, B, E);
         case kCfgS16: return launch_cfg<CfgS16>(dev, M, N, K, splits, k_chunk, A, B, E);
         default: return launch_cfg<CfgS8>(dev, M, N, K, splits, k_chunk, A, B, E);
     }

@@ -158,7 +158,6 @@ class Conv2 : public Layer {
     bool has_bias = false;
     Parameter bias;    // [outputs]
     ConvOptions options;
-    bool fuse_relu = false;  // set by the model when a Relu follows and no gradient is needed
 
     const char *name() const override { return "Conv2"; }
     void parameters(std::vector<Parameter *> &out) override {
@@ -166,6 +165,15 @@ class Conv2 : public Layer {
         if (has_bias) out.push_back(&bias);
     }
     Variable forward(Pool &pool, const Variable &input) override {
+        return forward_fused(pool, input, false, nullptr);
+    }
+    bool records_gradient(const Variable &input) const {
+        return input.node || weight.node || (has_bias && bias.node);
+    }
+    // Forward with the following Relu (and 2-D max pool, window = stride) folded in.
+    // Folding is only legal when no gradient is recorded: the backward edges of
+    // Relu and MaxPool2 need the intermediate tensors.
+    Variable forward_fused(Pool &pool, const Variable &input, bool relu, const int *pool_window) {
         const Tensor &x = input.value;
         if (x.ndim() != 4 || x.dim(1) != weight.value.dim(1))
             throw Error(AG_ERR_SHAPE, "Conv2: input channels do not match the weight");
@@ -176,13 +184,27 @@ class Conv2 : public Layer {
         const ag_conv2_options copt = to_c_options(filter, options);
         int64_t oh = 0, ow = 0;
         check(ag_conv2_output_shape(ih, iw, &copt, &oh, &ow));
-        Tensor y = Tensor::uninit(pool, {bs, oc, oh, ow}, x.dtype());
         Variable w = weight.to_variable();
         Variable b = has_bias ? bias.to_variable() : Variable{};
         const bool needs_grad = input.node || w.node || b.node;
+        if ((relu || pool_window) && needs_grad)
+            throw Error(AG_ERR_INVALID, "Conv2: fused forward while a gradient is recorded");
+        if (pool_window) {
+            const int64_t ph = (oh - pool_window[0]) / pool_window[0] + 1;
+            const int64_t pw = (ow - pool_window[1]) / pool_window[1] + 1;
+            if (oh < pool_window[0] || ow < pool_window[1])
+                throw Error(AG_ERR_SHAPE, "MaxPool2: window larger than input");
+            Tensor y = Tensor::uninit(pool, {bs, oc, ph, pw}, x.dtype());
+            check(ag_conv2_relu_max_pool2_forward(
+                x.device(), x.dtype(), x.data(), bs, ic, ih, iw, w.value.data(), oc,
+                has_bias ? b.value.data() : nullptr, &copt, relu ? 1 : 0, pool_window[0],
+                pool_window[1], y.data()));
+            return Variable{y, nullptr};
+        }
+        Tensor y = Tensor::uninit(pool, {bs, oc, oh, ow}, x.dtype());
         check(ag_conv2_forward(x.device(), x.dtype(), x.data(), bs, ic, ih, iw, w.value.data(), oc,
-                               has_bias ? b.value.data() : nullptr, &copt,
-                               (fuse_relu && !needs_grad) ? 1 : 0, y.data()));
+                               has_bias ? b.value.data() : nullptr, &copt, relu ? 1 : 0,
+                               y.data()));
         VariableBuilder builder;
         Pool *pp = &pool;
         if (input.node) {
@@ -214,9 +236,6 @@ class Conv2 : public Layer {
         }
         return builder.build(y);
     }
-    bool relu_was_fused(const Variable &input) const {
-        return fuse_relu && !(input.node || weight.node || (has_bias && bias.node));
-    }
 };
 
 // Dense (layer.rs:1070-1143): Y = X.W (+ b), W is [inputs, outputs];
@@ -234,11 +253,28 @@ class Dense : public Layer {
         if (has_bias) out.push_back(&bias);
     }
     Variable forward(Pool &pool, const Variable &input) override {
+        return forward_fused(pool, input, false);
+    }
+    bool records_gradient(const Variable &input) const {
+        return input.node || weight.node || (has_bias && bias.node);
+    }
+    // Forward with the bias add (and, when no gradient is recorded, the following
+    // Relu) folded into the product's epilogue.
+    Variable forward_fused(Pool &pool, const Variable &input, bool relu) {
         const Tensor &x = input.value;
         if (x.ndim() != 2) throw Error(AG_ERR_SHAPE, "Dense needs a 2-D input");
+        if (!x.is_standard_layout()) throw Error(AG_ERR_SHAPE, "Dense needs standard layout");
         Variable w = weight.to_variable();
-        Tensor y = x.dot(pool, w.value);
-        const int64_t bs = x.dim(0), outs = w.value.dim(1);
+        if (x.dim(1) != w.value.dim(0))
+            throw Error(AG_ERR_SHAPE, "a_cols != b_rows, " + std::to_string(x.dim(1)) +
+                                          " != " + std::to_string(w.value.dim(0)));
+        if (relu && records_gradient(input))
+            throw Error(AG_ERR_INVALID, "Dense: fused relu while a gradient is recorded");
+        const int64_t bs = x.dim(0), ins = x.dim(1), outs = w.value.dim(1);
+        Variable b = has_bias ? bias.to_variable() : Variable{};
+        Tensor y = Tensor::uninit(pool, {bs, outs}, x.dtype());
+        check(ag_dense_forward(x.device(), x.dtype(), x.data(), bs, ins, w.value.data(), outs,
+                               has_bias ? b.value.data() : nullptr, relu ? 1 : 0, y.data()));
         VariableBuilder builder;
         Pool *pp = &pool;
         if (input.node) {
@@ -255,17 +291,13 @@ class Dense : public Layer {
                 return xv.t().dot(*pp, dy);
             });
         }
-        if (has_bias) {
-            Variable b = bias.to_variable();
-            check(ag_bias_add(y.device(), y.dtype(), y.data(), b.value.data(), bs, outs, 1));
-            if (b.node) {
-                builder.edge(b.node, [=](const Tensor &dy, Tensor *into) {
-                    Tensor db = into ? *into : Tensor::uninit(*pp, {outs}, dy.dtype());
-                    check(ag_bias_grad(dy.device(), dy.dtype(), dy.data(), bs, outs, 1, 0.f,
-                                       db.data()));
-                    return db;
-                });
-            }
+        if (has_bias && b.node) {
+            builder.edge(b.node, [=](const Tensor &dy, Tensor *into) {
+                Tensor db = into ? *into : Tensor::uninit(*pp, {outs}, dy.dtype());
+                check(ag_bias_grad(dy.device(), dy.dtype(), dy.data(), bs, outs, 1, 0.f,
+                                   db.data()));
+                return db;
+            });
         }
         return builder.build(y);
     }

@@ -124,22 +124,33 @@ void build_model(ag_model *m, const ag_layer_spec *specs, int n, uint64_t seed) 
         fill_uniform(m, p->value, pending[i].a, rng);
         m->params.push_back(p);
     }
-    // A Relu that directly follows a Conv2 can be folded into its epilogue when
-    // no gradient is recorded.
-    for (size_t i = 0; i + 1 < m->layers.size(); ++i) {
-        auto *conv = dynamic_cast<Conv2 *>(m->layers[i].get());
-        if (conv && dynamic_cast<Relu *>(m->layers[i + 1].get())) conv->fuse_relu = true;
-    }
 }
 
 // ≙ the derived Forward: input.forward(&self.f0)?...forward(&self.fN) (autograph_derive/src/lib.rs:291-340)
+// When no gradient is recorded (inference), a Relu and a MaxPool2 that follow a
+// Conv2, and a Relu that follows a Dense, are folded into the producing kernel.
 Variable forward_chain(ag_model *m, Variable v) {
-    for (size_t i = 0; i < m->layers.size(); ++i) {
+    const size_t n = m->layers.size();
+    for (size_t i = 0; i < n; ++i) {
         Layer *l = m->layers[i].get();
-        auto *conv = dynamic_cast<Conv2 *>(l);
-        bool skip_next = conv && conv->relu_was_fused(v);
+        auto *relu1 = i + 1 < n ? dynamic_cast<Relu *>(m->layers[i + 1].get()) : nullptr;
+        if (auto *conv = dynamic_cast<Conv2 *>(l)) {
+            if (!conv->records_gradient(v) && relu1) {
+                auto *mp = i + 2 < n ? dynamic_cast<MaxPool2 *>(m->layers[i + 2].get()) : nullptr;
+                const bool pool_ok = mp && mp->stride[0] == mp->filter[0] &&
+                                     mp->stride[1] == mp->filter[1];
+                v = conv->forward_fused(m->pool, v, true, pool_ok ? mp->filter : nullptr);
+                i += pool_ok ? 2 : 1;
+                continue;
+            }
+        } else if (auto *dense = dynamic_cast<Dense *>(l)) {
+            if (!dense->records_gradient(v) && relu1) {
+                v = dense->forward_fused(m->pool, v, true);
+                i += 1;
+                continue;
+            }
+        }
         v = l->forward(m->pool, v);
-        if (skip_next) ++i;
     }
     return v;
 }

@@ -135,6 +135,15 @@ AG_API int ag_gemm_static_scratch(int ordinal, void *cuda_stream, ag_dtype dtype
                                   int64_t rsb, int64_t csb, float beta, void *c, int64_t off_c,
                                   int64_t rsc, int64_t csc);
 
+/* y = x . w (+ bias) (then relu when fuse_relu != 0), all row-major contiguous:
+ * ≙ Dense::forward (layer.rs:1134-1143: dot, then add_assign of the bias) with the
+ * following Relu::forward (layer.rs:1254-1267) folded in.  x [bs, inputs],
+ * w [inputs, outputs], bias [outputs] or NULL, y [bs, outputs].  Equals the
+ * separate calls bit for bit. */
+AG_API int ag_dense_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                            int64_t inputs, const void *w, int64_t outputs, const void *bias,
+                            int fuse_relu, void *y);
+
 /* ------------------------------------------------------------ convolution */
 
 /* y = conv2(x, w) (+ bias) (then relu when fuse_relu != 0), NCHW.
@@ -146,6 +155,18 @@ AG_API int ag_gemm_static_scratch(int ordinal, void *cuda_stream, ag_dtype dtype
 AG_API int ag_conv2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t ic,
                             int64_t ih, int64_t iw, const void *w, int64_t oc, const void *bias,
                             const ag_conv2_options *opt, int fuse_relu, void *y);
+
+/* Inference fusion of the chain Conv2::forward -> Relu::forward -> MaxPool2::forward
+ * (layer.rs:1035-1047, 1254-1267, 1193-1216 -> ops.rs:1106-1141): y = max_pool2(relu?(conv2(x, w)
+ * + bias)) with pool window (pool_h, pool_w) and stride = window.  Equals the three separate calls
+ * bit for bit; y is [bs, oc, (oh-pool_h)/pool_h+1, (ow-pool_w)/pool_w+1].  The convolution output
+ * is never written to memory when the direct kernel applies (default options, 5x5 / 3x3 filter,
+ * few channels, 2x2 pool); other shapes run convolution and pool back to back. */
+AG_API int ag_conv2_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const void *x,
+                                           int64_t bs, int64_t ic, int64_t ih, int64_t iw,
+                                           const void *w, int64_t oc, const void *bias,
+                                           const ag_conv2_options *opt, int fuse_relu,
+                                           int32_t pool_h, int32_t pool_w, void *y);
 
 /* dx = col2im(dy . Wmat): replaces the input edge of conv2_im2col
  * (layer.rs:976-988) = dot + kernels::col2im_conv2_<T> (src/tensor/ops.rs:1602-1667).

@@ -1,0 +1,85 @@
+"""GPU: the inference fusions (conv+relu+pool, dense+bias+relu) equal the separate
+operator calls bit for bit, and match the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _prep(a, dtype):
+    return oracle.round_bf16(a.astype(np.float32)) if dtype == torch.bfloat16 else a.astype(np.float32)
+
+
+CONV_SHAPES = [
+    # bs, ic, ih, iw, oc, fh, fw, pool      (first four take the direct kernel)
+    (37, 1, 28, 28, 6, 5, 5, (2, 2)), (37, 6, 12, 12, 16, 5, 5, (2, 2)),
+    (3, 3, 64, 64, 64, 3, 3, (2, 2)), (1000, 1, 28, 28, 6, 5, 5, (2, 2)),
+    (2, 64, 31, 31, 128, 3, 3, (2, 2)), (3, 5, 9, 11, 7, 3, 2, (2, 3)), (4, 2, 10, 10, 8, 3, 3, (3, 3)),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", CONV_SHAPES)
+def test_conv_relu_pool_equals_separate_calls(dev, dtype, shape):
+    bs, ic, ih, iw, oc, fh, fw, pool = shape
+    rng = np.random.default_rng(31 + ic + oc)
+    x = _prep(rng.standard_normal((bs, ic, ih, iw)), dtype)
+    a = np.sqrt(2.0 / (ic * fh * fw))
+    w = _prep(rng.uniform(-a, a, (oc, ic, fh, fw)), dtype)
+    b = _prep(rng.uniform(-a, a, oc), dtype)
+    xd, wd, bd = dev.tensor(x, dtype), dev.tensor(w, dtype), dev.tensor(b, dtype)
+    for bias in (None, bd):
+        for relu in (True, False):
+            fused = dev.conv2_relu_max_pool2(xd, wd, bias=bias, relu=relu, pool=pool)
+            y = dev.conv2_forward(xd, wd)
+            if bias is not None:
+                y = dev.bias_add(y, bias)
+            if relu:
+                y = dev.relu(y)
+            sep = dev.max_pool2(y, pool)
+            assert torch.equal(fused, sep), (shape, bias is not None, relu)
+    # against the oracle (f64 accumulation): tolerance of the convolution
+    ref = oracle.max_pool2(oracle.relu(oracle.conv2_naive(x, w, acc64=True)), pool)
+    got = dev.conv2_relu_max_pool2(xd, wd, pool=pool).float().cpu().numpy()
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5 * np.sqrt(ic * fh * fw)
+    assert np.abs(got - ref).max() <= tol * max(np.abs(ref).max(), 1e-30)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1000, 256, 128), (1000, 128, 84), (1000, 84, 10), (100, 256, 128),
+                                   (7, 5, 3), (256, 25088, 512), (300, 512, 10), (512, 512, 512)])
+def test_dense_forward_equals_separate_calls(dev, dtype, shape):
+    bs, ins, outs = shape
+    rng = np.random.default_rng(41 + outs)
+    x = _prep(rng.standard_normal((bs, ins)), dtype)
+    a = np.sqrt(2.0 / ins)
+    w = _prep(rng.uniform(-a, a, (ins, outs)), dtype)
+    b = _prep(rng.uniform(-a, a, outs), dtype)
+    xd, wd, bd = dev.tensor(x, dtype), dev.tensor(w, dtype), dev.tensor(b, dtype)
+    for bias in (None, bd):
+        for relu in (False, True):
+            fused = dev.dense_forward(xd, wd, bias=bias, relu=relu)
+            y = dev.dot(xd, wd)
+            if bias is not None:
+                y = dev.bias_add(y, bias)
+            if relu:
+                y = dev.relu(y)
+            assert torch.equal(fused, y), (shape, bias is not None, relu)
+    ref = x.astype(np.float64) @ w.astype(np.float64) + b
+    got = dev.dense_forward(xd, wd, bias=bd).float().cpu().numpy()
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5 * np.sqrt(ins)
+    assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
+
+
+def test_fused_errors(dev):
+    import autograph_b200 as ag
+    x = dev.empty((2, 1, 6, 6), torch.float32)
+    w = dev.empty((4, 1, 5, 5), torch.float32)
+    with pytest.raises(ag.AgError):
+        dev.conv2_relu_max_pool2(x, w, pool=(3, 3))       # conv output 2x2 < window
+    with pytest.raises(ag.AgError, match="a_cols != b_rows"):
+        dev.dense_forward(dev.empty((2, 3), torch.float32), dev.empty((4, 5), torch.float32))
