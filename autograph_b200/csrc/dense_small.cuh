@@ -1,0 +1,19 @@
+// Small row-major products y = x . w (+ bias) (relu): the Dense layers of
+// LeNet5-sized networks at small batch (see dense_small.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace ag {
+namespace dense_small {
+
+// True when the latency-oriented kernel should take y[m,n] = x[m,k] . w[k,n]
+// (all row-major contiguous): few rows, narrow output, moderate k.
+bool eligible(int64_t m, int64_t k, int64_t n);
+
+template <class T>
+int forward(ag_device *dev, const T *x, int m, int k, const T *w, int n, const T *bias, bool relu,
+            T *y);
+
+}  // namespace dense_small
+}  // namespace ag

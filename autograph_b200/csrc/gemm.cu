@@ -1,5 +1,6 @@
 // ag_gemm: argument checks and routing to the SIMT tile engine (f32, and bf16
 // shapes the tensor-core kernel does not take) or the tcgen05 kernel (bf16).
+#include "dense_small.cuh"
 #include "gemm_simt_launch.cuh"
 #include "gemm_tc.cuh"
 
@@ -75,6 +76,15 @@ extern "C" int ag_dense_forward(ag_device *dev, ag_dtype dtype, const void *x, i
                "dimension beyond 2^31");
     if (bs == 0 || outputs == 0) return AG_OK;
     AG_REQUIRE(y && (inputs == 0 || (x && w)), AG_ERR_INVALID, "null tensor pointer");
+    if (dense_small::eligible(bs, inputs, outputs)) {
+        if (dtype == AG_F32)
+            return dense_small::forward<float>(dev, (const float *)x, (int)bs, (int)inputs,
+                                               (const float *)w, (int)outputs, (const float *)bias,
+                                               fuse_relu != 0, (float *)y);
+        return dense_small::forward<__nv_bfloat16>(
+            dev, (const __nv_bfloat16 *)x, (int)bs, (int)inputs, (const __nv_bfloat16 *)w,
+            (int)outputs, (const __nv_bfloat16 *)bias, fuse_relu != 0, (__nv_bfloat16 *)y);
+    }
     if (dtype == AG_F32)
         return dense_forward_simt<float>(dev, (const float *)x, (int)bs, (int)inputs,
                                          (const float *)w, (int)outputs, (const float *)bias,
@@ -108,6 +118,18 @@ extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int
     AG_REQUIRE(c != nullptr && (k == 0 || (a != nullptr && b != nullptr)), AG_ERR_INVALID,
                "null operand pointer");
     AG_REQUIRE(off_a >= 0 && off_b >= 0 && off_c >= 0, AG_ERR_INVALID, "negative offset");
+    // Small plain products (row-major contiguous operands, alpha = 1, beta = 0) share the
+    // latency-oriented kernel with ag_dense_forward.
+    if (alpha == 1.f && beta == 0.f && k > 0 && csa == 1 && rsa == k && csb == 1 && rsb == n &&
+        csc == 1 && rsc == n && dense_small::eligible(m, k, n)) {
+        if (dtype == AG_F32)
+            return dense_small::forward<float>(dev, (const float *)a + off_a, (int)m, (int)k,
+                                               (const float *)b + off_b, (int)n, nullptr, false,
+                                               (float *)c + off_c);
+        return dense_small::forward<__nv_bfloat16>(
+            dev, (const __nv_bfloat16 *)a + off_a, (int)m, (int)k, (const __nv_bfloat16 *)b + off_b,
+            (int)n, nullptr, false, (__nv_bfloat16 *)c + off_c);
+    }
     if (dtype == AG_F32) {
         return gemm_simt_dispatch<float>(dev, (int)m, (int)k, (int)n, alpha,
                                          (const float *)a + off_a, rsa, csa,

@@ -29,8 +29,9 @@ struct TileCfg {
 
 using CfgL = TileCfg<128, 128, 16, 8, 8, 2>;  // 256 threads, large problems
 using CfgM = TileCfg<64, 64, 16, 4, 4, 3>;   // 256 threads, medium problems
-using CfgXS = TileCfg<32, 32, 16, 4, 4, 8>;   // 64 threads, small problems (more CTAs)
+using CfgXS = TileCfg<32, 32, 32, 4, 4, 8>;   // 64 threads, small problems (more CTAs, fewer k steps)
 using CfgS16 = TileCfg<128, 16, 16, 4, 4, 4>;  // 128 threads, n <= 16
+using CfgS16s = TileCfg<32, 16, 32, 4, 4, 8>;  // 32 threads, n <= 16 and few rows
 using CfgS8 = TileCfg<256, 8, 16, 4, 4, 4>;    // 128 threads, n <= 8
 
 // ---------------------------------------------------------------- accessors

@@ -19,9 +19,10 @@ int launch_cfg(ag_device *dev, int M, int N, int K, int splits, int k_chunk, con
     return AG_OK;
 }
 
-enum CfgId { kCfgL, kCfgM, kCfgXS, kCfgS16, kCfgS8 };
+enum CfgId { kCfgL, kCfgM, kCfgXS, kCfgS16, kCfgS16s, kCfgS8 };
 
 inline CfgId pick_cfg(int M, int N, int sms) {
+    if (N <= 16 && ceil_div(M, 128) * 2 < sms) return kCfgS16s;
     if (N <= 8) return kCfgS8;
     if (N <= 16) return kCfgS16;
     int64_t tiles_l = ceil_div(M, 128) * ceil_div(N, 128);
@@ -37,6 +38,7 @@ inline void cfg_dims(CfgId id, int &bm, int &bn) {
         case kCfgM: bm = 64; bn = 64; break;
         case kCfgXS: bm = 32; bn = 32; break;
         case kCfgS16: bm = 128; bn = 16; break;
+        case kCfgS16s: bm = 32; bn = 16; break;
         default: bm = 256; bn = 8; break;
     }
 }
@@ -49,6 +51,7 @@ int launch_any(ag_device *dev, CfgId id, int M, int N, int K, int splits, int k_
         case kCfgM: return launch_cfg<CfgM>(dev, M, N, K, splits, k_chunk, A, B, E);
         case kCfgXS: return launch_cfg<CfgXS>(dev, M, N, K, splits, k_chunk, A, B, E);
         case kCfgS16: return launch_cfg<CfgS16>(dev, M, N, K, splits, k_chunk, A, B, E);
+        case kCfgS16s: return launch_cfg<CfgS16s>(dev, M, N, K, splits, k_chunk, A, B, E);
         default: return launch_cfg<CfgS8>(dev, M, N, K, splits, k_chunk, A, B, E);
     }
 }
@@ -81,7 +84,7 @@ int gemm(ag_device *dev, int M, int N, int K, const AOp &A, const BOp &B, const 
         if (fit < splits) splits = (int)(fit < 1 ? 1 : fit);
     }
     if (splits <= 1) return launch_any(dev, id, M, N, K, 1, K > 0 ? K : 1, A, B, E);
-    int k_chunk = (int)(ceil_div(ceil_div(K, splits), 16) * 16);
+    int k_chunk = (int)(ceil_div(ceil_div(K, splits), 32) * 32);  // multiple of every BK
     splits = (int)ceil_div(K, k_chunk);
     int64_t plane = (int64_t)M * N;
     void *ws = scratch;

@@ -522,6 +522,8 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
               int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
               float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc) {
     (void)csc;
+    if (gemm_bf16_pair_enabled() && m >= 256 && n >= 256)
+        return gemm_bf16_pair(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta, c, rsc, csc);
     const bool a_mn = !(csa == 1 && rsa % 8 == 0 && rsa >= k);  // else contiguous along m
     const bool b_mn = !(rsb == 1 && csb % 8 == 0 && csb >= k);  // else contiguous along n
     CUtensorMap ta, tb;

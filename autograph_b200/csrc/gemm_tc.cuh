@@ -17,5 +17,12 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
               int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
               float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc);
 
+// Paired-SM variant (cta_group::2, 256 x 256 tile per CTA pair): used for m, n >= 256
+// unless the environment variable AG_TC2=0 selects the single-CTA kernel.
+bool gemm_bf16_pair_enabled();
+int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloat16 *a,
+                   int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
+                   float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc);
+
 }  // namespace tc
 }  // namespace ag
