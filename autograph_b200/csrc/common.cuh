@@ -40,6 +40,8 @@ int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)))
 
 // Counts kernel launches enqueued by the library (ag_kernel_launch_count).
 void count_launch();
+void count_launches(uint64_t n);
+uint64_t launch_count();
 
 // Checks the launch that was just enqueued.
 #define AG_CHECK_LAUNCH()                  \

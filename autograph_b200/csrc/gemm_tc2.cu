@@ -207,7 +207,7 @@ struct Params {
 struct Work {
     int m_blk, n_blk;
     int n_off;    // column offset of this piece inside the tile
-    int n_width;  // 256, 128 or 64
+    int n_width;  // 256, or 128 for a piece of a tail tile
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int &m_blk, int &n_blk) {
@@ -240,7 +240,8 @@ __device__ __forceinline__ Work decode_work(int w, const Params &p, int num_m, i
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_b_tail, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs of the pair compute the same aligned offset (the dynamic shared memory
     // window starts at the same address in every CTA of a kernel).
@@ -271,6 +272,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        prefetch_tmap(&tmap_b_tail);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -355,11 +357,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         for (int i = 0; i < half_n / 64; ++i)
                             tma_load_2d_pair(b_dst + i * ATOM_BYTES, &tmap_b, bar, n0 + i * 64,
                                              kb * BLOCK_K);
+                    } else if (half_n == 128) {
+                        tma_load_2d_pair(b_dst, &tmap_b, bar, kb * BLOCK_K, n0);
                     } else {
-                        // 32-row boxes: 4 per stage for a whole tile, fewer for a tail piece
-                        for (int i = 0; i < half_n / 32; ++i)
-                            tma_load_2d_pair(b_dst + i * (32 * BLOCK_K * 2), &tmap_b, bar,
-                                             kb * BLOCK_K, n0 + i * 32);
+                        // tail pieces: one 64-row box (tmap_b_tail) per stage
+                        tma_load_2d_pair(b_dst, &tmap_b_tail, bar, kb * BLOCK_K, n0);
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -542,14 +544,14 @@ static int make_tmap2(CUtensorMap *map, const void *base, uint64_t inner, uint64
 
 template <bool A_MN, bool B_MN>
 static int launch_pair(ag_device *dev, const CUtensorMap &ta, const CUtensorMap &tb,
-                       const pair::Params &p) {
+                       const CUtensorMap &tb_tail, const pair::Params &p) {
     auto kernel = pair::gemm_bf16_tc2_kernel<A_MN, B_MN>;
     AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      pair::SMEM_BYTES));
     const int tiles = (int)(ceil_div(p.M, pair::TILE_M) * ceil_div(p.N, pair::TILE_N));
     int pairs = dev->sm_count / 2;
     if (tiles < pairs) pairs = tiles;
-    kernel<<<2 * pairs, pair::NUM_THREADS, pair::SMEM_BYTES, dev->stream>>>(ta, tb, p);
+    kernel<<<2 * pairs, pair::NUM_THREADS, pair::SMEM_BYTES, dev->stream>>>(ta, tb, tb_tail, p);
     AG_CHECK_LAUNCH();
     return AG_OK;
 }
@@ -568,7 +570,7 @@ int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_
     (void)csc;
     const bool a_mn = !(csa == 1 && rsa % 8 == 0 && rsa >= k);
     const bool b_mn = !(rsb == 1 && csb % 8 == 0 && csb >= k);
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tb_tail;
     if (a_mn)
         AG_TRY(make_tmap2(&ta, a, (uint64_t)m, (uint64_t)k, (uint64_t)csa, 64, pair::BLOCK_K));
     else
@@ -576,7 +578,11 @@ int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_
     if (b_mn)
         AG_TRY(make_tmap2(&tb, b, (uint64_t)n, (uint64_t)k, (uint64_t)rsb, 64, pair::BLOCK_K));
     else
-        AG_TRY(make_tmap2(&tb, b, (uint64_t)k, (uint64_t)n, (uint64_t)csb, pair::BLOCK_K, 32));
+        AG_TRY(make_tmap2(&tb, b, (uint64_t)k, (uint64_t)n, (uint64_t)csb, pair::BLOCK_K, 128));
+    if (b_mn)
+        tb_tail = tb;
+    else
+        AG_TRY(make_tmap2(&tb_tail, b, (uint64_t)k, (uint64_t)n, (uint64_t)csb, pair::BLOCK_K, 64));
     pair::Params p;
     p.M = m;
     p.N = n;
@@ -591,19 +597,22 @@ int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_
         int pairs = dev->sm_count / 2;
         if (tiles < pairs) pairs = tiles;
         const int rem = tiles % pairs;
+        static const bool tail_enabled = []() {
+            const char *e = getenv("AG_TC2_TAIL");
+            return !(e && e[0] == '0');
+        }();
         int split = 1;
-        if (rem > 0 && tiles > pairs) {
-            if (4 * rem <= pairs && !b_mn) split = 4;
-            else if (2 * rem <= pairs) split = 2;
+        if (tail_enabled && rem > 0 && tiles > pairs) {
+            if (2 * rem <= pairs) split = 2;
         }
         p.tail_split = split;
         p.t_full = split > 1 ? tiles - rem : tiles;
         p.num_work = p.t_full + (split > 1 ? split * rem : 0);
     }
-    if (a_mn && b_mn) return launch_pair<true, true>(dev, ta, tb, p);
-    if (a_mn) return launch_pair<true, false>(dev, ta, tb, p);
-    if (b_mn) return launch_pair<false, true>(dev, ta, tb, p);
-    return launch_pair<false, false>(dev, ta, tb, p);
+    if (a_mn && b_mn) return launch_pair<true, true>(dev, ta, tb, tb_tail, p);
+    if (a_mn) return launch_pair<true, false>(dev, ta, tb, tb_tail, p);
+    if (b_mn) return launch_pair<false, true>(dev, ta, tb, tb_tail, p);
+    return launch_pair<false, false>(dev, ta, tb, tb_tail, p);
 }
 
 }  // namespace tc

@@ -2,6 +2,7 @@
 // access, inference and training steps (the counterpart of LeNet5Classifier in
 // benches/neural-network-benches/src/autograph_backend.rs:16-85).
 #include <cmath>
+#include <cstdlib>
 #include <cuda_bf16.h>
 
 #include "../common.cuh"
@@ -9,10 +10,36 @@
 
 using namespace autograph;
 
+// Captured inference passes for one input shape.  A graph holds the input copy
+// (device -> staging, or pinned host -> staging), the kernels of the layer chain
+// and the output copy; per call only the two copy nodes are re-pointed at the
+// caller's buffers, so a whole step is one graph launch.  Replaying removes the
+// per-kernel launch cost, which dominates at small batch.
+struct CapturedPass {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaGraphNode_t in_node = nullptr, out_node = nullptr;
+    const void *y_ptr = nullptr;  // the chain's output inside the graph
+    Pool::Parked parked;          // intermediate buffers baked into the graph
+    uint64_t kernels = 0;         // kernel launches recorded in the graph
+    int seen = 0;                 // calls before a graph exists
+};
+
+struct GraphEntry {
+    int64_t bs = 0, c = 0, h = 0, w = 0;
+    Tensor x_stage;               // the graphs' input
+    size_t out_bytes = 0;
+    CapturedPass from_device, from_host;
+    uint64_t last_use = 0;
+};
+
 struct ag_model {
     ag_device *dev;
     ag_dtype dtype;
     Pool pool;  // declared before every tensor so that it is destroyed last
+    std::vector<GraphEntry> graphs;
+    uint64_t tick = 0;
+    bool graphs_enabled = true;
     std::vector<std::unique_ptr<Layer>> layers;
     std::vector<Parameter *> params;
     std::vector<int64_t> offsets;  // element offset of each parameter in the buckets
@@ -21,7 +48,23 @@ struct ag_model {
     bool use_momentum = false;
     float momentum = 0.f;
     float grad_scale = 1.f;
-    ag_model(ag_device *d, ag_dtype t) : dev(d), dtype(t), pool(d) {}
+    ag_model(ag_device *d, ag_dtype t) : dev(d), dtype(t), pool(d) {
+        const char *e = getenv("AG_GRAPH");
+        graphs_enabled = !(e && e[0] == '0');
+    }
+    void drop(CapturedPass &p) {
+        if (p.exec) cudaGraphExecDestroy(p.exec);
+        if (p.graph) cudaGraphDestroy(p.graph);
+        p.exec = nullptr;
+        p.graph = nullptr;
+        pool.unpark(p.parked);
+    }
+    ~ag_model() {
+        for (auto &g : graphs) {
+            drop(g.from_device);
+            drop(g.from_host);
+        }
+    }
 };
 
 namespace {
@@ -153,6 +196,115 @@ Variable forward_chain(ag_model *m, Variable v) {
         v = l->forward(m->pool, v);
     }
     return v;
+}
+
+constexpr size_t kMaxGraphs = 16;
+
+GraphEntry *find_graph(ag_model *m, int64_t bs, int64_t c, int64_t h, int64_t w) {
+    for (auto &g : m->graphs)
+        if (g.bs == bs && g.c == c && g.h == h && g.w == w) return &g;
+    if (m->graphs.size() >= kMaxGraphs) {
+        size_t victim = 0;
+        for (size_t i = 1; i < m->graphs.size(); ++i)
+            if (m->graphs[i].last_use < m->graphs[victim].last_use) victim = i;
+        m->drop(m->graphs[victim].from_device);
+        m->drop(m->graphs[victim].from_host);
+        m->graphs.erase(m->graphs.begin() + victim);
+    }
+    m->graphs.emplace_back();
+    GraphEntry &g = m->graphs.back();
+    g.bs = bs; g.c = c; g.h = h; g.w = w;
+    g.x_stage = Tensor::uninit(m->pool, {bs, c, h, w}, m->dtype);
+    return &g;
+}
+
+bool is_pinned_host(const void *p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeHost;
+}
+
+// One inference pass x -> out.  `host` selects host pointers (x and out in host
+// memory: H2D, chain, D2H) or device pointers (D2D, chain, D2D).  The first call for
+// a shape runs eagerly; the second captures the pass; later calls replay it.
+void run_inference(ag_model *m, GraphEntry *g, bool host, const void *x, void *out) {
+    g->last_use = ++m->tick;
+    cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
+    CapturedPass &cp = host ? g->from_host : g->from_device;
+    const cudaMemcpyKind kin = host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+    const cudaMemcpyKind kout = host ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    auto cuda_ok = [](cudaError_t e, const char *what) {
+        if (e != cudaSuccess)
+            throw Error(AG_ERR_CUDA, std::string(what) + " failed: " + cudaGetErrorString(e));
+    };
+    if (cp.exec) {
+        cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(cp.exec, cp.in_node, g->x_stage.data(), x,
+                                                    g->x_stage.nbytes(), kin), "graph input update");
+        cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(cp.exec, cp.out_node, out, cp.y_ptr, g->out_bytes,
+                                                    kout), "graph output update");
+        cuda_ok(cudaGraphLaunch(cp.exec, stream), "cudaGraphLaunch");
+        ::ag::count_launches(cp.kernels);  // the replay enqueues the captured kernels
+        return;
+    }
+    const void *y_ptr = nullptr;
+    auto pass = [&]() {
+        cuda_ok(cudaMemcpyAsync(g->x_stage.data(), x, g->x_stage.nbytes(), kin, stream), "input copy");
+        Variable y = forward_chain(m, Variable{g->x_stage, nullptr});
+        g->out_bytes = y.value.nbytes();
+        y_ptr = y.value.data();
+        cuda_ok(cudaMemcpyAsync(out, y_ptr, g->out_bytes, kout, stream), "output copy");
+    };
+    const bool capturable = m->graphs_enabled && g->bs > 0 &&
+                            (!host || (is_pinned_host(x) && is_pinned_host(out)));
+    if (!capturable || ++cp.seen < 2) {
+        pass();
+        return;
+    }
+    // Capture.  Blocks released while capturing stay parked with the graph.
+    m->pool.set_hold(&cp.parked);
+    const uint64_t launches_before = ::ag::launch_count();
+    bool ok = cudaStreamBeginCapture(stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+    if (ok) {
+        try {
+            pass();
+        } catch (...) {
+            ok = false;
+        }
+        ok = (cudaStreamEndCapture(stream, &cp.graph) == cudaSuccess) && ok && cp.graph != nullptr;
+    }
+    m->pool.set_hold(nullptr);
+    cp.kernels = ::ag::launch_count() - launches_before;
+    cp.y_ptr = y_ptr;
+    if (ok) {
+        // Find the two copy nodes by the buffers they touch.
+        size_t n = 0;
+        ok = cudaGraphGetNodes(cp.graph, nullptr, &n) == cudaSuccess && n > 0;
+        std::vector<cudaGraphNode_t> nodes(n);
+        if (ok) ok = cudaGraphGetNodes(cp.graph, nodes.data(), &n) == cudaSuccess;
+        for (size_t i = 0; ok && i < n; ++i) {
+            cudaGraphNodeType type;
+            if (cudaGraphNodeGetType(nodes[i], &type) != cudaSuccess) { ok = false; break; }
+            if (type != cudaGraphNodeTypeMemcpy) continue;
+            cudaMemcpy3DParms mp;
+            if (cudaGraphMemcpyNodeGetParams(nodes[i], &mp) != cudaSuccess) { ok = false; break; }
+            if (mp.dstPtr.ptr == g->x_stage.data()) cp.in_node = nodes[i];
+            if (mp.srcPtr.ptr == y_ptr) cp.out_node = nodes[i];
+        }
+        ok = ok && cp.in_node && cp.out_node;
+    }
+    if (ok) ok = cudaGraphInstantiate(&cp.exec, cp.graph, 0) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        m->drop(cp);
+        m->graphs_enabled = false;  // this model runs eagerly from now on
+        pass();
+        return;
+    }
+    cuda_ok(cudaGraphLaunch(cp.exec, stream), "cudaGraphLaunch");
+    ::ag::count_launches(cp.kernels);
 }
 
 Tensor input_tensor(ag_model *m, const void *x, bool on_host, int64_t bs, int64_t c, int64_t h,
@@ -301,9 +453,13 @@ int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, i
     AG_REQUIRE(model && logits_host, AG_ERR_INVALID, "null argument");
     AG_ENTER(model->dev);
     AG_HOST_GUARD({
-        Tensor x = input_tensor(model, x_host, true, bs, c, h, w);
-        Variable y = forward_chain(model, Variable{x, nullptr});
-        y.value.to_host(logits_host);
+        if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+        if (!x_host && bs > 0) throw Error(AG_ERR_INVALID, "input pointer is null");
+        GraphEntry *g = find_graph(model, bs, c, h, w);
+        run_inference(model, g, true, x_host, logits_host);
+        cudaError_t e = cudaStreamSynchronize((cudaStream_t)ag_device_stream(model->dev));
+        if (e != cudaSuccess)
+            throw Error(AG_ERR_CUDA, std::string("cudaStreamSynchronize failed: ") + cudaGetErrorString(e));
     })
 }
 
@@ -312,9 +468,10 @@ int ag_model_forward_device(ag_model *model, const void *x_dev, int64_t bs, int6
     AG_REQUIRE(model && logits_dev, AG_ERR_INVALID, "null argument");
     AG_ENTER(model->dev);
     AG_HOST_GUARD({
-        Tensor x = input_tensor(model, x_dev, false, bs, c, h, w);
-        Variable y = forward_chain(model, Variable{x, nullptr});
-        check(ag_copy(model->dev, logits_dev, y.value.data(), y.value.nbytes()));
+        if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+        if (!x_dev && bs > 0) throw Error(AG_ERR_INVALID, "input pointer is null");
+        GraphEntry *g = find_graph(model, bs, c, h, w);
+        run_inference(model, g, false, x_dev, logits_dev);
     })
 }
 

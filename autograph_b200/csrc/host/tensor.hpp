@@ -75,7 +75,21 @@ class Pool {
         check(ag_alloc(dev_, cls, &p));
         return p;
     }
-    void release(void *p, size_t cls) { free_[cls].push_back(p); }
+    void release(void *p, size_t cls) {
+        if (hold_)
+            hold_->push_back({p, cls});
+        else
+            free_[cls].push_back(p);
+    }
+    // While a sink is set, released blocks are parked in it instead of becoming
+    // reusable.  A captured CUDA graph keeps the addresses of its intermediate
+    // buffers; parking them keeps those buffers private to the graph.
+    using Parked = std::vector<std::pair<void *, size_t>>;
+    void set_hold(Parked *sink) { hold_ = sink; }
+    void unpark(Parked &blocks) {
+        for (auto &b : blocks) free_[b.second].push_back(b.first);
+        blocks.clear();
+    }
 
    private:
     static size_t size_class(size_t bytes) {
@@ -91,6 +105,7 @@ class Pool {
     }
     ag_device *dev_;
     std::map<size_t, std::vector<void *>> free_;
+    Parked *hold_ = nullptr;
 };
 
 struct Buffer {

@@ -22,6 +22,8 @@ int fail(int status, const char *fmt, ...) {
 static std::atomic<uint64_t> g_launches{0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+void count_launches(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+uint64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int workspace(ag_device *dev, size_t bytes, void **out) {
     if (bytes > dev->workspace_bytes) {

@@ -32,7 +32,7 @@ def _check(c, ref, tol=1e-2):
 @pytest.mark.parametrize("shape", [(128, 64, 256), (256, 256, 256), (384, 200, 520),
                                    (1024, 1024, 1024),
                                    # 84 tiles of 256x256 on 74 SM pairs: the 10 tiles of the
-                                   # partial wave are cut into 4 (k-major B) or 2 pieces
+                                   # partial wave are cut into 2 pieces along n
                                    (3072, 256, 1792), (2560, 192, 2000)])
 def test_bf16_vs_f64(dev, layout, shape):
     m, k, n = shape
