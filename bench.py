@@ -120,6 +120,7 @@ def cpu_forward_rate(seconds: float, min_steps: int = 2):
     threaded GEMM) on all host cores, on batches of 1000 for about `seconds`."""
     import oracle
     from oracle import models
+    oracle.use_all_cores()
     P = models.init_params(models.LENET5, 2000)
     x = np.random.default_rng(1000).uniform(0, 1, (BATCH, 1, 28, 28)).astype(np.float32)
     models.forward(models.LENET5, P, x, fast=True)  # warm-up
@@ -141,6 +142,7 @@ def run_reference(args):
         return
     import oracle
     from oracle import models
+    oracle.use_all_cores()
     P = models.init_params(models.LENET5, 2000)
     x = np.random.default_rng(1000).uniform(0, 1, (BATCH, 1, 28, 28)).astype(np.float32)
     for _ in range(max(args.warmup, 1)):
@@ -262,6 +264,13 @@ def run_gpu(args):
         "e2e": e2e, "gpu_launches": int(launches),
     }
 
+    # configs[4b]: data-parallel training, 100 images per GPU, one NCCL sum-all-reduce of the
+    # flat gradient bucket per step, 1/world folded into the update.  Runs on every rank.
+    try:
+        line["train_dp"] = train_data_parallel(torch, ag, dp, dev, rank, world, barrier,
+                                               max_over_ranks)
+    except Exception as exc:
+        line["train_dp_error"] = repr(exc)
     if rank == 0:
         line["roofline"], line["stages"] = lenet5_roofline(torch, ag, dev, model, xs, K, peaks)
         if not args.quick:
@@ -288,6 +297,35 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def train_data_parallel(torch, ag, dp, dev, rank, world, barrier, max_over_ranks):
+    m = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)   # same seed: replicated parameters
+    m.set_sgd(None)
+    m.set_grad_scale(1.0 / world)
+    gen = torch.Generator(device=dev.torch_device).manual_seed(7000 + rank)
+    x = torch.rand((100, 1, 28, 28), generator=gen, device=dev.torch_device)
+    t = torch.randint(0, 10, (100,), generator=gen, device=dev.torch_device, dtype=torch.uint8)
+    bucket = None
+
+    def step(i):
+        nonlocal bucket
+        loss, ptr, length = m.train_forward_backward(x, t)
+        if bucket is None:
+            bucket = dp.bucket_view(ptr, length, torch.float32, dev.torch_device)
+        dp.allreduce_gradients(bucket, world)
+        m.apply_update(0.01)
+
+    for i in range(5):
+        step(i)
+    barrier()
+    n = 50
+    ms = max_over_ranks(event_time_ms(torch, step, n, dev.stream)) / n
+    barrier()
+    out = {"ms_per_step": ms, "img_per_s": 100 * world / ms * 1e3, "global_batch": 100 * world,
+           "allreduce_elements": int(bucket.numel()), "collective": "nccl all_reduce(sum)" if world > 1 else "none"}
+    m.close()
+    return out
 
 
 def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):

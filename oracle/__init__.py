@@ -75,6 +75,13 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def use_all_cores() -> int:
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(int(n))
+    return num_threads()
+
+
 def round_bf16(x: np.ndarray) -> np.ndarray:
     """Round float32 values to the nearest bf16 (ties to even), kept as float32."""
     y = np.ascontiguousarray(x, dtype=np.float32).copy()

@@ -51,6 +51,15 @@ ORC_API void orc_round_bf16(float *x, int64_t n) {
     for (int64_t i = 0; i < n; ++i) x[i] = bf16_round(x[i]);
 }
 
+/* Overrides OMP_NUM_THREADS (launchers such as torchrun set it to 1). */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
