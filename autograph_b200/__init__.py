@@ -202,6 +202,22 @@ class Device:
                                            w.shape[1], _ptr(bias), int(relu), _ptr(y)))
         return y
 
+    def dense_chain_forward(self, x, weights, biases=None, relus=None):
+        """A run of Dense (+ Relu) layers in one call; weights[i] is [in_i, out_i]."""
+        n = len(weights)
+        biases = biases or [None] * n
+        relus = relus or [False] * n
+        dims = (ctypes.c_int64 * (n + 1))(x.shape[1], *[w.shape[1] for w in weights])
+        ws = (ctypes.c_void_p * n)(*[w.contiguous().data_ptr() for w in weights])
+        bs = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
+        rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
+        y = self.empty((x.shape[0], weights[-1].shape[1]), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_dense_chain_forward(self._h, _dtype_code(x.dtype),
+                                                 _ptr(x.contiguous()), x.shape[0], n, dims, ws, bs,
+                                                 rl, _ptr(y)))
+        return y
+
     def conv2_backward_input(self, w, dy, input_hw, padding=(0, 0), stride=(1, 1),
                              dilation=(1, 1)):
         oc, ic, fh, fw = w.shape

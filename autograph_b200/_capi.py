@@ -68,6 +68,8 @@ _SIGNATURES = {
                                        c_int64, c_int64, c_int64, _P, c_int64, c_int64, c_int64,
                                        c_float, _P, c_int64, c_int64, c_int64]),
     "ag_dense_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, _P, c_int64, _P, c_int, _P]),
+    "ag_dense_chain_forward": (c_int, [_P, c_int, _P, c_int64, c_int32, POINTER(c_int64),
+                                       POINTER(_P), POINTER(_P), POINTER(c_int32), _P]),
     "ag_conv2_relu_max_pool2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
                                                 _P, c_int64, _P, POINTER(ConvOptions), c_int,
                                                 c_int32, c_int32, _P]),

@@ -95,6 +95,136 @@ int forward(ag_device *dev, const T *x, int m, int k, const T *w, int n, const T
     return AG_OK;
 }
 
+// ---------------------------------------------------------------- layer chain
+struct ChainStep {
+    const void *w, *bias;
+    int K, N, np, slices, kchunk, relu;
+};
+struct ChainParams {
+    ChainStep s[kMaxChain];
+    int n_layers, M, max_k, red_floats;
+};
+
+static void plan_step(int k, int n, int *np, int *slices, int *kchunk) {
+    *np = ((n + 31) / 32) * 32;
+    int sl = 1024 / *np;
+    if (sl > 16) sl = 16;
+    if (sl > k / 8) sl = k / 8;
+    if (sl < 1) sl = 1;
+    *kchunk = (k + sl - 1) / sl;
+    *slices = (k + *kchunk - 1) / *kchunk;
+}
+
+template <class T>
+__global__ void __launch_bounds__(1024)
+    dense_chain_kernel(const T *__restrict__ x, T *__restrict__ y, const ChainParams p) {
+    extern __shared__ __align__(16) float smem[];
+    float *xa = smem;                              // [max_k][ROWS] current layer input
+    float *xb = smem + (size_t)p.max_k * ROWS;     // next layer input
+    float *red = xb + (size_t)p.max_k * ROWS;      // [slices][ROWS][np]
+    const int m0 = blockIdx.x * ROWS;
+    const int rows = min(ROWS, p.M - m0);
+    {
+        const int K = p.s[0].K;
+        for (int i = threadIdx.x; i < ROWS * K; i += blockDim.x) {
+            const int r = i / K, k = i - r * K;
+            xa[k * ROWS + r] = (r < rows) ? to_f32(x[(int64_t)(m0 + r) * K + k]) : 0.f;
+        }
+    }
+    __syncthreads();
+    for (int l = 0; l < p.n_layers; ++l) {
+        const ChainStep st = p.s[l];
+        const T *w = reinterpret_cast<const T *>(st.w);
+        const T *bias = reinterpret_cast<const T *>(st.bias);
+        const int n = threadIdx.x % st.np, slice = threadIdx.x / st.np;
+        if (slice < st.slices) {
+            float acc[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+            if (n < st.N) {
+                const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
+                const T *wp = w + (int64_t)k0 * st.N + n;
+#pragma unroll 8
+                for (int k = k0; k < k1; ++k, wp += st.N) {
+                    const float wv = to_f32(*wp);
+                    const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
+                    const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
+                    acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
+                    acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
+                    acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
+                    acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * st.np + n] = acc[r];
+        }
+        __syncthreads();
+        const bool last = l + 1 == p.n_layers;
+        for (int i = threadIdx.x; i < ROWS * st.np; i += blockDim.x) {
+            const int r = i / st.np, c = i - r * st.np;
+            if (c >= st.N) continue;
+            float s = 0.f;
+            for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
+            float v = to_f32(from_f32<T>(s));
+            if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
+            if (st.relu) v = (v >= 0.f) ? v : 0.f;
+            if (last) {
+                if (r < rows) y[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
+            } else {
+                xb[c * ROWS + r] = v;  // already rounded to T: equals storing and reloading it
+            }
+        }
+        __syncthreads();
+        float *t = xa;
+        xa = xb;
+        xb = t;
+    }
+}
+
+bool chain_eligible(int64_t m, int n_layers, const ChainLayer *layers) {
+    if (n_layers < 2 || n_layers > kMaxChain) return false;
+    for (int i = 0; i < n_layers; ++i) {
+        if (!eligible(m, layers[i].inputs, layers[i].outputs)) return false;
+        if (i > 0 && layers[i].inputs != layers[i - 1].outputs) return false;
+    }
+    return true;
+}
+
+template <class T>
+int chain_forward(ag_device *dev, const T *x, int m, int n_layers, const ChainLayer *layers, T *y) {
+    ChainParams p;
+    p.n_layers = n_layers;
+    p.M = m;
+    p.max_k = 0;
+    p.red_floats = 0;
+    int threads = 32;
+    for (int i = 0; i < n_layers; ++i) {
+        ChainStep &st = p.s[i];
+        st.w = layers[i].w;
+        st.bias = layers[i].bias;
+        st.K = layers[i].inputs;
+        st.N = layers[i].outputs;
+        st.relu = layers[i].relu;
+        plan_step(st.K, st.N, &st.np, &st.slices, &st.kchunk);
+        if (st.K > p.max_k) p.max_k = st.K;
+        if (st.N > p.max_k) p.max_k = st.N;  // a layer's output is the next layer's input
+        if (st.slices * ROWS * st.np > p.red_floats) p.red_floats = st.slices * ROWS * st.np;
+        if (st.np * st.slices > threads) threads = st.np * st.slices;
+    }
+    const size_t smem = ((size_t)2 * p.max_k * ROWS + (size_t)p.red_floats) * sizeof(float);
+    auto kernel = dense_chain_kernel<T>;
+    if (smem > 48 * 1024)
+        AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    kernel<<<(unsigned)ceil_div(m, ROWS), threads, smem, dev->stream>>>(x, y, p);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+template int chain_forward<float>(ag_device *, const float *, int, int, const ChainLayer *, float *);
+template int chain_forward<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, int, int,
+                                          const ChainLayer *, __nv_bfloat16 *);
+
 template int forward<float>(ag_device *, const float *, int, int, const float *, int, const float *,
                             bool, float *);
 template int forward<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, int, int,

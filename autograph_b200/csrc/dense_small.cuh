@@ -15,5 +15,19 @@ template <class T>
 int forward(ag_device *dev, const T *x, int m, int k, const T *w, int n, const T *bias, bool relu,
             T *y);
 
+// A chain of up to kMaxChain small dense layers (each followed by an optional
+// relu) run by one kernel: the 8 rows a CTA owns pass from layer to layer
+// through shared memory, so the intermediate activations never leave the SM.
+constexpr int kMaxChain = 4;
+struct ChainLayer {
+    const void *w;     // [inputs, outputs]
+    const void *bias;  // [outputs] or null
+    int inputs, outputs;
+    int relu;
+};
+bool chain_eligible(int64_t m, int n_layers, const ChainLayer *layers);
+template <class T>
+int chain_forward(ag_device *dev, const T *x, int m, int n_layers, const ChainLayer *layers, T *y);
+
 }  // namespace dense_small
 }  // namespace ag

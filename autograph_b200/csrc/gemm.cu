@@ -103,6 +103,54 @@ extern "C" int ag_dense_forward(ag_device *dev, ag_dtype dtype, const void *x, i
                                              (const __nv_bfloat16 *)bias, fuse_relu != 0, py);
 }
 
+extern "C" int ag_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                      int32_t n_layers, const int64_t *dims,
+                                      const void *const *weights, const void *const *biases,
+                                      const int32_t *relu, void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(dtype == AG_F32 || dtype == AG_BF16, AG_ERR_DTYPE, "Dense %d not implemented",
+               (int)dtype);
+    AG_REQUIRE(n_layers >= 1 && dims && weights && relu, AG_ERR_INVALID, "null or empty chain");
+    AG_REQUIRE(bs >= 0, AG_ERR_SHAPE, "negative batch");
+    for (int i = 0; i <= n_layers; ++i)
+        AG_REQUIRE(dims[i] > 0 && dims[i] < (1ll << 31), AG_ERR_SHAPE, "bad layer width");
+    if (bs == 0) return AG_OK;
+    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    dense_small::ChainLayer layers[dense_small::kMaxChain];
+    bool fused = n_layers <= dense_small::kMaxChain;
+    if (fused) {
+        for (int i = 0; i < n_layers; ++i) {
+            AG_REQUIRE(weights[i] != nullptr, AG_ERR_INVALID, "null weight pointer");
+            layers[i] = {weights[i], biases ? biases[i] : nullptr, (int)dims[i], (int)dims[i + 1],
+                         relu[i]};
+        }
+        fused = dense_small::chain_eligible(bs, n_layers, layers);
+    }
+    if (fused) {
+        if (dtype == AG_F32)
+            return dense_small::chain_forward<float>(dev, (const float *)x, (int)bs, n_layers,
+                                                     layers, (float *)y);
+        return dense_small::chain_forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, (int)bs,
+                                                         n_layers, layers, (__nv_bfloat16 *)y);
+    }
+    // Shapes the fused kernel does not take: layer by layer through the workspace.
+    int64_t widest = 0;
+    for (int i = 1; i < n_layers; ++i) widest = dims[i] > widest ? dims[i] : widest;
+    void *tmp = nullptr;
+    const size_t plane = (size_t)bs * (size_t)widest * dtype_size(dtype);
+    if (n_layers > 1) AG_TRY(workspace(dev, 2 * plane + (64u << 20), &tmp));
+    // keep clear of the split-k scratch at the start of the workspace
+    char *ping = (char *)tmp + (64u << 20), *pong = ping + plane;
+    const void *in = x;
+    for (int i = 0; i < n_layers; ++i) {
+        void *out = (i + 1 == n_layers) ? y : (void *)((i & 1) ? pong : ping);
+        AG_TRY(ag_dense_forward(dev, dtype, in, bs, dims[i], weights[i], dims[i + 1],
+                                biases ? biases[i] : nullptr, relu[i], out));
+        in = out;
+    }
+    return AG_OK;
+}
+
 extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t n,
                        float alpha, const void *a, int64_t off_a, int64_t rsa, int64_t csa,
                        const void *b, int64_t off_b, int64_t rsb, int64_t csb, float beta,

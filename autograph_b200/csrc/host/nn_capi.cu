@@ -25,11 +25,23 @@ struct CapturedPass {
     int seen = 0;                 // calls before a graph exists
 };
 
+// A pass captured for one particular pair of pinned host buffers: the first kernel
+// reads the images straight from host memory (the transfer overlaps its arithmetic
+// instead of preceding it), so the pointers are part of the graph.
+struct ZeroCopyPass {
+    const void *x = nullptr;
+    void *out = nullptr;
+    CapturedPass pass;
+    uint64_t last_use = 0;
+};
+
 struct GraphEntry {
     int64_t bs = 0, c = 0, h = 0, w = 0;
     Tensor x_stage;               // the graphs' input
     size_t out_bytes = 0;
     CapturedPass from_device, from_host;
+    std::vector<ZeroCopyPass> zero_copy;  // host callers that reuse a few pinned buffers
+    int zero_copy_misses = 0;
     uint64_t last_use = 0;
 };
 
@@ -40,6 +52,7 @@ struct ag_model {
     std::vector<GraphEntry> graphs;
     uint64_t tick = 0;
     bool graphs_enabled = true;
+    bool zero_copy_enabled = true;
     std::vector<std::unique_ptr<Layer>> layers;
     std::vector<Parameter *> params;
     std::vector<int64_t> offsets;  // element offset of each parameter in the buckets
@@ -51,6 +64,8 @@ struct ag_model {
     ag_model(ag_device *d, ag_dtype t) : dev(d), dtype(t), pool(d) {
         const char *e = getenv("AG_GRAPH");
         graphs_enabled = !(e && e[0] == '0');
+        const char *z = getenv("AG_ZERO_COPY");
+        zero_copy_enabled = !(z && z[0] == '0');
     }
     void drop(CapturedPass &p) {
         if (p.exec) cudaGraphExecDestroy(p.exec);
@@ -59,11 +74,14 @@ struct ag_model {
         p.graph = nullptr;
         pool.unpark(p.parked);
     }
+    void drop(GraphEntry &g) {
+        drop(g.from_device);
+        drop(g.from_host);
+        for (auto &z : g.zero_copy) drop(z.pass);
+        g.zero_copy.clear();
+    }
     ~ag_model() {
-        for (auto &g : graphs) {
-            drop(g.from_device);
-            drop(g.from_host);
-        }
+        for (auto &g : graphs) drop(g);
     }
 };
 
@@ -187,6 +205,37 @@ Variable forward_chain(ag_model *m, Variable v) {
                 continue;
             }
         } else if (auto *dense = dynamic_cast<Dense *>(l)) {
+            // A run of Dense (+ Relu) layers goes to one fused call.
+            if (!dense->records_gradient(v) && v.value.ndim() == 2 && v.value.is_standard_layout()) {
+                std::vector<Dense *> run;
+                std::vector<int32_t> relus;
+                size_t j = i;
+                while (j < n && run.size() < 4) {
+                    auto *d = dynamic_cast<Dense *>(m->layers[j].get());
+                    if (!d || d->weight.node || (d->has_bias && d->bias.node)) break;
+                    if (!run.empty() && d->weight.value.dim(0) != run.back()->weight.value.dim(1)) break;
+                    const bool r = j + 1 < n && dynamic_cast<Relu *>(m->layers[j + 1].get());
+                    run.push_back(d);
+                    relus.push_back(r ? 1 : 0);
+                    j += r ? 2 : 1;
+                }
+                if (run.size() >= 2 && v.value.dim(1) == run[0]->weight.value.dim(0)) {
+                    std::vector<int64_t> dims = {v.value.dim(1)};
+                    std::vector<const void *> ws, bs;
+                    for (Dense *d : run) {
+                        dims.push_back(d->weight.value.dim(1));
+                        ws.push_back(d->weight.value.data());
+                        bs.push_back(d->has_bias ? d->bias.value.data() : nullptr);
+                    }
+                    Tensor y = Tensor::uninit(m->pool, {v.value.dim(0), dims.back()}, v.value.dtype());
+                    check(ag_dense_chain_forward(m->dev, v.value.dtype(), v.value.data(),
+                                                 v.value.dim(0), (int32_t)run.size(), dims.data(),
+                                                 ws.data(), bs.data(), relus.data(), y.data()));
+                    v = Variable{y, nullptr};
+                    i = j - 1;
+                    continue;
+                }
+            }
             if (!dense->records_gradient(v) && relu1) {
                 v = dense->forward_fused(m->pool, v, true);
                 i += 1;
@@ -207,8 +256,7 @@ GraphEntry *find_graph(ag_model *m, int64_t bs, int64_t c, int64_t h, int64_t w)
         size_t victim = 0;
         for (size_t i = 1; i < m->graphs.size(); ++i)
             if (m->graphs[i].last_use < m->graphs[victim].last_use) victim = i;
-        m->drop(m->graphs[victim].from_device);
-        m->drop(m->graphs[victim].from_host);
+        m->drop(m->graphs[victim]);
         m->graphs.erase(m->graphs.begin() + victim);
     }
     m->graphs.emplace_back();
@@ -218,13 +266,91 @@ GraphEntry *find_graph(ag_model *m, int64_t bs, int64_t c, int64_t h, int64_t w)
     return &g;
 }
 
-bool is_pinned_host(const void *p) {
+// Device-visible address of pinned host memory, or null when `p` is not pinned.
+void *pinned_device_pointer(const void *p) {
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
         cudaGetLastError();
-        return false;
+        return nullptr;
     }
-    return attr.type == cudaMemoryTypeHost;
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
+bool is_pinned_host(const void *p) { return pinned_device_pointer(p) != nullptr; }
+
+constexpr size_t kMaxZeroCopy = 8;
+constexpr int kZeroCopyMissLimit = 64;
+
+// Host path for callers that cycle through a few pinned buffers: one graph per
+// (input, output) pair whose first kernel reads the host images directly.
+// Returns false when the caller should use the copying path instead.
+bool run_zero_copy(ag_model *m, GraphEntry *g, const void *x, void *out) {
+    if (g->zero_copy_misses > kZeroCopyMissLimit) return false;  // too many distinct buffers
+    void *x_dev = pinned_device_pointer(x);
+    if (!x_dev || !is_pinned_host(out)) return false;
+    cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
+    ZeroCopyPass *z = nullptr;
+    for (auto &e : g->zero_copy)
+        if (e.x == x && e.out == out) z = &e;
+    if (!z) {
+        ++g->zero_copy_misses;
+        if (g->zero_copy.size() >= kMaxZeroCopy) {
+            size_t victim = 0;
+            for (size_t i = 1; i < g->zero_copy.size(); ++i)
+                if (g->zero_copy[i].last_use < g->zero_copy[victim].last_use) victim = i;
+            m->drop(g->zero_copy[victim].pass);
+            g->zero_copy.erase(g->zero_copy.begin() + victim);
+        }
+        g->zero_copy.emplace_back();
+        z = &g->zero_copy.back();
+        z->x = x;
+        z->out = out;
+    }
+    z->last_use = ++m->tick;
+    CapturedPass &cp = z->pass;
+    auto cuda_ok = [](cudaError_t e, const char *what) {
+        if (e != cudaSuccess)
+            throw Error(AG_ERR_CUDA, std::string(what) + " failed: " + cudaGetErrorString(e));
+    };
+    if (cp.exec) {
+        cuda_ok(cudaGraphLaunch(cp.exec, stream), "cudaGraphLaunch");
+        ::ag::count_launches(cp.kernels);
+        return true;
+    }
+    auto pass = [&]() {
+        Tensor xt = Tensor::external(m->dev, x_dev, {g->bs, g->c, g->h, g->w}, m->dtype);
+        Variable y = forward_chain(m, Variable{xt, nullptr});
+        cuda_ok(cudaMemcpyAsync(out, y.value.data(), y.value.nbytes(), cudaMemcpyDeviceToHost,
+                                stream), "output copy");
+    };
+    if (++cp.seen < 2) {
+        pass();
+        return true;
+    }
+    m->pool.set_hold(&cp.parked);
+    const uint64_t launches_before = ::ag::launch_count();
+    bool ok = cudaStreamBeginCapture(stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+    if (ok) {
+        try {
+            pass();
+        } catch (...) {
+            ok = false;
+        }
+        ok = (cudaStreamEndCapture(stream, &cp.graph) == cudaSuccess) && ok && cp.graph != nullptr;
+    }
+    m->pool.set_hold(nullptr);
+    cp.kernels = ::ag::launch_count() - launches_before;
+    if (ok) ok = cudaGraphInstantiate(&cp.exec, cp.graph, 0) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        m->drop(cp);
+        g->zero_copy_misses = kZeroCopyMissLimit + 1;  // stop trying for this shape
+        pass();
+        return true;
+    }
+    cuda_ok(cudaGraphLaunch(cp.exec, stream), "cudaGraphLaunch");
+    ::ag::count_launches(cp.kernels);
+    return true;
 }
 
 // One inference pass x -> out.  `host` selects host pointers (x and out in host
@@ -232,6 +358,9 @@ bool is_pinned_host(const void *p) {
 // a shape runs eagerly; the second captures the pass; later calls replay it.
 void run_inference(ag_model *m, GraphEntry *g, bool host, const void *x, void *out) {
     g->last_use = ++m->tick;
+    if (host && m->graphs_enabled && m->zero_copy_enabled && g->bs > 0 &&
+        run_zero_copy(m, g, x, out))
+        return;
     cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
     CapturedPass &cp = host ? g->from_host : g->from_device;
     const cudaMemcpyKind kin = host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;

@@ -144,6 +144,18 @@ AG_API int ag_dense_forward(ag_device *dev, ag_dtype dtype, const void *x, int64
                             int64_t inputs, const void *w, int64_t outputs, const void *bias,
                             int fuse_relu, void *y);
 
+/* A chain of Dense layers, each optionally followed by Relu, in one call:
+ * y = L_n(..relu?(L_1(x))), L_i(v) = v . w_i (+ bias_i); ≙ the run of Dense::forward /
+ * Relu::forward pairs at the end of a model's derived Forward (layer.rs:1134-1143,
+ * 1254-1267; autograph_backend.rs:129-146).  dims has n_layers + 1 entries (input width,
+ * then every output width); weights[i] is [dims[i], dims[i+1]] row-major; biases may be
+ * NULL or hold NULL entries.  Small chains run as one kernel that keeps the
+ * activations in shared memory; results equal the separate calls bit for bit. */
+AG_API int ag_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                  int32_t n_layers, const int64_t *dims,
+                                  const void *const *weights, const void *const *biases,
+                                  const int32_t *relu, void *y);
+
 /* ------------------------------------------------------------ convolution */
 
 /* y = conv2(x, w) (+ bias) (then relu when fuse_relu != 0), NCHW.

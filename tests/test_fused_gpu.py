@@ -75,6 +75,28 @@ def test_dense_forward_equals_separate_calls(dev, dtype, shape):
     assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(1000, [256, 128, 84, 10]), (37, [256, 128, 84, 10]),
+                                  (5, [7, 3, 9]), (256, [25088, 512, 10]), (9000, [64, 32, 16])])
+def test_dense_chain_equals_separate_calls(dev, dtype, case):
+    bs, widths = case
+    rng = np.random.default_rng(51 + bs)
+    x = _prep(rng.standard_normal((bs, widths[0])), dtype)
+    ws, bs_, relus = [], [], []
+    for i in range(len(widths) - 1):
+        a = np.sqrt(2.0 / widths[i])
+        ws.append(dev.tensor(_prep(rng.uniform(-a, a, (widths[i], widths[i + 1])), dtype), dtype))
+        last = i == len(widths) - 2
+        bs_.append(dev.tensor(_prep(rng.uniform(-a, a, widths[i + 1]), dtype), dtype) if last else None)
+        relus.append(not last)
+    xd = dev.tensor(x, dtype)
+    fused = dev.dense_chain_forward(xd, ws, bs_, relus)
+    h = xd
+    for w, b, r in zip(ws, bs_, relus):
+        h = dev.dense_forward(h, w, bias=b, relu=r)
+    assert torch.equal(fused, h)
+
+
 def test_fused_errors(dev):
     import autograph_b200 as ag
     x = dev.empty((2, 1, 6, 6), torch.float32)
