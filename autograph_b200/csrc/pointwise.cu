@@ -192,6 +192,49 @@ __global__ void max_pool2_backward_kernel(T *__restrict__ dx, const T *__restric
     }
 }
 
+// 2x2 window, stride 2, width a multiple of the vector length, 16-byte aligned rows:
+// each thread owns V/2 adjacent windows, reads and rewrites two 16-byte row segments.
+template <class T>
+__global__ void max_pool2_backward_2x2_kernel(T *__restrict__ dx, const T *__restrict__ dy,
+                                              int64_t planes, int ih, int iw, int oh, int ow) {
+    constexpr int V = Vec16<T>::N;
+    const int vec_per_row = iw / V;
+    const int64_t total = planes * oh * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int vx = (int)(i % vec_per_row);
+        int64_t t = i / vec_per_row;
+        int hid = (int)(t % oh);
+        int64_t plane = t / oh;
+        T *r0 = dx + (plane * ih + 2 * (int64_t)hid) * iw + vx * V;
+        const T *g = dy + (plane * oh + hid) * (int64_t)ow + vx * (V / 2);
+        Vec16<T> a, b, oa, ob;
+        a.raw = *reinterpret_cast<const uint4 *>(r0);
+        b.raw = *reinterpret_cast<const uint4 *>(r0 + iw);
+        oa.raw = make_uint4(0, 0, 0, 0);
+        ob.raw = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < V / 2; ++j) {
+            // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
+            float m = a.get(2 * j);
+            int am = 0;
+            float v = a.get(2 * j + 1);
+            if (v > m) { m = v; am = 1; }
+            v = b.get(2 * j);
+            if (v > m) { m = v; am = 2; }
+            v = b.get(2 * j + 1);
+            if (v > m) { m = v; am = 3; }
+            const float gv = __fadd_rn(0.f, to_f32(g[j]));
+            oa.set(2 * j, am == 0 ? gv : 0.f);
+            oa.set(2 * j + 1, am == 1 ? gv : 0.f);
+            ob.set(2 * j, am == 2 ? gv : 0.f);
+            ob.set(2 * j + 1, am == 3 ? gv : 0.f);
+        }
+        *reinterpret_cast<uint4 *>(r0) = oa.raw;
+        *reinterpret_cast<uint4 *>(r0 + iw) = ob.raw;
+    }
+}
+
 // ---- bias ---------------------------------------------------------------------
 template <class T>
 __global__ void bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias, int64_t total,
@@ -203,17 +246,45 @@ __global__ void bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias, i
     }
 }
 
-// One CTA per channel; fixed-shape tree reduction (deterministic).
+// Bias gradient y[c] = beta*y[c] + sum over (r, i) of x[r, c, i], in two passes with a
+// fixed summation order (deterministic):
+//   pass 1  partial[chunk][c] over a chunk of rows, reading x coalesced
+//   pass 2  y[c] = beta*y[c] + sum over chunks
+// inner == 1 (Dense): threads walk the columns.  inner > 1 (Conv2, NCHW): threads walk
+// the contiguous inner positions of one channel.
 template <class T>
-__global__ void bias_grad_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t rows,
-                                 int64_t cols, int64_t inner, float beta) {
+__global__ void bias_grad_cols_kernel(const T *__restrict__ x, float *__restrict__ partial,
+                                      int64_t rows, int64_t cols, int64_t rows_per_chunk) {
+    __shared__ float part[8][33];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;  // 32 columns x 8 row lanes
+    const int64_t c = (int64_t)blockIdx.x * 32 + cx;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
+    const int64_t r1 = min(rows, r0 + rows_per_chunk);
+    float s = 0.f;
+    if (c < cols)
+        for (int64_t r = r0 + ry; r < r1; r += 8) s += to_f32(x[r * cols + c]);
+    part[ry][cx] = s;
+    __syncthreads();
+    if (ry == 0 && c < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += part[k][cx];
+        partial[(int64_t)blockIdx.y * cols + c] = t;
+    }
+}
+
+template <class T>
+__global__ void bias_grad_inner_kernel(const T *__restrict__ x, float *__restrict__ partial,
+                                       int64_t rows, int64_t cols, int64_t inner,
+                                       int64_t rows_per_chunk) {
     __shared__ float part[256];
     const int64_t c = blockIdx.x;
-    const int64_t count = rows * inner;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
+    const int64_t r1 = min(rows, r0 + rows_per_chunk);
     float s = 0.f;
-    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
-        int64_t r = i / inner, in = i - r * inner;
-        s += to_f32(x[(r * cols + c) * inner + in]);
+    for (int64_t r = r0; r < r1; ++r) {
+        const T *seg = x + (r * cols + c) * inner;
+        for (int64_t i = threadIdx.x; i < inner; i += blockDim.x) s += to_f32(seg[i]);
     }
     part[threadIdx.x] = s;
     __syncthreads();
@@ -221,11 +292,46 @@ __global__ void bias_grad_kernel(const T *__restrict__ x, T *__restrict__ y, int
         if ((int)threadIdx.x < off) part[threadIdx.x] += part[threadIdx.x + off];
         __syncthreads();
     }
-    if (threadIdx.x == 0) {
-        float v = part[0];
-        if (beta != 0.f) v = __fadd_rn(v, __fmul_rn(beta, to_f32(y[c])));
-        y[c] = from_f32<T>(v);
-    }
+    if (threadIdx.x == 0) partial[(int64_t)blockIdx.y * cols + c] = part[0];
+}
+
+template <class T>
+__global__ void bias_grad_final_kernel(const float *__restrict__ partial, T *__restrict__ y,
+                                       int64_t cols, int chunks, float beta) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float v = 0.f;
+    for (int k = 0; k < chunks; ++k) v += partial[(int64_t)k * cols + c];
+    if (beta != 0.f) v = __fadd_rn(v, __fmul_rn(beta, to_f32(y[c])));
+    y[c] = from_f32<T>(v);
+}
+
+template <class T>
+static int bias_grad_run(ag_device *dev, const T *x, int64_t rows, int64_t cols, int64_t inner,
+                         float beta, T *y) {
+    // Enough row chunks to fill the GPU, at most 1024.
+    int64_t col_blocks = inner == 1 ? ceil_div(cols, 32) : cols;
+    int64_t chunks = ceil_div((int64_t)dev->sm_count * 4, col_blocks);
+    if (chunks > rows) chunks = rows;
+    if (chunks > 1024) chunks = 1024;
+    if (chunks < 1) chunks = 1;
+    const int64_t rows_per_chunk = ceil_div(rows > 0 ? rows : 1, chunks);
+    chunks = rows > 0 ? ceil_div(rows, rows_per_chunk) : 1;
+    void *ws = nullptr;
+    AG_TRY(workspace(dev, sizeof(float) * (size_t)chunks * (size_t)cols, &ws));
+    dim3 grid((unsigned)col_blocks, (unsigned)chunks);
+    AG_REQUIRE(col_blocks < (1ll << 31), AG_ERR_LIMIT, "too many columns");
+    if (inner == 1)
+        bias_grad_cols_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols,
+                                                                rows_per_chunk);
+    else
+        bias_grad_inner_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols, inner,
+                                                                 rows_per_chunk);
+    AG_CHECK_LAUNCH();
+    bias_grad_final_kernel<T><<<(unsigned)ceil_div(cols, 256), 256, 0, dev->stream>>>(
+        (const float *)ws, y, cols, (int)chunks, beta);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
 }
 
 // ---- SGD ------------------------------------------------------------------------
@@ -342,6 +448,16 @@ int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, 
     if (planes == 0) return AG_OK;
     AG_REQUIRE(dx && dy, AG_ERR_INVALID, "null tensor pointer");
     const int threads = 256;
+    const int vlen = dtype == AG_F32 ? 4 : 8;
+    if (h == 2 && w == 2 && sh == 2 && sw == 2 && iw % vlen == 0 &&
+        (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {
+        const unsigned grid2 = grid_for(planes * oh * (iw / vlen), threads, dev->sm_count);
+        AG_DISPATCH_FLOAT(dtype, T,
+            max_pool2_backward_2x2_kernel<T><<<grid2, threads, 0, dev->stream>>>(
+                (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow););
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
     const unsigned grid = grid_for(planes * oh * ow, threads, dev->sm_count);
     AG_DISPATCH_FLOAT(dtype, T,
         max_pool2_backward_kernel<T><<<grid, threads, 0, dev->stream>>>(
@@ -374,10 +490,7 @@ int ag_bias_grad(ag_device *dev, ag_dtype dtype, const void *x, int64_t rows, in
     if (cols == 0) return AG_OK;
     AG_REQUIRE(y && (rows * inner == 0 || x), AG_ERR_INVALID, "null tensor pointer");
     AG_REQUIRE(cols < (1ll << 31), AG_ERR_LIMIT, "too many columns");
-    AG_DISPATCH_FLOAT(dtype, T,
-        bias_grad_kernel<T><<<(unsigned)cols, 256, 0, dev->stream>>>((const T *)x, (T *)y, rows, cols, inner, beta););
-    AG_CHECK_LAUNCH();
-    return AG_OK;
+    AG_DISPATCH_FLOAT(dtype, T, return bias_grad_run<T>(dev, (const T *)x, rows, cols, inner, beta, (T *)y););
 }
 
 int ag_sgd_update(ag_device *dev, ag_dtype dtype, void *w, const void *g, int64_t n, float lr) {

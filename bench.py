@@ -328,57 +328,63 @@ def train_data_parallel(torch, ag, dp, dev, rank, world, barrier, max_over_ranks
     return out
 
 
+def graph_time_us(torch, dev, fns, reps=10):
+    """Device time per call of the launches in `fns`, measured by replaying a CUDA graph of
+    them (no host launch gaps between the kernels), CUDA events on the launching stream."""
+    for fn in fns[:3]:
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=dev.stream):
+        for fn in fns:
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    ms = event_time_ms(torch, lambda i: g.replay(), reps, dev.stream)
+    return ms / (reps * len(fns)) * 1e3
+
+
 def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):
-    """Times each stage of the f32 forward alone (CUDA events, rotating inputs) and reports
-    the dominant kernel against the measured HBM peak; the FP32-pipe view is added because
-    the convolution kernels are FFMA-bound, which the hbm / tensor choice cannot express."""
+    """Times the three kernels of the f32 inference step alone (graph replay, inputs rotating
+    through HBM) and reports the dominant one against the measured HBM peak; the FP32-pipe
+    view is added because these kernels are FFMA / latency bound, which the hbm / tensor
+    choice cannot express."""
     shapes = [(6, 1, 5, 5), (16, 6, 5, 5), (256, 128), (128, 84), (84, 10), (10,)]
     P = [dev.tensor(model.get_parameter(i).reshape(shp)) for i, shp in enumerate(shapes)]
     B = BATCH
-    x0 = xs[:, :, :, :, :]
-    c1 = dev.conv2_forward(xs[0], P[0], relu=True)
-    p1 = dev.max_pool2(c1)
-    p1s = torch.stack([p1 + 0.001 * i for i in range(16)])           # 16 * 3.5 MB
-    c2 = dev.conv2_forward(p1, P[1], relu=True)
-    p2 = dev.max_pool2(c2)
-    f = p2.reshape(B, 256)
-    d1 = dev.dot(f, P[2])
-    iters = max(min(K, 500), 20)
+    s = 4
+    p1 = dev.conv2_relu_max_pool2(xs[0], P[0])
+    p1s = [p1 + 0.001 * i for i in range(16)]
+    p2 = dev.conv2_relu_max_pool2(p1, P[1])
+    fs = [(p2 + 0.001 * i).reshape(B, 256) for i in range(16)]
     stages = {}
 
-    def timeit(name, fn, flops, bytes_):
-        for i in range(3):
-            fn(i)
-        ms = event_time_ms(torch, fn, iters, dev.stream) / iters
-        stages[name] = {"us": ms * 1e3, "gflops": flops / ms * 1e-6, "gbs": bytes_ / ms * 1e-6,
+    def add(name, fns, flops, bytes_):
+        us = graph_time_us(torch, dev, fns)
+        stages[name] = {"us": us, "gflops": flops / us * 1e-3, "gbs": bytes_ / us * 1e-3,
                         "alg_bytes": bytes_, "alg_flops": flops}
 
-    s = 4
-    timeit("conv1+relu (gemm_simt_kernel, implicit GEMM 576000x25x6)",
-           lambda i: dev.conv2_forward(x0[i % ROTATE], P[0], relu=True),
-           2 * B * 576 * 25 * 6, (B * 784 + 150 + B * 6 * 576) * s)
-    timeit("pool1 (max_pool2_2x2_kernel)", lambda i: dev.max_pool2(c1),
-           0, (B * 6 * 576 + B * 6 * 144) * s)
-    timeit("conv2+relu (gemm_simt_kernel, implicit GEMM 64000x150x16)",
-           lambda i: dev.conv2_forward(p1s[i % 16], P[1], relu=True),
-           2 * B * 64 * 150 * 16, (B * 6 * 144 + 2400 + B * 16 * 64) * s)
-    timeit("pool2 (max_pool2_2x2_kernel)", lambda i: dev.max_pool2(c2), 0,
-           (B * 16 * 64 + B * 256) * s)
-    timeit("dense1 (gemm_simt_kernel 1000x256x128)", lambda i: dev.dot(f, P[2]),
-           2 * B * 256 * 128, (B * 256 + 256 * 128 + B * 128) * s)
-    timeit("dense2 (gemm_simt_kernel 1000x128x84)", lambda i: dev.dot(d1, P[3]),
-           2 * B * 128 * 84, (B * 128 + 128 * 84 + B * 84) * s)
+    add("conv1+relu+pool (conv2_direct_kernel<5,5>, 1->6 ch, 28x28)",
+        [lambda i=i: dev.conv2_relu_max_pool2(xs[i], P[0]) for i in range(32)],
+        2 * B * 576 * 25 * 6, (B * 784 + 150 + B * 6 * 144) * s)
+    add("conv2+relu+pool (conv2_direct_kernel<5,5>, 6->16 ch, 12x12)",
+        [lambda i=i: dev.conv2_relu_max_pool2(p1s[i % 16], P[1]) for i in range(32)],
+        2 * B * 64 * 150 * 16, (B * 6 * 144 + 2400 + B * 256) * s)
+    add("dense chain 256-128-84-10 (dense_chain_kernel)",
+        [lambda i=i: dev.dense_chain_forward(fs[i % 16], [P[2], P[3], P[4]], [None, None, P[5]],
+                                             [True, True, False]) for i in range(32)],
+        2 * B * (256 * 128 + 128 * 84 + 84 * 10), (B * 256 + 46920 - 2550 + B * 10) * s)
     name = max(stages, key=lambda k: stages[k]["us"])
     st = stages[name]
-    clock_ghz = 1.965
-    fp32_peak = 148 * 128 * 2 * clock_ghz * 1e-3  # TFLOP/s at the maximum SM clock
+    fp32_peak = 148 * 128 * 2 * 1.965e-3  # TFLOP/s at the maximum SM clock
     roof = {"bound": "hbm", "kernel": name, "achieved": st["gbs"], "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": st["gbs"] / peaks["hbm_gbs"], "traffic": None,
             "peak_source": peaks["source"], "us_per_launch": st["us"],
             "algorithmic_bytes_per_launch": st["alg_bytes"],
             "fp32_pipe": {"achieved_tflops": st["gflops"] * 1e-3, "peak_tflops": fp32_peak,
                           "frac": st["gflops"] * 1e-3 / fp32_peak,
-                          "note": "148 SMs x 128 lanes x 2 x 1.965 GHz; this kernel is FFMA-bound"}}
+                          "note": "148 SMs x 128 lanes x 2 x 1.965 GHz; at batch 1000 this kernel "
+                                  "is FFMA-issue / latency bound, not HBM bound"}}
     return roof, stages
 
 
@@ -460,14 +466,50 @@ def extras(torch, ag, dev, peaks, world):
 
 def run_probe(args):
     """Runs one kernel family alone, for profiler captures:
-    gemm:<f32|bf16>:<n>:<nn|tn|nt|tt>, infer:<f32|bf16>:<batch>, train:<f32|bf16>:<batch>."""
+    gemm:<f32|bf16>:<n>:<nn|tn|nt|tt>, infer:<f32|bf16>:<batch>, train:<f32|bf16>:<batch>,
+    op:<f32|bf16>:<relu|relu_backward|scaled_add|sgd_momentum|max_pool2|max_pool2_backward|
+    bias_grad>:<elements>."""
     import torch
     import autograph_b200 as ag
     dev = ag.Device(0)
     parts = args.probe.split(":")
     dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[parts[1]]
     K, W = args.steps, args.warmup
-    if parts[0] == "gemm":
+    if parts[0] == "op":
+        # op:<dtype>:<name>:<elements>  memory-bound kernels on a large array
+        name, n = parts[2], int(parts[3])
+        es = 4 if dtype == torch.float32 else 2
+        a = (torch.rand((n,), device=dev.torch_device) - 0.5).to(dtype)
+        b = (torch.rand((n,), device=dev.torch_device) - 0.5).to(dtype)
+        c = torch.zeros((n,), device=dev.torch_device, dtype=dtype)
+        if name == "relu":
+            fn, nbytes = (lambda i: dev.relu(a, inplace=False)), 2 * n * es
+        elif name == "relu_backward":
+            fn, nbytes = (lambda i: dev.relu_backward(a, b)), 3 * n * es
+        elif name == "scaled_add":
+            fn, nbytes = (lambda i: dev.scaled_add(c, 0.5, a)), 3 * n * es
+        elif name == "sgd_momentum":
+            fn, nbytes = (lambda i: dev.sgd_update_momentum(c, a, b, 0.01, 0.01)), 5 * n * es
+        elif name == "max_pool2":
+            x4 = a[: (n // 4096) * 4096].reshape(-1, 16, 16, 16)
+            fn, nbytes = (lambda i: dev.max_pool2(x4)), x4.numel() * es * 5 // 4
+        elif name == "max_pool2_backward":
+            x4 = a[: (n // 4096) * 4096].reshape(-1, 16, 16, 16)
+            dy = b[: x4.numel() // 4].reshape(-1, 16, 8, 8)
+            dx = x4.clone()
+            h = dev._h
+            def fn(i):
+                ag._capi.check(ag.lib().ag_max_pool2_backward(
+                    h, 0 if dtype == torch.float32 else 1, dx.data_ptr(), x4.shape[0], 16, 16, 16,
+                    2, 2, 2, 2, dy.data_ptr()))
+            nbytes = x4.numel() * es * 9 // 4
+        elif name == "bias_grad":
+            x2 = a[: (n // 512) * 512].reshape(-1, 512)
+            fn, nbytes = (lambda i: dev.bias_grad(x2)), x2.numel() * es
+        else:
+            raise SystemExit(f"unknown op {name}")
+        work, unit = nbytes * 1e-9, "GB/s"
+    elif parts[0] == "gemm":
         n, layout = int(parts[2]), parts[3]
         a = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
         b = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
