@@ -96,6 +96,7 @@ _SIGNATURES = {
     "ag_bias_grad": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_float, _P]),
     "ag_cross_entropy_loss": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64,
                                       POINTER(c_float)]),
+    "ag_cross_entropy_loss_device": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, _P]),
     "ag_cross_entropy_loss_backward": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, c_float,
                                                _P]),
     "ag_accuracy": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, POINTER(c_uint64)]),

@@ -105,17 +105,25 @@ static unsigned warp_grid(int64_t rows, int threads, int sms) {
     return (unsigned)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
 }
 
+// Sum of the row losses into *loss_dev (device memory); no synchronisation.
 template <class T, class L>
-static int ce_loss(ag_device *dev, const T *x, const L *t, int64_t bs, int classes,
-                   float *loss_host) {
+static int ce_loss_device(ag_device *dev, const T *x, const L *t, int64_t bs, int classes,
+                          float *loss_dev) {
     void *ws;
     AG_TRY(workspace(dev, sizeof(float) * (size_t)bs, &ws));
     const int threads = 256;
     ce_loss_rows_kernel<T, L><<<warp_grid(bs, threads, dev->sm_count), threads, 0, dev->stream>>>(
         x, t, bs, classes, (float *)ws);
     AG_CHECK_LAUNCH();
-    sum_rows_kernel<<<1, 1024, 0, dev->stream>>>((const float *)ws, bs, dev->scalar_dev);
+    sum_rows_kernel<<<1, 1024, 0, dev->stream>>>((const float *)ws, bs, loss_dev);
     AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+template <class T, class L>
+static int ce_loss(ag_device *dev, const T *x, const L *t, int64_t bs, int classes,
+                   float *loss_host) {
+    AG_TRY((ce_loss_device<T, L>(dev, x, t, bs, classes, dev->scalar_dev)));
     AG_CUDA_TRY(cudaMemcpyAsync(dev->scalar_host, dev->scalar_dev, sizeof(float),
                                 cudaMemcpyDeviceToHost, dev->stream));
     AG_CUDA_TRY(cudaStreamSynchronize(dev->stream));
@@ -162,6 +170,18 @@ int ag_cross_entropy_loss(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype, 
     AG_REQUIRE(x && t, AG_ERR_INVALID, "null tensor pointer");
     AG_DISPATCH_XT(dtype, label_dtype, T, L,
                    return ce_loss<T, L>(dev, (const T *)x, (const L *)t, bs, (int)classes, loss_host););
+}
+
+int ag_cross_entropy_loss_device(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
+                                 const void *x, const void *t, int64_t bs, int64_t classes,
+                                 float *loss_dev) {
+    AG_ENTER(dev);
+    AG_TRY(check_ce_args(dtype, label_dtype, bs, classes));
+    AG_REQUIRE(loss_dev != nullptr, AG_ERR_INVALID, "loss_dev is null");
+    if (bs == 0) return ag_fill_zero(dev, loss_dev, sizeof(float));
+    AG_REQUIRE(x && t, AG_ERR_INVALID, "null tensor pointer");
+    AG_DISPATCH_XT(dtype, label_dtype, T, L,
+                   return ce_loss_device<T, L>(dev, (const T *)x, (const L *)t, bs, (int)classes, loss_dev););
 }
 
 int ag_cross_entropy_loss_backward(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,

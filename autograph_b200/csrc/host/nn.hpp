@@ -395,13 +395,21 @@ struct Loss {
     }
 };
 
-inline Loss cross_entropy_loss(Pool &pool, const Variable &input, const Tensor &target) {
+// loss_dev == null: the value is read back (synchronises), as the reference does.
+// loss_dev != null: the value is left in device memory and loss.value stays 0, so that
+// the whole step can be enqueued without a host round trip.
+inline Loss cross_entropy_loss(Pool &pool, const Variable &input, const Tensor &target,
+                               float *loss_dev = nullptr) {
     const Tensor &x = input.value;
     if (x.ndim() != 2 || target.ndim() != 1 || target.dim(0) != x.dim(0))
         throw Error(AG_ERR_SHAPE, "Expected target with shape [" + std::to_string(x.dim(0)) + "]");
     Loss loss;
-    check(ag_cross_entropy_loss(x.device(), x.dtype(), target.dtype(), x.data(), target.data(),
-                                x.dim(0), x.dim(1), &loss.value));
+    if (loss_dev)
+        check(ag_cross_entropy_loss_device(x.device(), x.dtype(), target.dtype(), x.data(),
+                                           target.data(), x.dim(0), x.dim(1), loss_dev));
+    else
+        check(ag_cross_entropy_loss(x.device(), x.dtype(), target.dtype(), x.data(), target.data(),
+                                    x.dim(0), x.dim(1), &loss.value));
     if (input.node) {
         Pool *pp = &pool;
         Tensor xv = x, tv = target;

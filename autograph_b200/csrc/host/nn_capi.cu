@@ -45,10 +45,28 @@ struct GraphEntry {
     uint64_t last_use = 0;
 };
 
+// A captured training step (host images and labels -> loss, gradients, update) for one
+// input shape and one set of optimizer scalars.
+struct TrainEntry {
+    int64_t bs = 0, c = 0, h = 0, w = 0;
+    float lr = 0.f, momentum = 0.f, grad_scale = 1.f;
+    bool use_momentum = false;
+    Tensor x_stage, t_stage;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    cudaGraphNode_t x_node = nullptr, t_node = nullptr;
+    Pool::Parked parked;
+    uint64_t kernels = 0;
+    int seen = 0;
+};
+
 struct ag_model {
     ag_device *dev;
     ag_dtype dtype;
     Pool pool;  // declared before every tensor so that it is destroyed last
+    std::vector<TrainEntry> train_graphs;
+    Tensor loss_dev;             // one f32: the loss of the step in flight
+    float *loss_pinned = nullptr;
     std::vector<GraphEntry> graphs;
     uint64_t tick = 0;
     bool graphs_enabled = true;
@@ -80,8 +98,17 @@ struct ag_model {
         for (auto &z : g.zero_copy) drop(z.pass);
         g.zero_copy.clear();
     }
+    void drop(TrainEntry &t) {
+        if (t.exec) cudaGraphExecDestroy(t.exec);
+        if (t.graph) cudaGraphDestroy(t.graph);
+        t.exec = nullptr;
+        t.graph = nullptr;
+        pool.unpark(t.parked);
+    }
     ~ag_model() {
         for (auto &g : graphs) drop(g);
+        for (auto &t : train_graphs) drop(t);
+        if (loss_pinned) ag_host_free(loss_pinned);
     }
 };
 
@@ -445,10 +472,10 @@ Tensor input_tensor(ag_model *m, const void *x, bool on_host, int64_t bs, int64_
     return Tensor::external(m->dev, const_cast<void *>(x), shape, m->dtype);
 }
 
-float forward_backward(ag_model *m, const Tensor &x, const Tensor &t) {
+float forward_backward(ag_model *m, const Tensor &x, const Tensor &t, float *loss_dev = nullptr) {
     for (Parameter *p : m->params) p->init_grad();  // ≙ model.init_parameter_grads()
     Variable y = forward_chain(m, Variable{x, nullptr});
-    Loss loss = cross_entropy_loss(m->pool, y, t);
+    Loss loss = cross_entropy_loss(m->pool, y, t, loss_dev);
     loss.backward();
     for (Parameter *p : m->params) {
         if (!p->has_grad()) throw Error(AG_ERR_INVALID, "a parameter received no gradient");
@@ -468,6 +495,117 @@ void apply_update(ag_model *m, float lr) {
     else
         check(ag_sgd_update(m->dev, m->dtype, m->values.data(), m->grads.data(), m->bucket_len, lr));
     for (Parameter *p : m->params) p->node.reset();  // ≙ take_grad consumed the gradient
+}
+
+// One training step from pinned host buffers, replayed from a CUDA graph from the second
+// call with the same shape and optimizer scalars on.  Returns false when the step has to
+// run eagerly (pageable host memory, graphs disabled, capture failed).
+bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, int64_t bs, int64_t c,
+                      int64_t h, int64_t w, float lr, float *loss_host) {
+    if (!m->graphs_enabled || bs <= 0 || !is_pinned_host(x_host) || !is_pinned_host(t_host))
+        return false;
+    cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
+    TrainEntry *e = nullptr;
+    for (auto &t : m->train_graphs)
+        if (t.bs == bs && t.c == c && t.h == h && t.w == w && t.lr == lr &&
+            t.momentum == m->momentum && t.use_momentum == m->use_momentum &&
+            t.grad_scale == m->grad_scale)
+            e = &t;
+    if (!e) {
+        if (m->train_graphs.size() >= 8) {
+            m->drop(m->train_graphs.front());
+            m->train_graphs.erase(m->train_graphs.begin());
+        }
+        m->train_graphs.emplace_back();
+        e = &m->train_graphs.back();
+        e->bs = bs; e->c = c; e->h = h; e->w = w;
+        e->lr = lr; e->momentum = m->momentum; e->use_momentum = m->use_momentum;
+        e->grad_scale = m->grad_scale;
+        e->x_stage = Tensor::uninit(m->pool, {bs, c, h, w}, m->dtype);
+        e->t_stage = Tensor::uninit(m->pool, {bs}, AG_U8);
+    }
+    if (!m->loss_dev.defined()) {
+        m->loss_dev = Tensor::zeros(m->pool, {1}, AG_F32);
+        void *hp = nullptr;
+        check(ag_host_alloc(sizeof(float), &hp));
+        m->loss_pinned = (float *)hp;
+    }
+    auto cuda_ok = [](cudaError_t err, const char *what) {
+        if (err != cudaSuccess)
+            throw Error(AG_ERR_CUDA, std::string(what) + " failed: " + cudaGetErrorString(err));
+    };
+    auto finish = [&]() {
+        cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        *loss_host = *m->loss_pinned;
+    };
+    if (e->exec) {
+        cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->x_node, e->x_stage.data(), x_host,
+                                                    e->x_stage.nbytes(), cudaMemcpyHostToDevice),
+                "graph input update");
+        cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->t_node, e->t_stage.data(), t_host,
+                                                    e->t_stage.nbytes(), cudaMemcpyHostToDevice),
+                "graph label update");
+        cuda_ok(cudaGraphLaunch(e->exec, stream), "cudaGraphLaunch");
+        ::ag::count_launches(e->kernels);
+        finish();
+        return true;
+    }
+    auto pass = [&]() {
+        cuda_ok(cudaMemcpyAsync(e->x_stage.data(), x_host, e->x_stage.nbytes(),
+                                cudaMemcpyHostToDevice, stream), "input copy");
+        cuda_ok(cudaMemcpyAsync(e->t_stage.data(), t_host, e->t_stage.nbytes(),
+                                cudaMemcpyHostToDevice, stream), "label copy");
+        forward_backward(m, e->x_stage, e->t_stage, (float *)m->loss_dev.data());
+        apply_update(m, lr);
+        cuda_ok(cudaMemcpyAsync(m->loss_pinned, m->loss_dev.data(), sizeof(float),
+                                cudaMemcpyDeviceToHost, stream), "loss copy");
+    };
+    if (++e->seen < 2) {
+        pass();
+        finish();
+        return true;
+    }
+    m->pool.set_hold(&e->parked);
+    const uint64_t launches_before = ::ag::launch_count();
+    bool ok = cudaStreamBeginCapture(stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+    if (ok) {
+        try {
+            pass();
+        } catch (...) {
+            ok = false;
+        }
+        ok = (cudaStreamEndCapture(stream, &e->graph) == cudaSuccess) && ok && e->graph != nullptr;
+    }
+    m->pool.set_hold(nullptr);
+    e->kernels = ::ag::launch_count() - launches_before;
+    if (ok) {
+        size_t n = 0;
+        ok = cudaGraphGetNodes(e->graph, nullptr, &n) == cudaSuccess && n > 0;
+        std::vector<cudaGraphNode_t> nodes(n);
+        if (ok) ok = cudaGraphGetNodes(e->graph, nodes.data(), &n) == cudaSuccess;
+        for (size_t i = 0; ok && i < n; ++i) {
+            cudaGraphNodeType type;
+            if (cudaGraphNodeGetType(nodes[i], &type) != cudaSuccess) { ok = false; break; }
+            if (type != cudaGraphNodeTypeMemcpy) continue;
+            cudaMemcpy3DParms mp;
+            if (cudaGraphMemcpyNodeGetParams(nodes[i], &mp) != cudaSuccess) { ok = false; break; }
+            if (mp.dstPtr.ptr == e->x_stage.data()) e->x_node = nodes[i];
+            if (mp.dstPtr.ptr == e->t_stage.data()) e->t_node = nodes[i];
+        }
+        ok = ok && e->x_node && e->t_node;
+    }
+    if (ok) ok = cudaGraphInstantiate(&e->exec, e->graph, 0) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        m->drop(*e);
+        for (Parameter *p : m->params) p->node.reset();
+        m->graphs_enabled = false;
+        return false;
+    }
+    cuda_ok(cudaGraphLaunch(e->exec, stream), "cudaGraphLaunch");
+    ::ag::count_launches(e->kernels);
+    finish();
+    return true;
 }
 
 }  // namespace
@@ -609,10 +747,14 @@ int ag_model_train_step(ag_model *model, const void *x_host, const uint8_t *t_ho
     AG_REQUIRE(model && t_host && loss_host, AG_ERR_INVALID, "null argument");
     AG_ENTER(model->dev);
     AG_HOST_GUARD({
-        Tensor x = input_tensor(model, x_host, true, bs, c, h, w);
-        Tensor t = Tensor::from_host(model->pool, {bs}, AG_U8, t_host);
-        *loss_host = forward_backward(model, x, t);
-        apply_update(model, lr);
+        if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+        if (!x_host && bs > 0) throw Error(AG_ERR_INVALID, "input pointer is null");
+        if (!train_step_graph(model, x_host, t_host, bs, c, h, w, lr, loss_host)) {
+            Tensor x = input_tensor(model, x_host, true, bs, c, h, w);
+            Tensor t = Tensor::from_host(model->pool, {bs}, AG_U8, t_host);
+            *loss_host = forward_backward(model, x, t);
+            apply_update(model, lr);
+        }
     })
 }
 

@@ -267,6 +267,13 @@ AG_API int ag_cross_entropy_loss(ag_device *dev, ag_dtype dtype, ag_dtype label_
                                  const void *x, const void *t, int64_t bs, int64_t classes,
                                  float *loss_host);
 
+/* The same loss left in device memory (*loss_dev, one f32) without synchronising, so
+ * that a whole training step can be enqueued (and captured in a CUDA graph) before
+ * the host reads the value. ≙ the same kernels as ag_cross_entropy_loss. */
+AG_API int ag_cross_entropy_loss_device(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
+                                        const void *x, const void *t, int64_t bs, int64_t classes,
+                                        float *loss_dev);
+
 /* ≙ kernels::cross_entropy_loss_backward_<X>_<T>
  * (src/learn/neural_network/criterion.rs:79-137, 154-184):
  * dx = (dy / bs) * (softmax(x) - onehot(t)). */
