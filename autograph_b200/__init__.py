@@ -218,6 +218,38 @@ class Device:
                                                  rl, _ptr(y)))
         return y
 
+    def conv_dense_chain_forward(self, x, convs, weights, biases=None, relus=None):
+        """A small network in one kernel.  convs: list of (w, bias, relu, pool) with pool a
+        (ph, pw) window or None; then Flatten and the Dense (+ Relu) layers of
+        dense_chain_forward.  Raises AgError(AG_ERR_UNSUPPORTED) when the network does not
+        fit the fused kernel."""
+        bs, ic, ih, iw = x.shape
+        stages = (_capi.ConvStage * len(convs))()
+        keep = []
+        for st, (w, b, relu, pool) in zip(stages, convs):
+            w = w.contiguous()
+            keep.append(w)
+            st.w = w.data_ptr()
+            st.bias = b.data_ptr() if b is not None else None
+            st.oc = w.shape[0]
+            st.options = _conv_options(tuple(w.shape[2:]))
+            st.relu = int(relu)
+            st.pool[0], st.pool[1] = pool if pool else (0, 0)
+        n = len(weights)
+        biases = biases or [None] * n
+        relus = relus or [False] * n
+        weights = [w.contiguous() for w in weights]
+        dims = (ctypes.c_int64 * (n + 1))(weights[0].shape[0], *[w.shape[1] for w in weights])
+        ws = (ctypes.c_void_p * n)(*[w.data_ptr() for w in weights])
+        bp = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
+        rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
+        y = self.empty((bs, weights[-1].shape[1]), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_conv_dense_chain_forward(
+            self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw, len(convs),
+            stages, n, dims, ws, bp, rl, _ptr(y)))
+        return y
+
     def conv2_backward_input(self, w, dy, input_hw, padding=(0, 0), stride=(1, 1),
                              dilation=(1, 1)):
         oc, ic, fh, fw = w.shape

@@ -32,6 +32,11 @@ class ConvOptions(ctypes.Structure):
                 ("dilation", c_int32 * 2)]
 
 
+class ConvStage(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("oc", c_int64),
+                ("options", ConvOptions), ("relu", c_int32), ("pool", c_int32 * 2)]
+
+
 class LayerSpec(ctypes.Structure):
     _fields_ = [("kind", c_int32), ("a", c_int32), ("b", c_int32), ("c", c_int32), ("d", c_int32),
                 ("bias", c_int32)]
@@ -70,6 +75,9 @@ _SIGNATURES = {
     "ag_dense_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, _P, c_int64, _P, c_int, _P]),
     "ag_dense_chain_forward": (c_int, [_P, c_int, _P, c_int64, c_int32, POINTER(c_int64),
                                        POINTER(_P), POINTER(_P), POINTER(c_int32), _P]),
+    "ag_conv_dense_chain_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
+                                            c_int32, POINTER(ConvStage), c_int32, POINTER(c_int64),
+                                            POINTER(_P), POINTER(_P), POINTER(c_int32), _P]),
     "ag_conv2_relu_max_pool2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
                                                 _P, c_int64, _P, POINTER(ConvOptions), c_int,
                                                 c_int32, c_int32, _P]),

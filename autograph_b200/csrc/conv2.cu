@@ -348,6 +348,14 @@ int ag_conv2_backward_input(ag_device *dev, ag_dtype dtype, const void *w, int64
                "bad output channel count");
     if (bs == 0 || ic == 0) return AG_OK;
     AG_REQUIRE(w && dy && dx, AG_ERR_INVALID, "null tensor pointer");
+    if (direct::eligible_backward_input(bs, ic, ih, iw, oc, opt)) {
+        if (dtype == AG_F32)
+            return direct::backward_input<float>(dev, (const float *)w, oc, ic, (const float *)dy,
+                                                 bs, ih, iw, opt, (float *)dx);
+        return direct::backward_input<__nv_bfloat16>(dev, (const __nv_bfloat16 *)w, oc, ic,
+                                                     (const __nv_bfloat16 *)dy, bs, ih, iw, opt,
+                                                     (__nv_bfloat16 *)dx);
+    }
     if (dtype == AG_F32)
         return conv2_backward_input_t<float>(dev, g, (const float *)w, (int)oc, (const float *)dy,
                                              (float *)dx);
@@ -365,6 +373,14 @@ int ag_conv2_backward_weight(ag_device *dev, ag_dtype dtype, const void *x, int6
     AG_REQUIRE(oc >= 0 && oc < (1 << 30), AG_ERR_SHAPE, "bad output channel count");
     if (oc == 0 || ic == 0) return AG_OK;
     AG_REQUIRE(dw && (bs == 0 || (x && dy)), AG_ERR_INVALID, "null tensor pointer");
+    if (direct::eligible_backward_weight(bs, ic, ih, iw, oc, opt)) {
+        if (dtype == AG_F32)
+            return direct::backward_weight<float>(dev, (const float *)x, bs, ic, ih, iw,
+                                                  (const float *)dy, oc, opt, beta, (float *)dw);
+        return direct::backward_weight<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw,
+                                                      (const __nv_bfloat16 *)dy, oc, opt, beta,
+                                                      (__nv_bfloat16 *)dw);
+    }
     if (dtype == AG_F32)
         return conv2_backward_weight_t<float>(dev, g, (const float *)x, (const float *)dy, (int)oc,
                                               beta, (float *)dw);

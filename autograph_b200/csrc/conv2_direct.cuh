@@ -17,5 +17,21 @@ template <class T>
 int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw, const T *w,
             int64_t oc, const T *bias, const ag_conv2_options *o, bool relu, bool pool, T *y);
 
+// dx = the gradient of conv2(x, w) with respect to x, given dy [bs, oc, oh, ow]
+// and w [oc, ic, fh, fw]: the same kernel run on the transposed problem.
+bool eligible_backward_input(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int64_t oc,
+                             const ag_conv2_options *o);
+template <class T>
+int backward_input(ag_device *dev, const T *w, int64_t oc, int64_t ic, const T *dy, int64_t bs,
+                   int64_t ih, int64_t iw, const ag_conv2_options *o, T *dx);
+
+// dw = beta * dw + the gradient of conv2(x, w) with respect to w: per-CTA partial
+// sums over a group of images, then a fixed-order reduction (deterministic).
+bool eligible_backward_weight(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int64_t oc,
+                              const ag_conv2_options *o);
+template <class T>
+int backward_weight(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw,
+                    const T *dy, int64_t oc, const ag_conv2_options *o, float beta, T *dw);
+
 }  // namespace direct
 }  // namespace ag

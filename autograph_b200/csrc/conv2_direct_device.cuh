@@ -1,0 +1,178 @@
+// Device-side pieces of the direct convolution, shared by the stand-alone
+// kernels (conv2_direct.cu) and the fused conv -> dense chain (conv_chain.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace ag {
+namespace direct {
+
+template <class T>
+__device__ __forceinline__ void load4_to_f32(const T *p, float *dst);
+template <>
+__device__ __forceinline__ void load4_to_f32<float>(const float *p, float *dst) {
+    *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(p);
+}
+template <>
+__device__ __forceinline__ void load4_to_f32<__nv_bfloat16>(const __nv_bfloat16 *p, float *dst) {
+    uint2 q = *reinterpret_cast<const uint2 *>(p);
+    dst[0] = __uint_as_float(q.x << 16);
+    dst[1] = __uint_as_float(q.x & 0xffff0000u);
+    dst[2] = __uint_as_float(q.y << 16);
+    dst[3] = __uint_as_float(q.y & 0xffff0000u);
+}
+
+// In the kernel's view: ic channels of ih x iw (staged in shared memory) are
+// correlated with an [oc][ic][FH][FW] filter bank into oc channels of
+// (ih-FH+1) x (iw-FW+1).  For the gradient with respect to the input the view
+// is the transposed problem: the staged image is dy with a zero border of
+// FH-1 / FW-1 on every side, ic counts dy's channels, oc the input channels, and
+// the filter bank is read with its two channel axes swapped and both spatial
+// axes reversed.
+struct Params {
+    int bs, ic, ih, iw, oc;
+    int group;       // images per CTA
+    int ocp;         // oc rounded up to a multiple of 2 (weight row pitch in shared memory)
+    bool relu, pool;
+};
+
+constexpr int OC_T = 2;  // output channels per thread
+constexpr int PBH = 2;   // a thread owns a PBH x PBW block of output pixels
+constexpr int PBW = 4;
+
+// Copies `total` contiguous elements to shared memory as f32.
+template <class T>
+__device__ __forceinline__ void stage_contiguous(const T *__restrict__ src, float *dst, int total) {
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) % (4 * sizeof(T))) == 0);
+    const int nvec = vec ? total / 4 : 0;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) load4_to_f32<T>(src + 4 * i, dst + 4 * i);
+    for (int i = nvec * 4 + threadIdx.x; i < total; i += blockDim.x) dst[i] = to_f32(src[i]);
+}
+
+// Filter bank [oc][taps] (taps = ic*FH*FW) to shared memory as [tap][ocp], and the
+// bias (zero where absent) to s_bias[ocp].
+template <class T>
+__device__ __forceinline__ void stage_filters(const T *__restrict__ w, const T *__restrict__ bias,
+                                              float *s_w, float *s_bias, int oc, int ocp, int taps) {
+    for (int i = threadIdx.x; i < oc * taps; i += blockDim.x) {
+        const int o = i / taps, tap = i - o * taps;
+        s_w[tap * ocp + o] = to_f32(w[i]);
+    }
+    if (ocp != oc)
+        for (int tap = threadIdx.x; tap < taps; tap += blockDim.x) s_w[tap * ocp + oc] = 0.f;
+    for (int i = threadIdx.x; i < ocp; i += blockDim.x)
+        s_bias[i] = (bias != nullptr && i < oc) ? to_f32(bias[i]) : 0.f;
+}
+
+// The work of one CTA once images, filters and bias are in shared memory.
+// Work item = (image, 2x4 pixel block, pair of output channels); consecutive
+// threads take consecutive channel pairs of one block, so a filter tap is one
+// 8-byte shared-memory load per thread (contiguous across the channel pairs)
+// and the input patch loads broadcast.  Per input channel a thread keeps the
+// (FH+1) x (FW+3) patch in registers: 16 FFMAs per weight load.
+//
+// Results leave through `out`:
+//   out.pooled(g, oc, py, px, v)  one value of the 2x2 / stride-2 max pool (p.pool)
+//   out.plain(g, oc, y, x, v)     one convolution output                  (!p.pool)
+// v has been rounded to T (after the sum and again after the bias) like a
+// store / reload of the layer's output would.
+template <class T, int FH, int FW, class Out>
+__device__ __forceinline__ void compute_items(const float *s_img, const float *s_w,
+                                              const float *s_bias, bool has_bias, const Params &p,
+                                              int nimg, Out out) {
+    const int img_elems = p.ic * p.ih * p.iw;
+    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;  // both even
+    const int nby = oh / PBH, nbx = (ow + PBW - 1) / PBW;
+    const int n_ocg = p.ocp / OC_T;
+    const int items_per_img = n_ocg * nby * nbx;
+    const int items = nimg * items_per_img;
+
+    for (int item = threadIdx.x; item < items; item += blockDim.x) {
+        const int g = item / items_per_img;
+        int r = item - g * items_per_img;
+        const int blk = r / n_ocg, ocg = r - blk * n_ocg;
+        const int by = blk / nbx, bx = blk - by * nbx;
+        const int oc0 = ocg * OC_T;
+        const int y0 = by * PBH, x0 = bx * PBW;
+        // Blocks at the right edge may hang over by two pixels (ow is even but not always
+        // a multiple of four): clamp their reads, drop their results.
+        const int col_max = p.iw - 1 - x0;
+
+        float acc[PBH][PBW][OC_T];
+#pragma unroll
+        for (int a = 0; a < PBH; ++a)
+#pragma unroll
+            for (int b = 0; b < PBW; ++b)
+#pragma unroll
+                for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
+
+        const float *img = s_img + g * img_elems + y0 * p.iw + x0;
+        for (int ci = 0; ci < p.ic; ++ci) {
+            float patch[FH + PBH - 1][FW + PBW - 1];
+            const float *pi = img + ci * p.ih * p.iw;
+#pragma unroll
+            for (int a = 0; a < FH + PBH - 1; ++a) {
+                const float *prow = pi + a * p.iw;
+#pragma unroll
+                for (int b = 0; b < FW + PBW - 1; ++b) patch[a][b] = prow[min(b, col_max)];
+            }
+            const float *wc = s_w + ci * FH * FW * p.ocp + oc0;
+#pragma unroll
+            for (int fi = 0; fi < FH; ++fi)
+#pragma unroll
+                for (int fj = 0; fj < FW; ++fj) {
+                    const float2 wv = *reinterpret_cast<const float2 *>(wc + (fi * FW + fj) * p.ocp);
+#pragma unroll
+                    for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                        for (int b = 0; b < PBW; ++b) {
+                            acc[a][b][0] = fmaf(patch[fi + a][fj + b], wv.x, acc[a][b][0]);
+                            acc[a][b][1] = fmaf(patch[fi + a][fj + b], wv.y, acc[a][b][1]);
+                        }
+                }
+        }
+
+        // ---- epilogue: round to T, bias, relu, optional 2x2 max pool ---------------
+#pragma unroll
+        for (int o = 0; o < OC_T; ++o) {
+            const int oc = oc0 + o;
+            if (oc >= p.oc) break;
+            float v[PBH][PBW];
+#pragma unroll
+            for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                for (int b = 0; b < PBW; ++b) {
+                    float t = to_f32(from_f32<T>(acc[a][b][o]));
+                    if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
+                    if (p.relu) t = (t >= 0.f) ? t : 0.f;
+                    v[a][b] = t;
+                }
+            if (p.pool) {
+                const int ph = oh / 2, pw = ow / 2;
+#pragma unroll
+                for (int wy = 0; wy < PBH / 2; ++wy)
+#pragma unroll
+                    for (int wx = 0; wx < PBW / 2; ++wx) {
+                        const int py = y0 / 2 + wy, px = x0 / 2 + wx;
+                        if (py < ph && px < pw) {
+                            // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
+                            float m = v[2 * wy][2 * wx];
+                            if (v[2 * wy][2 * wx + 1] > m) m = v[2 * wy][2 * wx + 1];
+                            if (v[2 * wy + 1][2 * wx] > m) m = v[2 * wy + 1][2 * wx];
+                            if (v[2 * wy + 1][2 * wx + 1] > m) m = v[2 * wy + 1][2 * wx + 1];
+                            out.pooled(g, oc, py, px, m);
+                        }
+                    }
+            } else {
+#pragma unroll
+                for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                    for (int b = 0; b < PBW; ++b)
+                        if (y0 + a < oh && x0 + b < ow) out.plain(g, oc, y0 + a, x0 + b, v[a][b]);
+            }
+        }
+    }
+}
+
+}  // namespace direct
+}  // namespace ag

@@ -1,0 +1,241 @@
+// A whole small network in one kernel: one or two (Conv2 -> Relu -> MaxPool2)
+// stages, Flatten, and a chain of Dense (-> Relu) layers -- the shape of LeNet5.
+//
+// At batch 1000 each layer of such a network is a few microseconds of work, so a
+// layer-by-layer run is bound by launch gaps, by the tail of every grid and by
+// the round trips of the activations through L2.  Here a CTA owns 8 images from
+// the input to the logits: the images and both filter banks are staged in shared
+// memory once, the activations of every layer stay in shared memory, and only the
+// dense weights are streamed (from L2) while the logits are the only thing
+// written back.  When the images live in pinned host memory, the CTAs that have
+// received theirs compute while the others still wait for PCIe.
+//
+// The arithmetic is that of the stand-alone kernels (conv2_direct_device.cuh,
+// dense_small_device.cuh), including the rounding to the tensor type at every
+// layer boundary, so the result equals the layer-by-layer calls bit for bit.
+#include "conv2_direct.cuh"
+#include "conv2_direct_device.cuh"
+#include "conv_chain.cuh"
+#include "dense_small_device.cuh"
+
+namespace ag {
+namespace conv_chain {
+
+using dense_small::ROWS;
+
+struct StagePlan {
+    const void *w, *bias;
+    direct::Params p;  // kernel view of the stage (group = ROWS)
+    int w_off, bias_off;  // float offsets into shared memory
+    int out_h, out_w;     // after the optional pool
+};
+
+struct Plan {
+    int bs, n_conv;
+    StagePlan st[kMaxConv];
+    int in_off, mid_off;  // staged input images; output of stage 0 when there are two stages
+    int xa_off, xb_off, red_off;
+    dense_small::ChainParams chain;
+};
+
+// Output of a conv stage as the next stage's image: [g][oc][h][w].
+struct ImageOut {
+    float *dst;
+    int oc, h, w;
+    __device__ __forceinline__ void pooled(int g, int c, int py, int px, float v) const {
+        dst[((g * oc + c) * h + py) * w + px] = v;
+    }
+    __device__ __forceinline__ void plain(int g, int c, int y, int x, float v) const {
+        pooled(g, c, y, x, v);
+    }
+};
+
+// Output of the last conv stage, flattened (c, h, w) into the dense chain's
+// input layout [k][ROWS].
+struct FlatOut {
+    float *xa;
+    int h, w;
+    __device__ __forceinline__ void pooled(int g, int c, int py, int px, float v) const {
+        xa[((c * h + py) * w + px) * ROWS + g] = v;
+    }
+    __device__ __forceinline__ void plain(int g, int c, int y, int x, float v) const {
+        pooled(g, c, y, x, v);
+    }
+};
+
+template <class T, int F>
+__global__ void __launch_bounds__(512, 1)
+    conv_chain_kernel(const T *__restrict__ x, T *__restrict__ y, const Plan pl) {
+    extern __shared__ __align__(16) float smem[];
+    const int b0 = blockIdx.x * ROWS;
+    const int nimg = min(ROWS, pl.bs - b0);
+    const direct::Params &p0 = pl.st[0].p;
+    const int img_elems = p0.ic * p0.ih * p0.iw;
+    float *xa = smem + pl.xa_off;
+
+    direct::stage_contiguous<T>(x + (int64_t)b0 * img_elems, smem + pl.in_off, nimg * img_elems);
+    for (int s = 0; s < pl.n_conv; ++s) {
+        const StagePlan &sp = pl.st[s];
+        direct::stage_filters<T>(reinterpret_cast<const T *>(sp.w),
+                                 reinterpret_cast<const T *>(sp.bias), smem + sp.w_off,
+                                 smem + sp.bias_off, sp.p.oc, sp.p.ocp, sp.p.ic * F * F);
+    }
+    if (nimg < ROWS) {
+        // rows without an image still flow through the dense layers: give them zeros
+        const int k0 = pl.chain.s[0].K;
+        for (int i = threadIdx.x; i < k0 * ROWS; i += blockDim.x) xa[i] = 0.f;
+    }
+    __syncthreads();
+
+    const float *img = smem + pl.in_off;
+    for (int s = 0; s < pl.n_conv; ++s) {
+        const StagePlan &sp = pl.st[s];
+        if (s + 1 < pl.n_conv) {
+            ImageOut out{smem + pl.mid_off, sp.p.oc, sp.out_h, sp.out_w};
+            direct::compute_items<T, F, F>(img, smem + sp.w_off, smem + sp.bias_off,
+                                           sp.bias != nullptr, sp.p, nimg, out);
+            img = smem + pl.mid_off;
+        } else {
+            FlatOut out{xa, sp.out_h, sp.out_w};
+            direct::compute_items<T, F, F>(img, smem + sp.w_off, smem + sp.bias_off,
+                                           sp.bias != nullptr, sp.p, nimg, out);
+        }
+        __syncthreads();
+    }
+    dense_small::chain_layers<T>(xa, smem + pl.xb_off, smem + pl.red_off, pl.chain, b0, nimg, y);
+}
+
+static bool default_options(const ag_conv2_options &o) {
+    return !o.padding[0] && !o.padding[1] && o.stride[0] == 1 && o.stride[1] == 1 &&
+           o.dilation[0] == 1 && o.dilation[1] == 1;
+}
+
+// Fills `pl`; returns the dynamic shared memory in bytes, or 0 when the network
+// does not fit the kernel.
+static size_t make_plan(Plan *pl, int64_t bs, int64_t ic, int64_t ih, int64_t iw, int n_conv,
+                        const ag_conv_stage *stages, int n_dense,
+                        const dense_small::ChainLayer *layers) {
+    if (n_conv < 1 || n_conv > kMaxConv || n_dense < 1 || n_dense > dense_small::kMaxChain) return 0;
+    if (bs <= 0 || bs > (int64_t)ROWS * 65535 * 32) return 0;
+    const int f = stages[0].options.filter[0];
+    int off = 0;
+    auto take = [&](int64_t floats) {
+        const int at = off;
+        off += (int)((floats + 3) & ~3ll);
+        return at;
+    };
+    pl->bs = (int)bs;
+    pl->n_conv = n_conv;
+    pl->in_off = take((int64_t)ROWS * ic * ih * iw);
+    pl->mid_off = 0;
+    int64_t c = ic, h = ih, w = iw;
+    for (int s = 0; s < n_conv; ++s) {
+        const ag_conv_stage &cs = stages[s];
+        if (!default_options(cs.options) || cs.options.filter[0] != f || cs.options.filter[1] != f)
+            return 0;
+        if (!direct::eligible(ROWS, c, h, w, cs.oc, &cs.options)) return 0;
+        const bool pool = cs.pool[0] != 0 || cs.pool[1] != 0;
+        if (pool && (cs.pool[0] != 2 || cs.pool[1] != 2)) return 0;
+        StagePlan &sp = pl->st[s];
+        sp.w = cs.w;
+        sp.bias = cs.bias;
+        sp.p.bs = (int)bs; sp.p.ic = (int)c; sp.p.ih = (int)h; sp.p.iw = (int)w;
+        sp.p.oc = (int)cs.oc;
+        sp.p.ocp = ((int)cs.oc + 1) & ~1;
+        sp.p.group = ROWS;
+        sp.p.relu = cs.relu != 0;
+        sp.p.pool = pool;
+        sp.w_off = take((int64_t)c * f * f * sp.p.ocp);
+        sp.bias_off = take(sp.p.ocp);
+        const int64_t oh = h - f + 1, ow = w - f + 1;
+        sp.out_h = (int)(pool ? oh / 2 : oh);
+        sp.out_w = (int)(pool ? ow / 2 : ow);
+        c = cs.oc; h = sp.out_h; w = sp.out_w;
+        if (s + 1 < n_conv) pl->mid_off = take((int64_t)ROWS * c * h * w);
+    }
+    if (c * h * w != layers[0].inputs) return 0;
+    for (int i = 0; i < n_dense; ++i) {
+        if (!dense_small::eligible(ROWS, layers[i].inputs, layers[i].outputs)) return 0;
+        if (i > 0 && layers[i].inputs != layers[i - 1].outputs) return 0;
+    }
+    const size_t chain_floats = dense_small::plan_chain(&pl->chain, (int)bs, n_dense, layers);
+    pl->xa_off = take((int64_t)pl->chain.max_k * ROWS);
+    pl->xb_off = take((int64_t)pl->chain.max_k * ROWS);
+    pl->red_off = take(pl->chain.red_floats);
+    (void)chain_floats;
+    const size_t bytes = (size_t)off * sizeof(float);
+    return bytes <= 200 * 1024 ? bytes : 0;
+}
+
+bool eligible(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int n_conv,
+              const ag_conv_stage *stages, int n_dense, const dense_small::ChainLayer *layers) {
+    Plan pl;
+    const int f = (n_conv >= 1) ? stages[0].options.filter[0] : 0;
+    if (f != 5 && f != 3) return false;
+    return make_plan(&pl, bs, ic, ih, iw, n_conv, stages, n_dense, layers) != 0;
+}
+
+template <class T, int F>
+static int launch(ag_device *dev, const T *x, T *y, const Plan &pl, size_t smem) {
+    auto kernel = conv_chain_kernel<T, F>;
+    if (smem > 48 * 1024)
+        AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    kernel<<<(unsigned)ceil_div(pl.bs, ROWS), 512, smem, dev->stream>>>(x, y, pl);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+template <class T>
+int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw, int n_conv,
+            const ag_conv_stage *stages, int n_dense, const dense_small::ChainLayer *layers, T *y) {
+    Plan pl;
+    const size_t smem = make_plan(&pl, bs, ic, ih, iw, n_conv, stages, n_dense, layers);
+    AG_REQUIRE(smem != 0, AG_ERR_UNSUPPORTED, "this network does not fit the fused kernel");
+    if (stages[0].options.filter[0] == 5) return launch<T, 5>(dev, x, y, pl, smem);
+    return launch<T, 3>(dev, x, y, pl, smem);
+}
+
+template int forward<float>(ag_device *, const float *, int64_t, int64_t, int64_t, int64_t, int,
+                            const ag_conv_stage *, int, const dense_small::ChainLayer *, float *);
+template int forward<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, int64_t, int64_t, int64_t,
+                                    int64_t, int, const ag_conv_stage *, int,
+                                    const dense_small::ChainLayer *, __nv_bfloat16 *);
+
+}  // namespace conv_chain
+}  // namespace ag
+
+using namespace ag;
+
+extern "C" int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                           int64_t ic, int64_t ih, int64_t iw, int32_t n_conv,
+                                           const ag_conv_stage *stages, int32_t n_dense,
+                                           const int64_t *dims, const void *const *weights,
+                                           const void *const *biases, const int32_t *relu,
+                                           void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "conv_dense_chain %d not implemented",
+               (int)dtype);
+    AG_REQUIRE(bs >= 0 && ic > 0 && ih > 0 && iw > 0, AG_ERR_SHAPE, "bad input shape");
+    AG_REQUIRE(n_conv >= 1 && n_conv <= conv_chain::kMaxConv && stages, AG_ERR_UNSUPPORTED,
+               "1..%d convolution stages are supported", conv_chain::kMaxConv);
+    AG_REQUIRE(n_dense >= 1 && n_dense <= dense_small::kMaxChain && dims && weights,
+               AG_ERR_UNSUPPORTED, "1..%d dense layers are supported", dense_small::kMaxChain);
+    dense_small::ChainLayer layers[dense_small::kMaxChain];
+    for (int i = 0; i < n_dense; ++i) {
+        AG_REQUIRE(dims[i] > 0 && dims[i + 1] > 0 && dims[i] < (1 << 30) && dims[i + 1] < (1 << 30),
+                   AG_ERR_SHAPE, "bad dense width");
+        AG_REQUIRE(weights[i] != nullptr, AG_ERR_INVALID, "null weight pointer");
+        layers[i] = {weights[i], biases ? biases[i] : nullptr, (int)dims[i], (int)dims[i + 1],
+                     relu ? relu[i] : 0};
+    }
+    for (int s = 0; s < n_conv; ++s)
+        AG_REQUIRE(stages[s].w != nullptr && stages[s].oc > 0, AG_ERR_INVALID, "bad conv stage");
+    if (bs == 0) return AG_OK;
+    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    if (dtype == AG_F32)
+        return conv_chain::forward<float>(dev, (const float *)x, bs, ic, ih, iw, n_conv, stages,
+                                          n_dense, layers, (float *)y);
+    return conv_chain::forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw, n_conv,
+                                              stages, n_dense, layers, (__nv_bfloat16 *)y);
+}

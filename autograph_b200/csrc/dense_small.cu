@@ -10,11 +10,10 @@
 // keeps 8 accumulators.  The k slices are then summed in a fixed order, so the
 // result is deterministic.  The code is small on purpose.
 #include "dense_small.cuh"
+#include "dense_small_device.cuh"
 
 namespace ag {
 namespace dense_small {
-
-constexpr int ROWS = 8;
 
 template <class T>
 __global__ void __launch_bounds__(1024)
@@ -96,25 +95,6 @@ int forward(ag_device *dev, const T *x, int m, int k, const T *w, int n, const T
 }
 
 // ---------------------------------------------------------------- layer chain
-struct ChainStep {
-    const void *w, *bias;
-    int K, N, np, slices, kchunk, relu;
-};
-struct ChainParams {
-    ChainStep s[kMaxChain];
-    int n_layers, M, max_k, red_floats;
-};
-
-static void plan_step(int k, int n, int *np, int *slices, int *kchunk) {
-    *np = ((n + 31) / 32) * 32;
-    int sl = 1024 / *np;
-    if (sl > 16) sl = 16;
-    if (sl > k / 8) sl = k / 8;
-    if (sl < 1) sl = 1;
-    *kchunk = (k + sl - 1) / sl;
-    *slices = (k + *kchunk - 1) / *kchunk;
-}
-
 template <class T>
 __global__ void __launch_bounds__(1024)
     dense_chain_kernel(const T *__restrict__ x, T *__restrict__ y, const ChainParams p) {
@@ -132,53 +112,7 @@ __global__ void __launch_bounds__(1024)
         }
     }
     __syncthreads();
-    for (int l = 0; l < p.n_layers; ++l) {
-        const ChainStep st = p.s[l];
-        const T *w = reinterpret_cast<const T *>(st.w);
-        const T *bias = reinterpret_cast<const T *>(st.bias);
-        const int n = threadIdx.x % st.np, slice = threadIdx.x / st.np;
-        if (slice < st.slices) {
-            float acc[ROWS];
-#pragma unroll
-            for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-            if (n < st.N) {
-                const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
-                const T *wp = w + (int64_t)k0 * st.N + n;
-#pragma unroll 8
-                for (int k = k0; k < k1; ++k, wp += st.N) {
-                    const float wv = to_f32(*wp);
-                    const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
-                    const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
-                    acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
-                    acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
-                    acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
-                    acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * st.np + n] = acc[r];
-        }
-        __syncthreads();
-        const bool last = l + 1 == p.n_layers;
-        for (int i = threadIdx.x; i < ROWS * st.np; i += blockDim.x) {
-            const int r = i / st.np, c = i - r * st.np;
-            if (c >= st.N) continue;
-            float s = 0.f;
-            for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
-            float v = to_f32(from_f32<T>(s));
-            if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
-            if (st.relu) v = (v >= 0.f) ? v : 0.f;
-            if (last) {
-                if (r < rows) y[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
-            } else {
-                xb[c * ROWS + r] = v;  // already rounded to T: equals storing and reloading it
-            }
-        }
-        __syncthreads();
-        float *t = xa;
-        xa = xb;
-        xb = t;
-    }
+    chain_layers<T>(xa, xb, red, p, m0, rows, y);
 }
 
 bool chain_eligible(int64_t m, int n_layers, const ChainLayer *layers) {
@@ -193,25 +127,8 @@ bool chain_eligible(int64_t m, int n_layers, const ChainLayer *layers) {
 template <class T>
 int chain_forward(ag_device *dev, const T *x, int m, int n_layers, const ChainLayer *layers, T *y) {
     ChainParams p;
-    p.n_layers = n_layers;
-    p.M = m;
-    p.max_k = 0;
-    p.red_floats = 0;
-    int threads = 32;
-    for (int i = 0; i < n_layers; ++i) {
-        ChainStep &st = p.s[i];
-        st.w = layers[i].w;
-        st.bias = layers[i].bias;
-        st.K = layers[i].inputs;
-        st.N = layers[i].outputs;
-        st.relu = layers[i].relu;
-        plan_step(st.K, st.N, &st.np, &st.slices, &st.kchunk);
-        if (st.K > p.max_k) p.max_k = st.K;
-        if (st.N > p.max_k) p.max_k = st.N;  // a layer's output is the next layer's input
-        if (st.slices * ROWS * st.np > p.red_floats) p.red_floats = st.slices * ROWS * st.np;
-        if (st.np * st.slices > threads) threads = st.np * st.slices;
-    }
-    const size_t smem = ((size_t)2 * p.max_k * ROWS + (size_t)p.red_floats) * sizeof(float);
+    const size_t smem = plan_chain(&p, m, n_layers, layers) * sizeof(float);
+    const int threads = p.threads;
     auto kernel = dense_chain_kernel<T>;
     if (smem > 48 * 1024)
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

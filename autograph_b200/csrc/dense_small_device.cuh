@@ -1,0 +1,116 @@
+// Device-side pieces of the dense layer chain, shared by the stand-alone kernel
+// (dense_small.cu) and the fused conv -> dense chain (conv_chain.cu).
+#pragma once
+
+#include "dense_small.cuh"
+
+namespace ag {
+namespace dense_small {
+
+constexpr int ROWS = 8;  // rows of x a CTA owns
+
+struct ChainStep {
+    const void *w, *bias;
+    int K, N, np, slices, kchunk, relu;
+};
+struct ChainParams {
+    ChainStep s[kMaxChain];
+    int n_layers, M, max_k, red_floats;
+    int threads;  // (column, k slice) pairs of the widest layer
+};
+
+// Split of one layer over up to 1024 (column, k slice) pairs.
+inline void plan_step(int k, int n, int *np, int *slices, int *kchunk) {
+    *np = ((n + 31) / 32) * 32;
+    int sl = 1024 / *np;
+    if (sl > 16) sl = 16;
+    if (sl > k / 8) sl = k / 8;
+    if (sl < 1) sl = 1;
+    *kchunk = (k + sl - 1) / sl;
+    *slices = (k + *kchunk - 1) / *kchunk;
+}
+
+// Fills the plan; returns the shared-memory floats the layers need
+// (2 * max_k * ROWS for the two activation buffers + red_floats).
+inline size_t plan_chain(ChainParams *p, int m, int n_layers, const ChainLayer *layers) {
+    p->n_layers = n_layers;
+    p->M = m;
+    p->max_k = 0;
+    p->red_floats = 0;
+    p->threads = 32;
+    for (int i = 0; i < n_layers; ++i) {
+        ChainStep &st = p->s[i];
+        st.w = layers[i].w;
+        st.bias = layers[i].bias;
+        st.K = layers[i].inputs;
+        st.N = layers[i].outputs;
+        st.relu = layers[i].relu;
+        plan_step(st.K, st.N, &st.np, &st.slices, &st.kchunk);
+        if (st.K > p->max_k) p->max_k = st.K;
+        if (st.N > p->max_k) p->max_k = st.N;  // a layer's output is the next layer's input
+        if (st.slices * ROWS * st.np > p->red_floats) p->red_floats = st.slices * ROWS * st.np;
+        if (st.np * st.slices > p->threads) p->threads = st.np * st.slices;
+    }
+    return (size_t)2 * p->max_k * ROWS + (size_t)p->red_floats;
+}
+
+// Runs every layer of the chain for the ROWS rows whose first-layer input is in
+// xa as [k][ROWS] (f32).  xb is the second activation buffer, red the
+// [slices][ROWS][np] scratch.  The plan's (column, k slice) pairs are spread over
+// the CTA's threads (a CTA with fewer threads than pairs takes several each), so
+// the sums and their order do not depend on the CTA size.  Rows >= rows are
+// computed but not stored.  All threads of the CTA must call this.
+template <class T>
+__device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, const ChainParams &p,
+                                             int m0, int rows, T *__restrict__ y) {
+    for (int l = 0; l < p.n_layers; ++l) {
+        const ChainStep st = p.s[l];
+        const T *w = reinterpret_cast<const T *>(st.w);
+        const T *bias = reinterpret_cast<const T *>(st.bias);
+        for (int vt = threadIdx.x; vt < st.np * st.slices; vt += blockDim.x) {
+            const int n = vt % st.np, slice = vt / st.np;
+            float acc[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+            if (n < st.N) {
+                const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
+                const T *wp = w + (int64_t)k0 * st.N + n;
+#pragma unroll 8
+                for (int k = k0; k < k1; ++k, wp += st.N) {
+                    const float wv = to_f32(*wp);
+                    const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
+                    const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
+                    acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
+                    acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
+                    acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
+                    acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * st.np + n] = acc[r];
+        }
+        __syncthreads();
+        const bool last = l + 1 == p.n_layers;
+        for (int i = threadIdx.x; i < ROWS * st.np; i += blockDim.x) {
+            const int r = i / st.np, c = i - r * st.np;
+            if (c >= st.N) continue;
+            float s = 0.f;
+            for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
+            float v = to_f32(from_f32<T>(s));
+            if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
+            if (st.relu) v = (v >= 0.f) ? v : 0.f;
+            if (last) {
+                if (r < rows) y[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
+            } else {
+                xb[c * ROWS + r] = v;  // already rounded to T: equals storing and reloading it
+            }
+        }
+        __syncthreads();
+        float *t = xa;
+        xa = xb;
+        xb = t;
+    }
+}
+
+}  // namespace dense_small
+}  // namespace ag

@@ -363,5 +363,27 @@ __global__ void splitk_reduce_kernel(const float *ws, int64_t plane, int splits,
     E.store(m, n, s);
 }
 
+// The same sum for small planes with many splits: a CTA takes 32 outputs, eight
+// thread groups each add every eighth plane, and the eight partial sums are added
+// in group order (again a fixed order, so the result is reproducible).
+template <class Epi>
+__global__ void __launch_bounds__(256)
+    splitk_reduce_small_kernel(const float *ws, int64_t plane, int splits, int M, int N, Epi E) {
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int64_t i = (int64_t)blockIdx.x * 32 + lane;
+    float s = 0.f;
+    if (i < plane)
+        for (int z = grp; z < splits; z += 8) s += ws[(int64_t)z * plane + i];
+    part[grp][lane] = s;
+    __syncthreads();
+    if (grp == 0 && i < plane) {
+        float t = part[0][lane];
+#pragma unroll
+        for (int g = 1; g < 8; ++g) t += part[g][lane];
+        E.store((int)(i / N), (int)(i % N), t);
+    }
+}
+
 }  // namespace simt
 }  // namespace ag

@@ -91,9 +91,14 @@ int gemm(ag_device *dev, int M, int N, int K, const AOp &A, const BOp &B, const 
     if (!ws) AG_TRY(workspace(dev, sizeof(float) * (size_t)plane * (size_t)splits, &ws));
     PartialEpilogue P{(float *)ws, plane, N};
     AG_TRY(launch_any(dev, id, M, N, K, splits, k_chunk, A, B, P));
-    int threads = 256;
-    splitk_reduce_kernel<Epi><<<(unsigned)ceil_div(plane, threads), threads, 0, dev->stream>>>(
-        (const float *)ws, plane, splits, M, N, E);
+    if (splits >= 16 && plane <= 32 * 4 * (int64_t)dev->sm_count) {
+        splitk_reduce_small_kernel<Epi><<<(unsigned)ceil_div(plane, 32), 256, 0, dev->stream>>>(
+            (const float *)ws, plane, splits, M, N, E);
+    } else {
+        int threads = 256;
+        splitk_reduce_kernel<Epi><<<(unsigned)ceil_div(plane, threads), threads, 0, dev->stream>>>(
+            (const float *)ws, plane, splits, M, N, E);
+    }
     AG_CHECK_LAUNCH();
     return AG_OK;
 }

@@ -71,6 +71,14 @@ struct ag_model {
     uint64_t tick = 0;
     bool graphs_enabled = true;
     bool zero_copy_enabled = true;
+    // Two side streams (each behind its own device handle) and the events that fork
+    // and join them: a host-input pass is captured as batch slices that alternate
+    // between the two, so one slice's later layers run while the next slice's first
+    // layer is still pulling its images over PCIe.
+    ag_device *side[2] = {nullptr, nullptr};
+    cudaEvent_t fork_event = nullptr, join_event[2] = {nullptr, nullptr};
+    int slices = 0;  // 0: chosen from the batch size
+    bool whole_network = true;  // try the one-kernel form of the network at inference
     std::vector<std::unique_ptr<Layer>> layers;
     std::vector<Parameter *> params;
     std::vector<int64_t> offsets;  // element offset of each parameter in the buckets
@@ -84,6 +92,19 @@ struct ag_model {
         graphs_enabled = !(e && e[0] == '0');
         const char *z = getenv("AG_ZERO_COPY");
         zero_copy_enabled = !(z && z[0] == '0');
+        if (const char *c = getenv("AG_INFER_SLICES")) slices = std::max(1, std::min(16, atoi(c)));
+        const char *f = getenv("AG_FUSE_NET");
+        whole_network = !(f && f[0] == '0');
+    }
+    bool ensure_side_streams() {
+        if (side[0]) return true;
+        if (ag_device_create(ag_device_ordinal(dev), &side[0]) != AG_OK ||
+            ag_device_create(ag_device_ordinal(dev), &side[1]) != AG_OK)
+            return false;
+        bool ok = cudaEventCreateWithFlags(&fork_event, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < 2; ++i)
+            ok = ok && cudaEventCreateWithFlags(&join_event[i], cudaEventDisableTiming) == cudaSuccess;
+        return ok;
     }
     void drop(CapturedPass &p) {
         if (p.exec) cudaGraphExecDestroy(p.exec);
@@ -109,6 +130,11 @@ struct ag_model {
         for (auto &g : graphs) drop(g);
         for (auto &t : train_graphs) drop(t);
         if (loss_pinned) ag_host_free(loss_pinned);
+        for (int i = 0; i < 2; ++i) {
+            if (side[i]) ag_device_destroy(side[i]);
+            if (join_event[i]) cudaEventDestroy(join_event[i]);
+        }
+        if (fork_event) cudaEventDestroy(fork_event);
     }
 };
 
@@ -217,8 +243,83 @@ void build_model(ag_model *m, const ag_layer_spec *specs, int n, uint64_t seed) 
 // ≙ the derived Forward: input.forward(&self.f0)?...forward(&self.fN) (autograph_derive/src/lib.rs:291-340)
 // When no gradient is recorded (inference), a Relu and a MaxPool2 that follow a
 // Conv2, and a Relu that follows a Dense, are folded into the producing kernel.
+// The whole network as one kernel when it has the shape
+// (Conv2 [Relu] [MaxPool2]){1,2} Flatten (Dense [Relu]){1,4}, no gradient is
+// recorded and the kernel takes its sizes.  Returns false when the layers have to
+// run one by one.
+bool forward_whole_network(ag_model *m, const Variable &v, Variable *out) {
+    if (!m->whole_network || v.node || v.value.ndim() != 4 || !v.value.is_standard_layout())
+        return false;
+    const size_t n = m->layers.size();
+    size_t i = 0;
+    std::vector<ag_conv_stage> stages;
+    while (i < n) {
+        auto *conv = dynamic_cast<Conv2 *>(m->layers[i].get());
+        if (!conv) break;
+        if (conv->records_gradient(v)) return false;
+        ag_conv_stage st;
+        st.w = conv->weight.value.data();
+        st.bias = conv->has_bias ? conv->bias.value.data() : nullptr;
+        st.oc = conv->weight.value.dim(0);
+        st.options = to_c_options({conv->weight.value.dim(2), conv->weight.value.dim(3)},
+                                  conv->options);
+        st.relu = 0;
+        st.pool[0] = st.pool[1] = 0;
+        ++i;
+        if (i < n && dynamic_cast<Relu *>(m->layers[i].get())) {
+            st.relu = 1;
+            ++i;
+        }
+        if (i < n) {
+            if (auto *mp = dynamic_cast<MaxPool2 *>(m->layers[i].get())) {
+                if (mp->stride[0] != mp->filter[0] || mp->stride[1] != mp->filter[1]) return false;
+                st.pool[0] = mp->filter[0];
+                st.pool[1] = mp->filter[1];
+                ++i;
+            }
+        }
+        stages.push_back(st);
+    }
+    if (stages.empty() || i >= n || !dynamic_cast<Flatten *>(m->layers[i].get())) return false;
+    ++i;
+    std::vector<int64_t> dims;
+    std::vector<const void *> ws, bs;
+    std::vector<int32_t> relus;
+    while (i < n) {
+        auto *d = dynamic_cast<Dense *>(m->layers[i].get());
+        if (!d || d->weight.node || (d->has_bias && d->bias.node)) return false;
+        if (dims.empty()) dims.push_back(d->weight.value.dim(0));
+        if (d->weight.value.dim(0) != dims.back()) return false;
+        dims.push_back(d->weight.value.dim(1));
+        ws.push_back(d->weight.value.data());
+        bs.push_back(d->has_bias ? d->bias.value.data() : nullptr);
+        const bool r = i + 1 < n && dynamic_cast<Relu *>(m->layers[i + 1].get());
+        relus.push_back(r ? 1 : 0);
+        i += r ? 2 : 1;
+    }
+    if (ws.empty()) return false;
+    const Tensor &x = v.value;
+    if (x.dim(0) == 0) return false;
+    Tensor y = Tensor::uninit(m->pool, {x.dim(0), dims.back()}, x.dtype());
+    const int status = ag_conv_dense_chain_forward(
+        x.device(), x.dtype(), x.data(), x.dim(0), x.dim(1), x.dim(2), x.dim(3),
+        (int32_t)stages.size(), stages.data(), (int32_t)ws.size(), dims.data(), ws.data(),
+        bs.data(), relus.data(), y.data());
+    if (status == AG_ERR_UNSUPPORTED) {
+        m->whole_network = false;  // decided by the layer sizes: do not ask again
+        return false;
+    }
+    check(status);
+    *out = Variable{y, nullptr};
+    return true;
+}
+
 Variable forward_chain(ag_model *m, Variable v) {
     const size_t n = m->layers.size();
+    {
+        Variable whole;
+        if (forward_whole_network(m, v, &whole)) return whole;
+    }
     for (size_t i = 0; i < n; ++i) {
         Layer *l = m->layers[i].get();
         auto *relu1 = i + 1 < n ? dynamic_cast<Relu *>(m->layers[i + 1].get()) : nullptr;
@@ -255,7 +356,7 @@ Variable forward_chain(ag_model *m, Variable v) {
                         bs.push_back(d->has_bias ? d->bias.value.data() : nullptr);
                     }
                     Tensor y = Tensor::uninit(m->pool, {v.value.dim(0), dims.back()}, v.value.dtype());
-                    check(ag_dense_chain_forward(m->dev, v.value.dtype(), v.value.data(),
+                    check(ag_dense_chain_forward(v.value.device(), v.value.dtype(), v.value.data(),
                                                  v.value.dim(0), (int32_t)run.size(), dims.data(),
                                                  ws.data(), bs.data(), relus.data(), y.data()));
                     v = Variable{y, nullptr};
@@ -350,6 +451,39 @@ bool run_zero_copy(ag_model *m, GraphEntry *g, const void *x, void *out) {
         cuda_ok(cudaMemcpyAsync(out, y.value.data(), y.value.nbytes(), cudaMemcpyDeviceToHost,
                                 stream), "output copy");
     };
+    // The captured form: batch slices alternating between the two side streams.
+    // Every slice adds graph nodes and cross-stream dependencies (a few microseconds
+    // each), so only batches whose copy takes far longer than that are sliced.
+    const int want = m->slices > 0 ? m->slices : (g->bs >= 16384 ? 4 : 1);
+    const int64_t slices = (want > 1 && g->bs >= 64 * want && m->ensure_side_streams()) ? want : 1;
+    auto sliced_pass = [&]() {
+        if (slices == 1) return pass();
+        struct Restore {
+            Pool &p; ag_device *d;
+            ~Restore() { p.set_device(d); }
+        } restore{m->pool, m->dev};
+        const int64_t per = (g->bs + slices - 1) / slices;
+        const size_t image_bytes = (size_t)(g->c * g->h * g->w) * element_size(m->dtype);
+        cuda_ok(cudaEventRecord(m->fork_event, stream), "fork");
+        size_t out_off = 0;
+        for (int64_t s = 0, first = 0; first < g->bs; ++s, first += per) {
+            ag_device *d = m->side[s & 1];
+            cudaStream_t st = (cudaStream_t)ag_device_stream(d);
+            if (s < 2) cuda_ok(cudaStreamWaitEvent(st, m->fork_event, 0), "fork wait");
+            const int64_t n = std::min(per, g->bs - first);
+            m->pool.set_device(d);
+            Tensor xt = Tensor::external(d, (char *)x_dev + (size_t)first * image_bytes,
+                                         {n, g->c, g->h, g->w}, m->dtype);
+            Variable y = forward_chain(m, Variable{xt, nullptr});
+            cuda_ok(cudaMemcpyAsync((char *)out + out_off, y.value.data(), y.value.nbytes(),
+                                    cudaMemcpyDeviceToHost, st), "output copy");
+            out_off += y.value.nbytes();
+        }
+        for (int i = 0; i < 2; ++i) {
+            cuda_ok(cudaEventRecord(m->join_event[i], (cudaStream_t)ag_device_stream(m->side[i])), "join");
+            cuda_ok(cudaStreamWaitEvent(stream, m->join_event[i], 0), "join wait");
+        }
+    };
     if (++cp.seen < 2) {
         pass();
         return true;
@@ -359,7 +493,7 @@ bool run_zero_copy(ag_model *m, GraphEntry *g, const void *x, void *out) {
     bool ok = cudaStreamBeginCapture(stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
     if (ok) {
         try {
-            pass();
+            sliced_pass();
         } catch (...) {
             ok = false;
         }

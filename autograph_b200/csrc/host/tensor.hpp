@@ -62,6 +62,8 @@ class Pool {
             for (void *p : kv.second) ag_free(dev_, p);
     }
     ag_device *device() const { return dev_; }
+    // New tensors are bound to `dev` (another stream of the same GPU) from now on.
+    void set_device(ag_device *dev) { dev_ = dev; }
     void *acquire(size_t bytes, size_t *granted) {
         size_t cls = size_class(bytes);
         *granted = cls;

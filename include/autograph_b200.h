@@ -180,6 +180,35 @@ AG_API int ag_conv2_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const
                                            const ag_conv2_options *opt, int fuse_relu,
                                            int32_t pool_h, int32_t pool_w, void *y);
 
+/* One convolution stage of ag_conv_dense_chain_forward: y = max_pool2?(relu?(conv2(x, w) + bias)).
+ * pool = {0, 0} means no pool; otherwise the window, with stride = window. */
+typedef struct ag_conv_stage {
+    const void *w;            /* [oc, ic, fh, fw] */
+    const void *bias;         /* [oc] or NULL */
+    int64_t oc;
+    ag_conv2_options options;
+    int32_t relu;
+    int32_t pool[2];
+} ag_conv_stage;
+
+/* Inference fusion of a whole small network: n_conv stages of Conv2::forward -> Relu::forward ->
+ * MaxPool2::forward (layer.rs:1035-1047, 1254-1267, 1193-1216), Flatten::forward
+ * (layer.rs:1297-1309) and n_dense Dense::forward / Relu::forward pairs (layer.rs:1134-1143) --
+ * the derived Forward of the reference's LeNet5 (benches/neural-network-benches/src/
+ * autograph_backend.rs:129-146) -- as ONE kernel that keeps every activation in shared memory.
+ * x [bs, ic, ih, iw]; dense arguments as in ag_dense_chain_forward (dims[0] must equal the
+ * flattened size of the last stage); y [bs, dims[n_dense]].  Equals the layer-by-layer calls bit
+ * for bit.  Only networks that fit the kernel are taken (default convolution options, one 5x5 or
+ * 3x3 filter size, 2x2 pools, <= 16 input and <= 64 output channels per stage, dense layers with
+ * <= 2048 inputs and <= 256 outputs, 8 images of every activation within one CTA's shared
+ * memory); any other network returns AG_ERR_UNSUPPORTED without touching y, and the caller runs
+ * the layers one by one. */
+AG_API int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                       int64_t ic, int64_t ih, int64_t iw, int32_t n_conv,
+                                       const ag_conv_stage *stages, int32_t n_dense,
+                                       const int64_t *dims, const void *const *weights,
+                                       const void *const *biases, const int32_t *relu, void *y);
+
 /* dx = col2im(dy . Wmat): replaces the input edge of conv2_im2col
  * (layer.rs:976-988) = dot + kernels::col2im_conv2_<T> (src/tensor/ops.rs:1602-1667).
  * dy [bs,oc,oh,ow] (NCHW, as the autograd edge receives it), dx [bs,ic,ih,iw]. */

@@ -70,6 +70,8 @@ SHAPES = [
     # (bs, ic, ih, iw, oc, fh, fw)  -- LeNet5 and wide-stack layers at small batch
     (16, 1, 28, 28, 6, 5, 5), (16, 6, 12, 12, 16, 5, 5), (2, 3, 64, 64, 64, 3, 3),
     (2, 64, 31, 31, 128, 3, 3), (3, 5, 9, 11, 7, 3, 2),
+    # several images per CTA in the direct forward / backward kernels, ragged last group
+    (601, 6, 12, 12, 16, 5, 5), (303, 1, 28, 28, 6, 5, 5), (5, 2, 10, 8, 3, 3, 3),
 ]
 
 

@@ -97,6 +97,67 @@ def test_dense_chain_equals_separate_calls(dev, dtype, case):
     assert torch.equal(fused, h)
 
 
+NETS = [
+    # bs, (ic, ih, iw), conv stages [(oc, f, relu, pool)], dense widths after the flatten
+    (1000, (1, 28, 28), [(6, 5, True, (2, 2)), (16, 5, True, (2, 2))], [120, 84, 10]),   # LeNet5
+    (9, (1, 28, 28), [(6, 5, True, (2, 2)), (16, 5, True, (2, 2))], [120, 84, 10]),
+    (7, (1, 28, 28), [(6, 5, True, (2, 2)), (16, 5, True, (2, 2))], [120, 84, 10]),
+    (1, (1, 28, 28), [(6, 5, True, (2, 2)), (16, 5, True, (2, 2))], [120, 84, 10]),
+    (21, (3, 12, 14), [(5, 3, True, (2, 2))], [33, 7]),               # one 3x3 stage, odd widths
+    (18, (2, 10, 10), [(4, 3, False, None), (7, 3, True, (2, 2))], [10]),  # no pool, no relu
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("net", NETS)
+def test_conv_dense_chain_equals_separate_calls(dev, dtype, net):
+    """The one-kernel form of a small network gives the bits of the layer-by-layer calls."""
+    bs, (ic, ih, iw), convs, widths = net
+    rng = np.random.default_rng(77 + bs)
+    x = dev.tensor(_prep(rng.uniform(0, 1, (bs, ic, ih, iw)), dtype), dtype)
+    stages, c, h, w = [], ic, ih, iw
+    for oc, f, relu, pool in convs:
+        a = np.sqrt(2.0 / (c * f * f))
+        wt = dev.tensor(_prep(rng.uniform(-a, a, (oc, c, f, f)), dtype), dtype)
+        b = dev.tensor(_prep(rng.uniform(-a, a, oc), dtype), dtype)
+        stages.append((wt, b, relu, pool))
+        c, h, w = oc, h - f + 1, w - f + 1
+        if pool:
+            h, w = h // 2, w // 2
+    dims = [c * h * w] + widths
+    ws, bs_, relus = [], [], []
+    for i in range(len(dims) - 1):
+        a = np.sqrt(2.0 / dims[i])
+        ws.append(dev.tensor(_prep(rng.uniform(-a, a, (dims[i], dims[i + 1])), dtype), dtype))
+        bs_.append(dev.tensor(_prep(rng.uniform(-a, a, dims[i + 1]), dtype), dtype))
+        relus.append(i < len(dims) - 2)
+    fused = dev.conv_dense_chain_forward(x, stages, ws, bs_, relus)
+    v = x
+    for wt, b, relu, pool in stages:
+        v = dev.conv2_forward(v, wt, bias=b, relu=relu)
+        if pool:
+            v = dev.max_pool2(v, pool)
+    v = v.reshape(bs, -1)
+    for wd, b, r in zip(ws, bs_, relus):
+        v = dev.dense_forward(v, wd, bias=b, relu=r)
+    assert torch.equal(fused, v)
+
+
+def test_conv_dense_chain_unsupported(dev):
+    """Networks the one-kernel form does not take are refused, not approximated."""
+    import autograph_b200 as ag
+    x = dev.empty((4, 1, 28, 28), torch.float32)
+    w = dev.empty((6, 1, 4, 4), torch.float32)                       # 4x4 filter
+    d = dev.empty((6 * 25 * 25, 10), torch.float32)
+    with pytest.raises(ag.AgError) as e:
+        dev.conv_dense_chain_forward(x, [(w, None, True, None)], [d])
+    assert e.value.status == ag._capi.AG_ERR_UNSUPPORTED
+    w5 = dev.empty((6, 1, 5, 5), torch.float32)
+    wide = dev.empty((6 * 12 * 12, 4096), torch.float32)              # dense layer too wide
+    with pytest.raises(ag.AgError):
+        dev.conv_dense_chain_forward(x, [(w5, None, True, (2, 2))], [wide])
+
+
 def test_fused_errors(dev):
     import autograph_b200 as ag
     x = dev.empty((2, 1, 6, 6), torch.float32)
