@@ -64,6 +64,8 @@ struct ag_device {
     std::recursive_mutex mu;
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
+    void *staging = nullptr;        // second scratch block: operand re-layouts of the
+    size_t staging_bytes = 0;       // tensor-core convolution (may be live next to workspace)
     int *status_dev = nullptr;      // device word: 0 = ok, else a timeout code
     int *status_host = nullptr;     // pinned mirror
     float *scalar_dev = nullptr;    // small device buffer for loss / accuracy sums (64 B)
@@ -92,6 +94,8 @@ class DeviceGuard {
 
 // Returns a workspace of at least `bytes` (grown on demand; growth synchronises).
 int workspace(ag_device *dev, size_t bytes, void **out);
+// The same for the second scratch block.
+int staging(ag_device *dev, size_t bytes, void **out);
 
 inline size_t dtype_size(ag_dtype t) {
     switch (t) {

@@ -2,6 +2,7 @@
 // backward-weight on the SIMT tile engine (the patch matrix is never written to
 // memory), plus the stand-alone im2col / col2im kernels.
 #include "conv2_direct.cuh"
+#include "conv_tc.cuh"
 #include "gemm_simt_launch.cuh"
 
 namespace ag {
@@ -286,6 +287,10 @@ int ag_conv2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, 
     AG_REQUIRE(oc >= 0 && oc < (1 << 30), AG_ERR_SHAPE, "bad output channel count");
     if (bs == 0 || oc == 0) return AG_OK;
     AG_REQUIRE(x && w && y, AG_ERR_INVALID, "null tensor pointer");
+    if (dtype == AG_BF16 && convtc::eligible_forward(bs, ic, ih, iw, oc, opt))
+        return convtc::forward(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw,
+                               (const __nv_bfloat16 *)w, oc, (const __nv_bfloat16 *)bias, opt,
+                               fuse_relu != 0, (__nv_bfloat16 *)y);
     if (direct::eligible(bs, ic, ih, iw, oc, opt)) {
         if (dtype == AG_F32)
             return direct::forward<float>(dev, (const float *)x, bs, ic, ih, iw, (const float *)w,
@@ -348,6 +353,10 @@ int ag_conv2_backward_input(ag_device *dev, ag_dtype dtype, const void *w, int64
                "bad output channel count");
     if (bs == 0 || ic == 0) return AG_OK;
     AG_REQUIRE(w && dy && dx, AG_ERR_INVALID, "null tensor pointer");
+    if (dtype == AG_BF16 && convtc::eligible_backward_input(bs, ic, ih, iw, oc, opt))
+        return convtc::backward_input(dev, (const __nv_bfloat16 *)w, oc, ic,
+                                      (const __nv_bfloat16 *)dy, bs, ih, iw, opt,
+                                      (__nv_bfloat16 *)dx);
     if (direct::eligible_backward_input(bs, ic, ih, iw, oc, opt)) {
         if (dtype == AG_F32)
             return direct::backward_input<float>(dev, (const float *)w, oc, ic, (const float *)dy,
@@ -373,6 +382,10 @@ int ag_conv2_backward_weight(ag_device *dev, ag_dtype dtype, const void *x, int6
     AG_REQUIRE(oc >= 0 && oc < (1 << 30), AG_ERR_SHAPE, "bad output channel count");
     if (oc == 0 || ic == 0) return AG_OK;
     AG_REQUIRE(dw && (bs == 0 || (x && dy)), AG_ERR_INVALID, "null tensor pointer");
+    if (dtype == AG_BF16 && convtc::eligible_backward_weight(bs, ic, ih, iw, oc, opt))
+        return convtc::backward_weight(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw,
+                                       (const __nv_bfloat16 *)dy, oc, opt, beta,
+                                       (__nv_bfloat16 *)dw);
     if (direct::eligible_backward_weight(bs, ic, ih, iw, oc, opt)) {
         if (dtype == AG_F32)
             return direct::backward_weight<float>(dev, (const float *)x, bs, ic, ih, iw,

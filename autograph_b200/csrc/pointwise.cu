@@ -4,6 +4,8 @@
 // the SM count.  Arithmetic is written with explicit round-to-nearest multiply
 // and add (no fused multiply-add) so that results are bit-identical to the
 // reference's host code, which does not contract.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace ag {
@@ -235,6 +237,63 @@ __global__ void max_pool2_backward_2x2_kernel(T *__restrict__ dx, const T *__res
     }
 }
 
+// Any non-overlapping window, any width: a CTA stages a run of whole planes in
+// shared memory with 16-byte loads (the staged copy keeps the alignment of the
+// global run), works on the windows there, and writes the run back with 16-byte
+// stores, so the 2- and 4-byte window accesses never reach global memory.
+template <class T>
+__global__ void max_pool2_backward_staged_kernel(T *__restrict__ dx, const T *__restrict__ dy,
+                                                 int64_t planes, int ih, int iw, int oh, int ow,
+                                                 int h, int w, int sh, int sw, int per_cta) {
+    extern __shared__ __align__(16) unsigned char staged_raw[];
+    T *s = reinterpret_cast<T *>(staged_raw);
+    constexpr int V = 16 / (int)sizeof(T);
+    const int plane_len = ih * iw;
+    for (int64_t p0 = (int64_t)blockIdx.x * per_cta; p0 < planes;
+         p0 += (int64_t)gridDim.x * per_cta) {
+        const int np = (int)min((int64_t)per_cta, planes - p0);
+        const int n = np * plane_len;
+        T *base = dx + p0 * plane_len;
+        const int shift = (int)((reinterpret_cast<uintptr_t>(base) & 15) / sizeof(T));
+        const int head = min(n, (V - shift) % V);
+        const int nv = (n - head) / V;
+        const int tail0 = head + nv * V;
+        for (int i = threadIdx.x; i < head; i += blockDim.x) s[shift + i] = base[i];
+        for (int v = threadIdx.x; v < nv; v += blockDim.x)
+            *reinterpret_cast<uint4 *>(s + shift + head + v * V) =
+                *reinterpret_cast<const uint4 *>(base + head + v * V);
+        for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) s[shift + i] = base[i];
+        __syncthreads();
+        const int windows = np * oh * ow;
+        const T *g = dy + p0 * oh * ow;
+        for (int i = threadIdx.x; i < windows; i += blockDim.x) {
+            const int wid = i % ow;
+            const int t = i / ow;
+            const int hid = t % oh, plane = t / oh;
+            T *win = s + shift + plane * plane_len + hid * sh * iw + wid * sw;
+            float m = 0.f;
+            int am = 0;
+            for (int fi = 0; fi < h; ++fi)
+                for (int fj = 0; fj < w; ++fj) {
+                    const float v = to_f32(win[fi * iw + fj]);
+                    if ((fi == 0 && fj == 0) || v > m) {
+                        m = v;
+                        am = fi * iw + fj;
+                    }
+                    win[fi * iw + fj] = from_f32<T>(0.f);
+                }
+            win[am] = from_f32<T>(__fadd_rn(0.f, to_f32(g[i])));
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < head; i += blockDim.x) base[i] = s[shift + i];
+        for (int v = threadIdx.x; v < nv; v += blockDim.x)
+            *reinterpret_cast<uint4 *>(base + head + v * V) =
+                *reinterpret_cast<const uint4 *>(s + shift + head + v * V);
+        for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) base[i] = s[shift + i];
+        __syncthreads();
+    }
+}
+
 // ---- bias ---------------------------------------------------------------------
 template <class T>
 __global__ void bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias, int64_t total,
@@ -455,6 +514,21 @@ int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, 
         AG_DISPATCH_FLOAT(dtype, T,
             max_pool2_backward_2x2_kernel<T><<<grid2, threads, 0, dev->stream>>>(
                 (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow););
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
+    const int64_t plane_bytes = ih * iw * (int64_t)dtype_size(dtype);
+    if (plane_bytes <= 40 * 1024) {
+        // a run of whole planes per CTA, about four CTAs per SM
+        int per_cta = (int)((40 * 1024) / plane_bytes);
+        const int64_t spread = ceil_div(planes, (int64_t)dev->sm_count * 4);
+        if (per_cta > spread) per_cta = (int)(spread < 1 ? 1 : spread);
+        const size_t smem = (size_t)per_cta * (size_t)plane_bytes + 16;
+        const unsigned gridp = (unsigned)std::min<int64_t>(ceil_div(planes, per_cta),
+                                                           (int64_t)dev->sm_count * 8);
+        AG_DISPATCH_FLOAT(dtype, T,
+            max_pool2_backward_staged_kernel<T><<<gridp, threads, smem, dev->stream>>>(
+                (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow, h, w, sh, sw, per_cta););
         AG_CHECK_LAUNCH();
         return AG_OK;
     }

@@ -40,6 +40,20 @@ int workspace(ag_device *dev, size_t bytes, void **out) {
     return AG_OK;
 }
 
+int staging(ag_device *dev, size_t bytes, void **out) {
+    if (bytes > dev->staging_bytes) {
+        AG_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+        if (dev->staging) AG_CUDA_TRY(cudaFree(dev->staging));
+        dev->staging = nullptr;
+        dev->staging_bytes = 0;
+        size_t want = bytes + bytes / 4;
+        AG_CUDA_TRY(cudaMalloc(&dev->staging, want));
+        dev->staging_bytes = want;
+    }
+    *out = dev->staging;
+    return AG_OK;
+}
+
 static int device_init(int ordinal, cudaStream_t stream, bool owns, ag_device **out) {
     AG_REQUIRE(out != nullptr, AG_ERR_INVALID, "out is null");
     int count = 0;
@@ -112,6 +126,7 @@ int ag_device_destroy(ag_device *dev) {
     cudaSetDevice(dev->ordinal);
     if (dev->stream) cudaStreamSynchronize(dev->stream);
     if (dev->workspace) cudaFree(dev->workspace);
+    if (dev->staging) cudaFree(dev->staging);
     if (dev->status_dev) cudaFree(dev->status_dev);
     if (dev->scalar_dev) cudaFree(dev->scalar_dev);
     if (dev->status_host) cudaFreeHost(dev->status_host);

@@ -467,6 +467,8 @@ def extras(torch, ag, dev, peaks, world):
 def run_probe(args):
     """Runs one kernel family alone, for profiler captures:
     gemm:<f32|bf16>:<n>:<nn|tn|nt|tt>, infer:<f32|bf16>:<batch>, train:<f32|bf16>:<batch>,
+    wide:<f32|bf16>:<batch> (training step of the wider conv stack), conv:bf16:<batch>
+    (its second convolution alone: forward and input gradient),
     op:<f32|bf16>:<relu|relu_backward|scaled_add|sgd_momentum|max_pool2|max_pool2_backward|
     bias_grad>:<elements>."""
     import torch
@@ -518,6 +520,23 @@ def run_probe(args):
         bv = b.t() if layout[1] == "t" else b
         fn = lambda i: dev.gemm(1.0, av, bv, 0.0, c)
         work, unit = 2.0 * n ** 3 * 1e-12, "TFLOP/s"
+    elif parts[0] == "conv":
+        bs = int(parts[2])
+        x = torch.randn((bs, 64, 31, 31), device=dev.torch_device).to(dtype)
+        w = (torch.rand((128, 64, 3, 3), device=dev.torch_device) * 0.1 - 0.05).to(dtype)
+        bias = torch.zeros((128,), device=dev.torch_device).to(dtype)
+        dy = torch.randn((bs, 128, 29, 29), device=dev.torch_device).to(dtype)
+        def fn(i):
+            dev.conv2_forward(x, w, bias=bias, relu=True)
+            dev.conv2_backward_input(w, dy, (31, 31))
+        work, unit = 2 * 2.0 * bs * 128 * 29 * 29 * 64 * 9 * 1e-12, "TFLOP/s"
+    elif parts[0] == "wide":
+        bs = int(parts[2])
+        model = ag.Model(dev, ag.WIDE_STACK_SPEC, dtype, seed=2000)
+        xh = torch.randn((bs, 3, 64, 64)).to(dtype).pin_memory()
+        th = torch.randint(0, 10, (bs,), dtype=torch.uint8).pin_memory()
+        fn = lambda i: model.train_step(xh, th, 0.01)
+        work, unit = float(bs), "img/s"
     else:
         bs = int(parts[2])
         model = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=2000)
