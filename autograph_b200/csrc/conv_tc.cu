@@ -15,9 +15,11 @@
 //
 // Warp roles are those of the GEMM kernel (gemm_tc.cu): warp 0 issues TMA, warp
 // 1 issues tcgen05.mma into one of two TMEM accumulators, warps 2..5 drain the
-// other accumulator: bias, ReLU, bf16 rounding and NCHW stores (a warp's 32
-// lanes are 32 consecutive pixels of a row, so each store instruction writes
-// one run of an output channel plane).
+// other accumulator: bias, ReLU, bf16 rounding and 16-byte stores of channels-last
+// rows (a thread owns one pixel, 32 channels are 64 contiguous bytes).  A last
+// kernel turns the channels-last result into the caller's NCHW tensor through
+// shared memory, again with 16-byte accesses on both sides: scattering 2-byte
+// NCHW stores straight from the epilogue cost more than the whole main loop.
 //
 // The gradient with respect to the input is the same kernel on the transposed
 // problem: dy as the activation, zero border F-1-p, filter bank repacked with
@@ -48,14 +50,14 @@ struct Cfg {
 };
 
 struct Params {
-    int B, OH, OW, OC;       // output geometry
+    int B, OH, OW, OC, OCp;  // output geometry; OCp = OC rounded up to a multiple of 64
     int TW, tw_shift;        // pixel tile: TH x TW = 128, TW = 1 << tw_shift
     int tiles_y, tiles_x, n_blocks;
     int FH, FW, CB;          // filter taps; channel blocks of 64
     int pad_h, pad_w;
     const __nv_bfloat16 *bias;  // [OC] or null
     int relu;
-    __nv_bfloat16 *y;        // NCHW [B][OC][OH][OW]
+    __nv_bfloat16 *y;        // channels-last [B][OH][OW][OCp]
     int *status;
 };
 
@@ -213,7 +215,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int quarter = warp % 4;  // TMEM lanes this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
-        const int64_t plane = (int64_t)p.OH * p.OW;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const TileCoord t = tile_coord(tile, p);
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag)) {
@@ -227,26 +228,37 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const bool valid = oy < p.OH && ox < p.OW;
             const uint32_t taddr =
                 tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N);
-            __nv_bfloat16 *dst = p.y + ((int64_t)t.b * p.OC) * plane + (int64_t)oy * p.OW + ox;
+            // channels-last row of this pixel: 32 channels = 64 contiguous, 16-byte aligned bytes
+            __nv_bfloat16 *dst = p.y + (((int64_t)t.b * p.OH + oy) * p.OW + ox) * p.OCp;
 #pragma unroll 1
             for (int chunk = 0; chunk < BLOCK_N / 32; ++chunk) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + chunk * 32, r);
                 tmem_ld_wait();
                 const int oc0 = t.n_blk * BLOCK_N + chunk * 32;
-                if (valid && oc0 < p.OC) {
+                if (valid && oc0 < p.OCp) {
+                    uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int oc = oc0 + j;
-                        if (oc < p.OC) {
-                            float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
-                            if (p.bias != nullptr)
-                                v = __bfloat162float(
-                                    __float2bfloat16_rn(v + __bfloat162float(p.bias[oc])));
-                            if (p.relu) v = v >= 0.f ? v : 0.f;
-                            dst[(int64_t)oc * plane] = __float2bfloat16_rn(v);
+                    for (int j = 0; j < 32; j += 2) {
+                        float v[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int oc = oc0 + j + e;
+                            float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j + e])));
+                            if (p.bias != nullptr && oc < p.OC)
+                                x = __bfloat162float(
+                                    __float2bfloat16_rn(x + __bfloat162float(p.bias[oc])));
+                            if (p.relu) x = x >= 0.f ? x : 0.f;
+                            v[e] = x;
                         }
+                        __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
+                        packed[j / 2] = *reinterpret_cast<uint32_t *>(&h);
                     }
+                    uint4 *d4 = reinterpret_cast<uint4 *>(dst + oc0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        d4[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
+                                           packed[4 * q + 3]);
                 }
             }
             tc_fence_before();
@@ -274,26 +286,77 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
 // ------------------------------------------------------- layout conversions
 // x [B][C][HW] -> out [B][HW][Cp] (Cp a multiple of 64, channels >= C are zero).
-// grid (ceil(HW / 32), B), 256 threads.
+// A thread owns 16 channels of one pixel: 16 independent 2-byte loads, each
+// coalesced across the warp (lanes are consecutive pixels of one channel plane),
+// then one full 32-byte sector of the channels-last copy.  No shared memory.
+// grid (ceil(HW / 256), Cp / 16, B), 256 threads.
 __global__ void __launch_bounds__(256)
     nchw_to_nhwc_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ out, int C,
                         int HW, int Cp) {
-    __shared__ __nv_bfloat16 tile[64][34];
-    const int p0 = blockIdx.x * 32;
-    const int b = blockIdx.y;
-    const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
-    for (int cb = 0; cb < Cp; cb += 64) {
-        for (int i = threadIdx.x; i < 64 * 32; i += 256) {
-            const int c = i >> 5, px = i & 31;
-            const bool in = (cb + c) < C && (p0 + px) < HW;
-            tile[c][px] = in ? x[((int64_t)b * C + cb + c) * HW + p0 + px] : zero;
+    const int px = blockIdx.x * 256 + threadIdx.x;
+    if (px >= HW) return;
+    const int c0 = blockIdx.y * 16;
+    const int b = blockIdx.z;
+    const unsigned short *src =
+        reinterpret_cast<const unsigned short *>(x) + ((int64_t)b * C + c0) * HW + px;
+    unsigned short v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = (c0 + j < C) ? src[(int64_t)j * HW] : (unsigned short)0;
+    uint4 lo, hi;
+    lo.x = v[0] | ((uint32_t)v[1] << 16);   lo.y = v[2] | ((uint32_t)v[3] << 16);
+    lo.z = v[4] | ((uint32_t)v[5] << 16);   lo.w = v[6] | ((uint32_t)v[7] << 16);
+    hi.x = v[8] | ((uint32_t)v[9] << 16);   hi.y = v[10] | ((uint32_t)v[11] << 16);
+    hi.z = v[12] | ((uint32_t)v[13] << 16); hi.w = v[14] | ((uint32_t)v[15] << 16);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + ((int64_t)b * HW + px) * Cp + c0);
+    dst[0] = lo;
+    dst[1] = hi;
+}
+
+// in [B][HW][Cp] -> out [B][C][HW].  A CTA takes 16 channels of up to 1024 pixels
+// of one image: 32-byte loads (lanes are consecutive pixels), a transposed copy
+// in shared memory whose rows start at the same offset modulo 8 elements as the
+// runs they are written to, then 16-byte stores of whole runs (2-byte stores only
+// at ragged ends).  grid (ceil(HW / 1024), ceil(C / 16), B), 256 threads.
+constexpr int NCHW_PIX = 1024;
+constexpr int NCHW_PITCH = NCHW_PIX + 16;
+__global__ void __launch_bounds__(256)
+    nhwc_to_nchw_kernel(const __nv_bfloat16 *__restrict__ in, __nv_bfloat16 *__restrict__ out, int C,
+                        int HW, int Cp) {
+    __shared__ __align__(16) unsigned short tile[16 * NCHW_PITCH];
+    const int p0 = blockIdx.x * NCHW_PIX;
+    const int c0 = blockIdx.y * 16;
+    const int b = blockIdx.z;
+    const int np = min(NCHW_PIX, HW - p0);
+    const int nc = min(16, C - c0);
+    // a staged row starts at the same offset modulo 8 elements (16 bytes) as its run in out
+    const int64_t run0 = ((int64_t)b * C + c0) * HW + p0;
+    for (int px = threadIdx.x; px < np; px += 256) {
+        const uint4 *src =
+            reinterpret_cast<const uint4 *>(in + ((int64_t)b * HW + p0 + px) * Cp + c0);
+        const uint4 lo = src[0], hi = src[1];
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int off = (int)((reinterpret_cast<uintptr_t>(out + run0 + (int64_t)j * HW) >> 1) & 7);
+            tile[j * NCHW_PITCH + off + px] =
+                (unsigned short)((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu));
         }
-        __syncthreads();
-        for (int i = threadIdx.x; i < 32 * 64; i += 256) {
-            const int px = i >> 6, c = i & 63;
-            if (p0 + px < HW) out[((int64_t)b * HW + p0 + px) * Cp + cb + c] = tile[c][px];
-        }
-        __syncthreads();
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int j = warp; j < nc; j += 8) {
+        const int64_t start = run0 + (int64_t)j * HW;  // element index of the run in out
+        const int off = (int)((reinterpret_cast<uintptr_t>(out + start) >> 1) & 7);
+        const unsigned short *row = tile + j * NCHW_PITCH;   // row[off + i] = element i of the run
+        unsigned short *dst = reinterpret_cast<unsigned short *>(out) + start;
+        const int head = min(np, (8 - off) & 7);
+        const int nvec = (np - head) / 8;
+        if (lane < head) dst[lane] = row[off + lane];
+        for (int v = lane; v < nvec; v += 32)
+            *reinterpret_cast<uint4 *>(dst + head + v * 8) =
+                *reinterpret_cast<const uint4 *>(row + off + head + v * 8);
+        const int tail0 = head + nvec * 8;
+        if (tail0 + lane < np) dst[tail0 + lane] = row[off + tail0 + lane];
     }
 }
 
@@ -337,8 +400,8 @@ static int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 int to_nhwc(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64_t hw, int64_t cp,
             __nv_bfloat16 *out) {
-    nchw_to_nhwc_kernel<<<dim3((unsigned)ceil_div(hw, 32), (unsigned)bs), 256, 0, dev->stream>>>(
-        x, out, (int)c, (int)hw, (int)cp);
+    nchw_to_nhwc_kernel<<<dim3((unsigned)ceil_div(hw, 256), (unsigned)(cp / 16), (unsigned)bs), 256,
+                          0, dev->stream>>>(x, out, (int)c, (int)hw, (int)cp);
     AG_CHECK_LAUNCH();
     return AG_OK;
 }
@@ -348,10 +411,10 @@ int to_nhwc(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64
 static bool shape_ok(int64_t bs, int64_t c_in, int64_t in_h, int64_t in_w, int64_t c_out,
                      int64_t out_h, int64_t out_w, int fh, int fw) {
     if (!tc_conv_enabled() || encode_tiled_fn() == nullptr) return false;
-    if (bs <= 0 || c_in < 32 || c_out < 32 || out_h <= 0 || out_w <= 0) return false;
+    if (bs <= 0 || c_in < 1 || c_out < 32 || out_h <= 0 || out_w <= 0) return false;
     if (fh < 1 || fw < 1 || fh * fw > 49) return false;
     if (bs * out_h * out_w < 4096) return false;  // too little work for 128-pixel tiles
-    if (in_h > 32768 || in_w > 32768 || bs > 65535 * 16) return false;
+    if (in_h > 32768 || in_w > 32768 || bs > 65535) return false;
     const int64_t cp = round_up(c_in, 64);
     if (bs * in_h * in_w * cp >= (int64_t(1) << 40)) return false;
     if (c_out * (int64_t)fh * fw * cp >= (int64_t(1) << 31)) return false;
@@ -405,10 +468,14 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
     const int taps = fh * fw;
     const int64_t act_bytes = round_up(bs * in_h * in_w * cp * 2, 1024);
     const int64_t wk_elems = c_out * taps * cp;
+    const int64_t wk_bytes = round_up(wk_elems * 2, 1024);
+    const int64_t ocp = round_up(c_out, 64);
+    const int64_t out_bytes = bs * out_h * out_w * ocp * 2;
     void *ws = nullptr;
-    AG_TRY(staging(dev, (size_t)(act_bytes + wk_elems * 2), &ws));
+    AG_TRY(staging(dev, (size_t)(act_bytes + wk_bytes + out_bytes), &ws));
     __nv_bfloat16 *act_nhwc = (__nv_bfloat16 *)ws;
     __nv_bfloat16 *wk = (__nv_bfloat16 *)((char *)ws + act_bytes);
+    __nv_bfloat16 *out_nhwc = (__nv_bfloat16 *)((char *)ws + act_bytes + wk_bytes);
 
     AG_TRY(to_nhwc(dev, act, bs, c_in, in_h * in_w, cp, act_nhwc));
     const unsigned rgrid = (unsigned)ceil_div(wk_elems, 256);
@@ -426,13 +493,14 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
     for (int shift = 3; shift <= 7; ++shift) {
         const int64_t tw = 1 << shift, th = BLOCK_M / tw;
         const int64_t cover = round_up(out_w, tw) * round_up(out_h, th);
-        if (best_cover < 0 || cover < best_cover) {
+        if (best_cover < 0 || cover <= best_cover) {  // ties: the wider tile (longer store runs)
             best_cover = cover;
             best_shift = shift;
         }
     }
     Params p;
     p.B = (int)bs; p.OH = (int)out_h; p.OW = (int)out_w; p.OC = (int)c_out;
+    p.OCp = (int)ocp;
     p.tw_shift = best_shift;
     p.TW = 1 << best_shift;
     const int th = BLOCK_M / p.TW;
@@ -443,7 +511,7 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
     p.pad_h = pad_h; p.pad_w = pad_w;
     p.bias = bias;
     p.relu = relu ? 1 : 0;
-    p.y = y;
+    p.y = out_nhwc;
     p.status = dev->status_dev;
     const int block_n = c_out <= 64 ? 64 : (c_out <= 128 ? 128 : 256);
     p.n_blocks = (int)ceil_div(c_out, block_n);
@@ -462,9 +530,18 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
         const uint32_t box[2] = {64, (uint32_t)block_n};
         AG_TRY(make_tmap_bf16(&tw, wk, 2, dims, strides, box));
     }
-    if (block_n == 64) return launch<64>(dev, tx, tw, p);
-    if (block_n == 128) return launch<128>(dev, tx, tw, p);
-    return launch<256>(dev, tx, tw, p);
+    if (block_n == 64)
+        AG_TRY(launch<64>(dev, tx, tw, p));
+    else if (block_n == 128)
+        AG_TRY(launch<128>(dev, tx, tw, p));
+    else
+        AG_TRY(launch<256>(dev, tx, tw, p));
+    const int64_t out_hw = out_h * out_w;
+    nhwc_to_nchw_kernel<<<dim3((unsigned)ceil_div(out_hw, NCHW_PIX), (unsigned)ceil_div(c_out, 16),
+                               (unsigned)bs),
+                          256, 0, dev->stream>>>(out_nhwc, y, (int)c_out, (int)out_hw, (int)ocp);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
 }
 
 int forward(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw,

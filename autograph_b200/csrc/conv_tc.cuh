@@ -7,7 +7,7 @@ namespace ag {
 namespace convtc {
 
 // True when the tensor-core kernel takes the problem: stride 1, dilation 1, at
-// least 32 input and 32 output channels in the kernel's view, at least 4096
+// least 32 output channels in the kernel's view (few input channels are zero-padded to 64), at least 4096
 // output pixels.  Any padding up to filter - 1 is handled by the zero fill of
 // out-of-range TMA coordinates.
 bool eligible_forward(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int64_t oc,

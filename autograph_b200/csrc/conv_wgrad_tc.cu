@@ -264,7 +264,7 @@ bool eligible_backward_weight(int64_t bs, int64_t ic, int64_t ih, int64_t iw, in
     if (bs <= 0 || ic <= 0 || oc < 32 || oh <= 0 || ow <= 0) return false;
     if (fw < 1 || fw > 8 || fh < 1 || fh > 8) return false;
     if (bs * oh * ow < 4096) return false;
-    if (ih > 32768 || iw > 32768 || bs > 65535 * 16) return false;
+    if (ih > 32768 || iw > 32768 || bs > 65535) return false;
     const int64_t cp = round_up64(ic, 64), ocp = round_up64(oc, 64);
     if (bs * ih * iw * cp >= (int64_t(1) << 40) || bs * oh * ow * ocp >= (int64_t(1) << 40))
         return false;
@@ -295,7 +295,7 @@ int backward_weight(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t 
     for (int shift = 3; shift <= 6; ++shift) {
         const int64_t tw = 1 << shift, th = WG_CHUNK / tw;
         const int64_t cover = round_up64(ow, tw) * round_up64(oh, th);
-        if (best_cover < 0 || cover < best_cover) {
+        if (best_cover < 0 || cover <= best_cover) {  // ties: the wider chunk
             best_cover = cover;
             best_shift = shift;
         }

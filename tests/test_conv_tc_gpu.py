@@ -16,6 +16,7 @@ SHAPES = [
     (4, 64, 40, 40, 300, 3, 1),      # two 256-wide output-channel blocks, the second ragged
     (5, 96, 14, 150, 64, 3, 0),      # wide rows: 1 x 128 pixel tiles, two channel blocks
     (70, 128, 9, 9, 64, 3, 1),       # small images: 8 x 16 tiles hanging over both edges
+    (3, 3, 64, 64, 64, 3, 0),        # the wide stack's first layer: 3 channels padded to 64
 ]
 
 
