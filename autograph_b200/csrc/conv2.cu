@@ -324,7 +324,10 @@ int ag_conv2_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const void *
                g.oh, g.ow);
     if (bs == 0 || oc == 0) return AG_OK;
     AG_REQUIRE(x && w && y, AG_ERR_INVALID, "null tensor pointer");
-    if (pool_h == 2 && pool_w == 2 && direct::eligible(bs, ic, ih, iw, oc, opt)) {
+    // Same engine as ag_conv2_forward would pick, so that the fused call equals the
+    // separate calls bit for bit.
+    const bool tensor_core = dtype == AG_BF16 && convtc::eligible_forward(bs, ic, ih, iw, oc, opt);
+    if (!tensor_core && pool_h == 2 && pool_w == 2 && direct::eligible(bs, ic, ih, iw, oc, opt)) {
         if (dtype == AG_F32)
             return direct::forward<float>(dev, (const float *)x, bs, ic, ih, iw, (const float *)w,
                                           oc, (const float *)bias, opt, fuse_relu != 0, true,

@@ -107,14 +107,35 @@ __device__ __forceinline__ void compute_items(const float *s_img, const float *s
                 for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
 
         const float *img = s_img + g * img_elems + y0 * p.iw + x0;
+        // Rows whose length is a multiple of four floats keep every patch row 16-byte
+        // aligned (x0 is a multiple of four): two or three 16-byte loads per row.  A block
+        // at the right edge may then read a few floats past its row (the next row, or the
+        // buffer that follows the images); only outputs that are dropped use them.
+        const bool vec_rows = (p.iw & 3) == 0;
         for (int ci = 0; ci < p.ic; ++ci) {
-            float patch[FH + PBH - 1][FW + PBW - 1];
+            constexpr int PW = FW + PBW - 1;
+            float patch[FH + PBH - 1][PW];
             const float *pi = img + ci * p.ih * p.iw;
+            if (vec_rows) {
 #pragma unroll
-            for (int a = 0; a < FH + PBH - 1; ++a) {
-                const float *prow = pi + a * p.iw;
+                for (int a = 0; a < FH + PBH - 1; ++a) {
+                    const float4 *prow = reinterpret_cast<const float4 *>(pi + a * p.iw);
 #pragma unroll
-                for (int b = 0; b < FW + PBW - 1; ++b) patch[a][b] = prow[min(b, col_max)];
+                    for (int q = 0; q < (PW + 3) / 4; ++q) {
+                        const float4 v = prow[q];
+                        if (4 * q + 0 < PW) patch[a][4 * q + 0] = v.x;
+                        if (4 * q + 1 < PW) patch[a][4 * q + 1] = v.y;
+                        if (4 * q + 2 < PW) patch[a][4 * q + 2] = v.z;
+                        if (4 * q + 3 < PW) patch[a][4 * q + 3] = v.w;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int a = 0; a < FH + PBH - 1; ++a) {
+                    const float *prow = pi + a * p.iw;
+#pragma unroll
+                    for (int b = 0; b < PW; ++b) patch[a][b] = prow[min(b, col_max)];
+                }
             }
             const float *wc = s_w + ci * FH * FW * p.ocp + oc0;
 #pragma unroll

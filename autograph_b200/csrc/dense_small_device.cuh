@@ -54,6 +54,17 @@ inline size_t plan_chain(ChainParams *p, int m, int n_layers, const ChainLayer *
     return (size_t)2 * p->max_k * ROWS + (size_t)p->red_floats;
 }
 
+__device__ __forceinline__ void load2_to_f32(const float *p, float &a, float &b) {
+    const float2 v = *reinterpret_cast<const float2 *>(p);
+    a = v.x;
+    b = v.y;
+}
+__device__ __forceinline__ void load2_to_f32(const __nv_bfloat16 *p, float &a, float &b) {
+    const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+    a = __uint_as_float(v << 16);
+    b = __uint_as_float(v & 0xffff0000u);
+}
+
 // Runs every layer of the chain for the ROWS rows whose first-layer input is in
 // xa as [k][ROWS] (f32).  xb is the second activation buffer, red the
 // [slices][ROWS][np] scratch.  The plan's (column, k slice) pairs are spread over
@@ -67,27 +78,65 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
         const ChainStep st = p.s[l];
         const T *w = reinterpret_cast<const T *>(st.w);
         const T *bias = reinterpret_cast<const T *>(st.bias);
-        for (int vt = threadIdx.x; vt < st.np * st.slices; vt += blockDim.x) {
-            const int n = vt % st.np, slice = vt / st.np;
-            float acc[ROWS];
+        // Two adjacent output columns per (column, k slice) work item when the weight rows
+        // allow an aligned two-element load: twice the FFMAs per load instruction.  The sum
+        // for every output is the same either way (same k slices, same order).
+        const bool pairs = (st.N % 2 == 0) &&
+                           (reinterpret_cast<uintptr_t>(w) % (2 * sizeof(T)) == 0);
+        if (pairs) {
+            const int half = st.np / 2;
+            for (int vt = threadIdx.x; vt < half * st.slices; vt += blockDim.x) {
+                const int n = 2 * (vt % half), slice = vt / half;
+                float acc0[ROWS], acc1[ROWS];
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-            if (n < st.N) {
-                const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
-                const T *wp = w + (int64_t)k0 * st.N + n;
-#pragma unroll 8
-                for (int k = k0; k < k1; ++k, wp += st.N) {
-                    const float wv = to_f32(*wp);
-                    const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
-                    const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
-                    acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
-                    acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
-                    acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
-                    acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
+                for (int r = 0; r < ROWS; ++r) acc0[r] = acc1[r] = 0.f;
+                if (n < st.N) {
+                    const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
+                    const T *wp = w + (int64_t)k0 * st.N + n;
+#pragma unroll 4
+                    for (int k = k0; k < k1; ++k, wp += st.N) {
+                        float w0, w1;
+                        load2_to_f32(wp, w0, w1);
+                        const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
+                        const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
+                        acc0[0] = fmaf(a.x, w0, acc0[0]); acc1[0] = fmaf(a.x, w1, acc1[0]);
+                        acc0[1] = fmaf(a.y, w0, acc0[1]); acc1[1] = fmaf(a.y, w1, acc1[1]);
+                        acc0[2] = fmaf(a.z, w0, acc0[2]); acc1[2] = fmaf(a.z, w1, acc1[2]);
+                        acc0[3] = fmaf(a.w, w0, acc0[3]); acc1[3] = fmaf(a.w, w1, acc1[3]);
+                        acc0[4] = fmaf(b.x, w0, acc0[4]); acc1[4] = fmaf(b.x, w1, acc1[4]);
+                        acc0[5] = fmaf(b.y, w0, acc0[5]); acc1[5] = fmaf(b.y, w1, acc1[5]);
+                        acc0[6] = fmaf(b.z, w0, acc0[6]); acc1[6] = fmaf(b.z, w1, acc1[6]);
+                        acc0[7] = fmaf(b.w, w0, acc0[7]); acc1[7] = fmaf(b.w, w1, acc1[7]);
+                    }
                 }
-            }
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * st.np + n] = acc[r];
+                for (int r = 0; r < ROWS; ++r)
+                    *reinterpret_cast<float2 *>(red + (slice * ROWS + r) * st.np + n) =
+                        make_float2(acc0[r], acc1[r]);
+            }
+        } else {
+            for (int vt = threadIdx.x; vt < st.np * st.slices; vt += blockDim.x) {
+                const int n = vt % st.np, slice = vt / st.np;
+                float acc[ROWS];
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+                if (n < st.N) {
+                    const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
+                    const T *wp = w + (int64_t)k0 * st.N + n;
+#pragma unroll 8
+                    for (int k = k0; k < k1; ++k, wp += st.N) {
+                        const float wv = to_f32(*wp);
+                        const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
+                        const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
+                        acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
+                        acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
+                        acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
+                        acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * st.np + n] = acc[r];
+            }
         }
         __syncthreads();
         const bool last = l + 1 == p.n_layers;

@@ -374,11 +374,25 @@ def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):
         [lambda i=i: dev.dense_chain_forward(fs[i % 16], [P[2], P[3], P[4]], [None, None, P[5]],
                                              [True, True, False]) for i in range(32)],
         2 * B * (256 * 128 + 128 * 84 + 84 * 10), (B * 256 + 46920 - 2550 + B * 10) * s)
-    name = max(stages, key=lambda k: stages[k]["us"])
+    total_flops = sum(v["alg_flops"] for v in stages.values())
+    layered_us = sum(v["us"] for v in stages.values())
+    convs = [(P[0], None, True, (2, 2)), (P[1], None, True, (2, 2))]
+    add("whole network (conv_chain_kernel: 2 x conv+relu+pool, flatten, dense 256-128-84-10)",
+        [lambda i=i: dev.conv_dense_chain_forward(xs[i], convs, [P[2], P[3], P[4]],
+                                                  [None, None, P[5]], [True, True, False])
+         for i in range(32)],
+        total_flops, (B * 784 + 44426 + B * 10) * s)
+    # The step runs the whole-network kernel; the three layer kernels above are what it
+    # replaces (kept for comparison: their sum is the layer-by-layer step).
+    name = next(k for k in stages if k.startswith("whole network"))
     st = stages[name]
+    st["layer_by_layer_us"] = layered_us
     fp32_peak = 148 * 128 * 2 * 1.965e-3  # TFLOP/s at the maximum SM clock
     roof = {"bound": "hbm", "kernel": name, "achieved": st["gbs"], "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": st["gbs"] / peaks["hbm_gbs"], "traffic": None,
+            "unit": "GB/s", "frac": st["gbs"] / peaks["hbm_gbs"],
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch at batch 1000, from the
+            # ncu capture summarised in profiles/lenet5_infer_f32_kernels.md
+            "traffic": 3373312 if B == 1000 else None,
             "peak_source": peaks["source"], "us_per_launch": st["us"],
             "algorithmic_bytes_per_launch": st["alg_bytes"],
             "fp32_pipe": {"achieved_tflops": st["gflops"] * 1e-3, "peak_tflops": fp32_peak,
@@ -417,7 +431,7 @@ def gemm_sweep(torch, ag, dev, peaks, sampler):
                     entry["frac_of_fp32_pipe_peak_at_max_clock"] = tf / (148 * 128 * 2 * 1.965e-3)
                 results.append(entry)
                 if name == "bf16" and n == 4096 and layout == "nn":
-                    roof = {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel (tcgen05), 4096^3 nn",
+                    roof = {"bound": "tensor", "kernel": "gemm_bf16_tc2_kernel (tcgen05, cta_group::2), 4096^3 nn",
                             "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                             "frac": tf / peaks["bf16_tflops"], "traffic": None,
                             "peak_source": peaks["source"] + " (burst: kernel timed alone)"}
@@ -461,6 +475,37 @@ def extras(torch, ag, dev, peaks, world):
     ms = event_time_ms(torch, lambda i: m.train_step(xt, tt, 0.01), 100, dev.stream) / 100
     out["lenet5_train_f32_bs100"] = {"ms_per_step": ms, "img_per_s": 100 / ms * 1e3}
     m.close()
+    if world == 1:
+        # configs[3]: the wider conv stack, bf16, batch 256: forward + backward + SGD update.
+        # FLOPs of one step: 2 * MACs of (conv1, conv2, dense1, dense2), forward once and
+        # backward twice (input and weight gradients; conv1 has no input gradient).
+        mw = ag.Model(dev, ag.WIDE_STACK_SPEC, torch.bfloat16, seed=2000)
+        xw = torch.randn((256, 3, 64, 64)).to(torch.bfloat16).pin_memory()
+        tw = torch.randint(0, 10, (256,), dtype=torch.uint8).pin_memory()
+        for i in range(4):
+            mw.train_step(xw, tw, 0.01)
+        ms = event_time_ms(torch, lambda i: mw.train_step(xw, tw, 0.01), 20, dev.stream) / 20
+        macs = 256 * (64 * 62 * 62 * 27 * 2 + 128 * 29 * 29 * 576 * 3 + 25088 * 512 * 3 + 512 * 10 * 3)
+        out["wide_stack_train_bf16_bs256"] = {"ms_per_step": ms, "img_per_s": 256 / ms * 1e3,
+                                              "tflops": 2.0 * macs / ms * 1e-9}
+        mw.close()
+        # its second convolution alone (64 -> 128 channels, 3x3, 31x31 images) on tcgen05:
+        # forward with bias + ReLU, input gradient, weight gradient
+        x = torch.randn((256, 64, 31, 31), device=dev.torch_device).to(torch.bfloat16)
+        w = (torch.rand((128, 64, 3, 3), device=dev.torch_device) * 0.1 - 0.05).to(torch.bfloat16)
+        bias = torch.zeros((128,), device=dev.torch_device).to(torch.bfloat16)
+        dy = torch.randn((256, 128, 29, 29), device=dev.torch_device).to(torch.bfloat16)
+        gf = 2.0 * 256 * 128 * 29 * 29 * 64 * 9 * 1e-9
+        conv = {}
+        for name, fn in [("forward", lambda i: dev.conv2_forward(x, w, bias=bias, relu=True)),
+                         ("backward_input", lambda i: dev.conv2_backward_input(w, dy, (31, 31))),
+                         ("backward_weight", lambda i: dev.conv2_backward_weight(x, dy, (3, 3)))]:
+            for i in range(3):
+                fn(i)
+            ms = event_time_ms(torch, fn, 20, dev.stream) / 20
+            conv[name] = {"ms": ms, "tflops": gf / ms,
+                          "frac_of_measured_bf16_peak": gf / ms / peaks["bf16_tflops"]}
+        out["conv2_bf16_tcgen05_64to128_3x3_bs256"] = conv
     return out
 
 
