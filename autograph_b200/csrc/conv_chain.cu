@@ -3,7 +3,7 @@
 //
 // At batch 1000 each layer of such a network is a few microseconds of work, so a
 // layer-by-layer run is bound by launch gaps, by the tail of every grid and by
-// the round trips of the activations through L2.  Here a CTA owns 8 images from
+// the round trips of the activations through L2.  Here a CTA owns up to 8 images from
 // the input to the logits: the images and both filter banks are staged in shared
 // memory once, the activations of every layer stay in shared memory, and only the
 // dense weights are streamed (from L2) while the logits are the only thing
@@ -32,6 +32,7 @@ struct StagePlan {
 
 struct Plan {
     int bs, n_conv;
+    int group;  // images per CTA (<= ROWS)
     StagePlan st[kMaxConv];
     int in_off, mid_off;  // staged input images; output of stage 0 when there are two stages
     int xa_off, xb_off, red_off;
@@ -67,8 +68,8 @@ template <class T, int F>
 __global__ void __launch_bounds__(512, 1)
     conv_chain_kernel(const T *__restrict__ x, T *__restrict__ y, const Plan pl) {
     extern __shared__ __align__(16) float smem[];
-    const int b0 = blockIdx.x * ROWS;
-    const int nimg = min(ROWS, pl.bs - b0);
+    const int b0 = blockIdx.x * pl.group;
+    const int nimg = min(pl.group, pl.bs - b0);
     const direct::Params &p0 = pl.st[0].p;
     const int img_elems = p0.ic * p0.ih * p0.iw;
     float *xa = smem + pl.xa_off;
@@ -181,7 +182,7 @@ static int launch(ag_device *dev, const T *x, T *y, const Plan &pl, size_t smem)
     if (smem > 48 * 1024)
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
-    kernel<<<(unsigned)ceil_div(pl.bs, ROWS), 512, smem, dev->stream>>>(x, y, pl);
+    kernel<<<(unsigned)ceil_div(pl.bs, pl.group), 512, smem, dev->stream>>>(x, y, pl);
     AG_CHECK_LAUNCH();
     return AG_OK;
 }
@@ -192,6 +193,10 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
     Plan pl;
     const size_t smem = make_plan(&pl, bs, ic, ih, iw, n_conv, stages, n_dense, layers);
     AG_REQUIRE(smem != 0, AG_ERR_UNSUPPORTED, "this network does not fit the fused kernel");
+    // Images per CTA: a batch that does not fill the GPU at 8 per CTA is spread over all
+    // SMs instead (fewer rounds of convolution work items per CTA, one wave of CTAs).
+    int64_t group = ceil_div(bs, (int64_t)dev->sm_count);
+    pl.group = (int)(group < 1 ? 1 : (group > ROWS ? ROWS : group));
     if (stages[0].options.filter[0] == 5) return launch<T, 5>(dev, x, y, pl, smem);
     return launch<T, 3>(dev, x, y, pl, smem);
 }

@@ -93,7 +93,7 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
                 if (n < st.N) {
                     const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
                     const T *wp = w + (int64_t)k0 * st.N + n;
-#pragma unroll 4
+#pragma unroll 8
                     for (int k = k0; k < k1; ++k, wp += st.N) {
                         float w0, w1;
                         load2_to_f32(wp, w0, w1);

@@ -247,7 +247,7 @@ void build_model(ag_model *m, const ag_layer_spec *specs, int n, uint64_t seed) 
 // (Conv2 [Relu] [MaxPool2]){1,2} Flatten (Dense [Relu]){1,4}, no gradient is
 // recorded and the kernel takes its sizes.  Returns false when the layers have to
 // run one by one.
-bool forward_whole_network(ag_model *m, const Variable &v, Variable *out) {
+bool forward_whole_network(ag_model *m, const Variable &v, Variable *out, void *out_ptr) {
     if (!m->whole_network || v.node || v.value.ndim() != 4 || !v.value.is_standard_layout())
         return false;
     const size_t n = m->layers.size();
@@ -300,7 +300,9 @@ bool forward_whole_network(ag_model *m, const Variable &v, Variable *out) {
     if (ws.empty()) return false;
     const Tensor &x = v.value;
     if (x.dim(0) == 0) return false;
-    Tensor y = Tensor::uninit(m->pool, {x.dim(0), dims.back()}, x.dtype());
+    // out_ptr: device-visible memory of the caller that receives the logits directly
+    Tensor y = out_ptr ? Tensor::external(x.device(), out_ptr, {x.dim(0), dims.back()}, x.dtype())
+                       : Tensor::uninit(m->pool, {x.dim(0), dims.back()}, x.dtype());
     const int status = ag_conv_dense_chain_forward(
         x.device(), x.dtype(), x.data(), x.dim(0), x.dim(1), x.dim(2), x.dim(3),
         (int32_t)stages.size(), stages.data(), (int32_t)ws.size(), dims.data(), ws.data(),
@@ -314,11 +316,13 @@ bool forward_whole_network(ag_model *m, const Variable &v, Variable *out) {
     return true;
 }
 
-Variable forward_chain(ag_model *m, Variable v) {
+// out_ptr (optional): where the result should land when the network runs as one kernel;
+// the caller compares the returned tensor's address to see whether it did.
+Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
     const size_t n = m->layers.size();
     {
         Variable whole;
-        if (forward_whole_network(m, v, &whole)) return whole;
+        if (forward_whole_network(m, v, &whole, out_ptr)) return whole;
     }
     for (size_t i = 0; i < n; ++i) {
         Layer *l = m->layers[i].get();
@@ -389,8 +393,7 @@ GraphEntry *find_graph(ag_model *m, int64_t bs, int64_t c, int64_t h, int64_t w)
     }
     m->graphs.emplace_back();
     GraphEntry &g = m->graphs.back();
-    g.bs = bs; g.c = c; g.h = h; g.w = w;
-    g.x_stage = Tensor::uninit(m->pool, {bs, c, h, w}, m->dtype);
+    g.bs = bs; g.c = c; g.h = h; g.w = w;  // the staging tensor is made on first use
     return &g;
 }
 
@@ -445,11 +448,15 @@ bool run_zero_copy(ag_model *m, GraphEntry *g, const void *x, void *out) {
         ::ag::count_launches(cp.kernels);
         return true;
     }
+    void *out_dev = pinned_device_pointer(out);
     auto pass = [&]() {
+        // The one-kernel network writes its logits straight into the caller's pinned
+        // buffer; any other network leaves them on the device and they are copied.
         Tensor xt = Tensor::external(m->dev, x_dev, {g->bs, g->c, g->h, g->w}, m->dtype);
-        Variable y = forward_chain(m, Variable{xt, nullptr});
-        cuda_ok(cudaMemcpyAsync(out, y.value.data(), y.value.nbytes(), cudaMemcpyDeviceToHost,
-                                stream), "output copy");
+        Variable y = forward_chain(m, Variable{xt, nullptr}, out_dev);
+        if (y.value.data() != out_dev)
+            cuda_ok(cudaMemcpyAsync(out, y.value.data(), y.value.nbytes(), cudaMemcpyDeviceToHost,
+                                    stream), "output copy");
     };
     // The captured form: batch slices alternating between the two side streams.
     // Every slice adds graph nodes and cross-stream dependencies (a few microseconds
@@ -519,10 +526,34 @@ bool run_zero_copy(ag_model *m, GraphEntry *g, const void *x, void *out) {
 // a shape runs eagerly; the second captures the pass; later calls replay it.
 void run_inference(ag_model *m, GraphEntry *g, bool host, const void *x, void *out) {
     g->last_use = ++m->tick;
+    // A network that runs as one kernel needs neither staging copies nor a graph: the
+    // kernel reads the caller's images and writes the caller's logits (device memory, or
+    // pinned host memory through its device address).
+    if (m->whole_network && g->bs > 0 && (!host || m->zero_copy_enabled)) {
+        void *x_dev = host ? pinned_device_pointer(x) : const_cast<void *>(x);
+        void *out_dev = host ? pinned_device_pointer(out) : out;
+        if (x_dev && out_dev) {
+            Tensor xt = Tensor::external(m->dev, x_dev, {g->bs, g->c, g->h, g->w}, m->dtype);
+            Variable y = forward_chain(m, Variable{xt, nullptr}, out_dev);
+            if (y.value.data() != out_dev) {
+                // not a one-kernel network after all (remembered): hand this result over
+                cudaStream_t st = (cudaStream_t)ag_device_stream(m->dev);
+                if (cudaMemcpyAsync(out, y.value.data(), y.value.nbytes(),
+                                    host ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice,
+                                    st) != cudaSuccess)
+                    throw Error(AG_ERR_CUDA, "output copy failed");
+                // y's block returns to the pool; later work on this stream is ordered after
+                // the copy, so reuse is safe
+            }
+            return;
+        }
+    }
     if (host && m->graphs_enabled && m->zero_copy_enabled && g->bs > 0 &&
         run_zero_copy(m, g, x, out))
         return;
     cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
+    if (!g->x_stage.defined())
+        g->x_stage = Tensor::uninit(m->pool, {g->bs, g->c, g->h, g->w}, m->dtype);
     CapturedPass &cp = host ? g->from_host : g->from_device;
     const cudaMemcpyKind kin = host ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
     const cudaMemcpyKind kout = host ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
