@@ -513,7 +513,7 @@ def run_probe(args):
     """Runs one kernel family alone, for profiler captures:
     gemm:<f32|bf16>:<n>:<nn|tn|nt|tt>, infer:<f32|bf16>:<batch>, train:<f32|bf16>:<batch>,
     wide:<f32|bf16>:<batch> (training step of the wider conv stack), conv:bf16:<batch>
-    (its second convolution alone: forward and input gradient),
+    (its second convolution alone: forward, input gradient and weight gradient),
     op:<f32|bf16>:<relu|relu_backward|scaled_add|sgd_momentum|max_pool2|max_pool2_backward|
     bias_grad>:<elements>."""
     import torch
@@ -574,7 +574,8 @@ def run_probe(args):
         def fn(i):
             dev.conv2_forward(x, w, bias=bias, relu=True)
             dev.conv2_backward_input(w, dy, (31, 31))
-        work, unit = 2 * 2.0 * bs * 128 * 29 * 29 * 64 * 9 * 1e-12, "TFLOP/s"
+            dev.conv2_backward_weight(x, dy, (3, 3))
+        work, unit = 3 * 2.0 * bs * 128 * 29 * 29 * 64 * 9 * 1e-12, "TFLOP/s"
     elif parts[0] == "wide":
         bs = int(parts[2])
         model = ag.Model(dev, ag.WIDE_STACK_SPEC, dtype, seed=2000)
