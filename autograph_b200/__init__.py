@@ -218,11 +218,20 @@ class Device:
                                                  rl, _ptr(y)))
         return y
 
-    def conv_dense_chain_forward(self, x, convs, weights, biases=None, relus=None):
+    def scaled_cast_u8(self, x_u8, alpha, dtype):
+        """≙ Tensor::scaled_cast for u8 input: alpha * x in `dtype` (f32 or bf16)."""
+        y = self.empty(tuple(x_u8.shape), dtype)
+        self._sync_in()
+        _capi.check(lib().ag_scaled_cast_u8(self._h, _dtype_code(dtype), ctypes.c_float(alpha),
+                                            _ptr(x_u8.contiguous()), _ptr(y), x_u8.numel()))
+        return y
+
+    def conv_dense_chain_forward(self, x, convs, weights, biases=None, relus=None, u8_alpha=None):
         """A small network in one kernel.  convs: list of (w, bias, relu, pool) with pool a
         (ph, pw) window or None; then Flatten and the Dense (+ Relu) layers of
-        dense_chain_forward.  Raises AgError(AG_ERR_UNSUPPORTED) when the network does not
-        fit the fused kernel."""
+        dense_chain_forward.  With u8_alpha, x is a u8 tensor that the kernel scales by
+        u8_alpha into the weights' dtype while staging it.  Raises AgError(AG_ERR_UNSUPPORTED)
+        when the network does not fit the fused kernel."""
         bs, ic, ih, iw = x.shape
         stages = (_capi.ConvStage * len(convs))()
         keep = []
@@ -243,11 +252,17 @@ class Device:
         ws = (ctypes.c_void_p * n)(*[w.data_ptr() for w in weights])
         bp = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
         rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
-        y = self.empty((bs, weights[-1].shape[1]), x.dtype)
+        out_dtype = weights[0].dtype
+        y = self.empty((bs, weights[-1].shape[1]), out_dtype)
         self._sync_in()
-        _capi.check(lib().ag_conv_dense_chain_forward(
-            self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw, len(convs),
-            stages, n, dims, ws, bp, rl, _ptr(y)))
+        if u8_alpha is not None:
+            _capi.check(lib().ag_conv_dense_chain_forward_u8(
+                self._h, _dtype_code(out_dtype), _ptr(x.contiguous()), ctypes.c_float(u8_alpha), bs,
+                ic, ih, iw, len(convs), stages, n, dims, ws, bp, rl, _ptr(y)))
+        else:
+            _capi.check(lib().ag_conv_dense_chain_forward(
+                self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw, len(convs),
+                stages, n, dims, ws, bp, rl, _ptr(y)))
         return y
 
     def conv2_backward_input(self, w, dy, input_hw, padding=(0, 0), stride=(1, 1),
@@ -525,6 +540,17 @@ class Model:
         if out_host is None:
             out_host = torch.empty((bs, self.out_features), dtype=self.dtype)
         _capi.check(lib().ag_model_infer(self._h, _ptr(x_host), bs, c, h, w, _ptr(out_host)))
+        return out_host
+
+    def infer_u8(self, x_host_u8, alpha=1.0 / 255.0, out_host=None):
+        """u8 host images [bs,c,h,w] -> alpha * x in the model dtype -> host logits (blocking);
+        ≙ images_to_device_and_scale + forward of the reference's MNIST example."""
+        torch = _torch()
+        bs, c, h, w = x_host_u8.shape
+        if out_host is None:
+            out_host = torch.empty((bs, self.out_features), dtype=self.dtype)
+        _capi.check(lib().ag_model_infer_u8(self._h, _ptr(x_host_u8), bs, c, h, w,
+                                            ctypes.c_float(alpha), _ptr(out_host)))
         return out_host
 
     def forward_device(self, x_dev, out_dev=None):

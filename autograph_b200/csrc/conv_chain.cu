@@ -33,6 +33,8 @@ struct StagePlan {
 struct Plan {
     int bs, n_conv;
     int group;  // images per CTA (<= ROWS)
+    const uint8_t *x8;  // when set: u8 images, scaled by alpha while they are staged
+    float alpha;
     StagePlan st[kMaxConv];
     int in_off, mid_off;  // staged input images; output of stage 0 when there are two stages
     int xa_off, xb_off, red_off;
@@ -74,7 +76,27 @@ __global__ void __launch_bounds__(512, 1)
     const int img_elems = p0.ic * p0.ih * p0.iw;
     float *xa = smem + pl.xa_off;
 
-    direct::stage_contiguous<T>(x + (int64_t)b0 * img_elems, smem + pl.in_off, nimg * img_elems);
+    if (pl.x8 != nullptr) {
+        // scaled_cast on the way in: alpha * u8 in T (alpha rounded to T, one rounding of the product)
+        const float a = to_f32(from_f32<T>(pl.alpha));
+        const uint8_t *src = pl.x8 + (int64_t)b0 * img_elems;
+        float *dst = smem + pl.in_off;
+        const int total = nimg * img_elems;
+        const int nvec = (reinterpret_cast<uintptr_t>(src) & 3) == 0 ? total / 4 : 0;
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            const uint32_t q = reinterpret_cast<const uint32_t *>(src)[i];
+            float4 v;
+            v.x = to_f32(from_f32<T>(a * (float)(q & 0xffu)));
+            v.y = to_f32(from_f32<T>(a * (float)((q >> 8) & 0xffu)));
+            v.z = to_f32(from_f32<T>(a * (float)((q >> 16) & 0xffu)));
+            v.w = to_f32(from_f32<T>(a * (float)(q >> 24)));
+            reinterpret_cast<float4 *>(dst)[i] = v;
+        }
+        for (int i = nvec * 4 + threadIdx.x; i < total; i += blockDim.x)
+            dst[i] = to_f32(from_f32<T>(a * (float)src[i]));
+    } else {
+        direct::stage_contiguous<T>(x + (int64_t)b0 * img_elems, smem + pl.in_off, nimg * img_elems);
+    }
     for (int s = 0; s < pl.n_conv; ++s) {
         const StagePlan &sp = pl.st[s];
         direct::stage_filters<T>(reinterpret_cast<const T *>(sp.w),
@@ -188,9 +210,12 @@ static int launch(ag_device *dev, const T *x, T *y, const Plan &pl, size_t smem)
 }
 
 template <class T>
-int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw, int n_conv,
-            const ag_conv_stage *stages, int n_dense, const dense_small::ChainLayer *layers, T *y) {
+int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t bs, int64_t ic,
+            int64_t ih, int64_t iw, int n_conv, const ag_conv_stage *stages, int n_dense,
+            const dense_small::ChainLayer *layers, T *y) {
     Plan pl;
+    pl.x8 = x8;
+    pl.alpha = alpha;
     const size_t smem = make_plan(&pl, bs, ic, ih, iw, n_conv, stages, n_dense, layers);
     AG_REQUIRE(smem != 0, AG_ERR_UNSUPPORTED, "this network does not fit the fused kernel");
     // Images per CTA: a batch that does not fill the GPU at 8 per CTA is spread over all
@@ -201,23 +226,23 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
     return launch<T, 3>(dev, x, y, pl, smem);
 }
 
-template int forward<float>(ag_device *, const float *, int64_t, int64_t, int64_t, int64_t, int,
-                            const ag_conv_stage *, int, const dense_small::ChainLayer *, float *);
-template int forward<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, int64_t, int64_t, int64_t,
-                                    int64_t, int, const ag_conv_stage *, int,
-                                    const dense_small::ChainLayer *, __nv_bfloat16 *);
+template int forward<float>(ag_device *, const float *, const uint8_t *, float, int64_t, int64_t,
+                            int64_t, int64_t, int, const ag_conv_stage *, int,
+                            const dense_small::ChainLayer *, float *);
+template int forward<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, const uint8_t *, float,
+                                    int64_t, int64_t, int64_t, int64_t, int, const ag_conv_stage *,
+                                    int, const dense_small::ChainLayer *, __nv_bfloat16 *);
 
 }  // namespace conv_chain
 }  // namespace ag
 
 using namespace ag;
 
-extern "C" int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
-                                           int64_t ic, int64_t ih, int64_t iw, int32_t n_conv,
-                                           const ag_conv_stage *stages, int32_t n_dense,
-                                           const int64_t *dims, const void *const *weights,
-                                           const void *const *biases, const int32_t *relu,
-                                           void *y) {
+static int conv_dense_chain_entry(ag_device *dev, ag_dtype dtype, const void *x, const uint8_t *x8,
+                                  float alpha, int64_t bs, int64_t ic, int64_t ih, int64_t iw,
+                                  int32_t n_conv, const ag_conv_stage *stages, int32_t n_dense,
+                                  const int64_t *dims, const void *const *weights,
+                                  const void *const *biases, const int32_t *relu, void *y) {
     AG_ENTER(dev);
     AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "conv_dense_chain %d not implemented",
                (int)dtype);
@@ -237,10 +262,34 @@ extern "C" int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const
     for (int s = 0; s < n_conv; ++s)
         AG_REQUIRE(stages[s].w != nullptr && stages[s].oc > 0, AG_ERR_INVALID, "bad conv stage");
     if (bs == 0) return AG_OK;
-    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    AG_REQUIRE((x || x8) && y, AG_ERR_INVALID, "null tensor pointer");
     if (dtype == AG_F32)
-        return conv_chain::forward<float>(dev, (const float *)x, bs, ic, ih, iw, n_conv, stages,
-                                          n_dense, layers, (float *)y);
-    return conv_chain::forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw, n_conv,
-                                              stages, n_dense, layers, (__nv_bfloat16 *)y);
+        return conv_chain::forward<float>(dev, (const float *)x, x8, alpha, bs, ic, ih, iw, n_conv,
+                                          stages, n_dense, layers, (float *)y);
+    return conv_chain::forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, x8, alpha, bs, ic, ih,
+                                              iw, n_conv, stages, n_dense, layers,
+                                              (__nv_bfloat16 *)y);
+}
+
+extern "C" int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                           int64_t ic, int64_t ih, int64_t iw, int32_t n_conv,
+                                           const ag_conv_stage *stages, int32_t n_dense,
+                                           const int64_t *dims, const void *const *weights,
+                                           const void *const *biases, const int32_t *relu,
+                                           void *y) {
+    AG_REQUIRE(x != nullptr || bs == 0, AG_ERR_INVALID, "null tensor pointer");
+    return conv_dense_chain_entry(dev, dtype, x, nullptr, 0.f, bs, ic, ih, iw, n_conv, stages,
+                                  n_dense, dims, weights, biases, relu, y);
+}
+
+extern "C" int ag_conv_dense_chain_forward_u8(ag_device *dev, ag_dtype dtype, const uint8_t *x,
+                                              float alpha, int64_t bs, int64_t ic, int64_t ih,
+                                              int64_t iw, int32_t n_conv,
+                                              const ag_conv_stage *stages, int32_t n_dense,
+                                              const int64_t *dims, const void *const *weights,
+                                              const void *const *biases, const int32_t *relu,
+                                              void *y) {
+    AG_REQUIRE(x != nullptr || bs == 0, AG_ERR_INVALID, "null tensor pointer");
+    return conv_dense_chain_entry(dev, dtype, nullptr, x, alpha, bs, ic, ih, iw, n_conv, stages,
+                                  n_dense, dims, weights, biases, relu, y);
 }

@@ -17,9 +17,11 @@ constexpr int kMaxConv = 2;
 bool eligible(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int n_conv,
               const ag_conv_stage *stages, int n_dense, const dense_small::ChainLayer *layers);
 
+// Reads x, or (x8 != null) u8 images that are scaled by alpha while they are staged.
 template <class T>
-int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw, int n_conv,
-            const ag_conv_stage *stages, int n_dense, const dense_small::ChainLayer *layers, T *y);
+int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t bs, int64_t ic,
+            int64_t ih, int64_t iw, int n_conv, const ag_conv_stage *stages, int n_dense,
+            const dense_small::ChainLayer *layers, T *y);
 
 }  // namespace conv_chain
 }  // namespace ag

@@ -247,7 +247,14 @@ void build_model(ag_model *m, const ag_layer_spec *specs, int n, uint64_t seed) 
 // (Conv2 [Relu] [MaxPool2]){1,2} Flatten (Dense [Relu]){1,4}, no gradient is
 // recorded and the kernel takes its sizes.  Returns false when the layers have to
 // run one by one.
-bool forward_whole_network(ag_model *m, const Variable &v, Variable *out, void *out_ptr) {
+// u8 images (device-visible) standing in for v's data, scaled by alpha inside the kernel.
+struct U8Images {
+    const uint8_t *ptr;
+    float alpha;
+};
+
+bool forward_whole_network(ag_model *m, const Variable &v, Variable *out, void *out_ptr,
+                           const U8Images *u8 = nullptr) {
     if (!m->whole_network || v.node || v.value.ndim() != 4 || !v.value.is_standard_layout())
         return false;
     const size_t n = m->layers.size();
@@ -303,10 +310,15 @@ bool forward_whole_network(ag_model *m, const Variable &v, Variable *out, void *
     // out_ptr: device-visible memory of the caller that receives the logits directly
     Tensor y = out_ptr ? Tensor::external(x.device(), out_ptr, {x.dim(0), dims.back()}, x.dtype())
                        : Tensor::uninit(m->pool, {x.dim(0), dims.back()}, x.dtype());
-    const int status = ag_conv_dense_chain_forward(
-        x.device(), x.dtype(), x.data(), x.dim(0), x.dim(1), x.dim(2), x.dim(3),
-        (int32_t)stages.size(), stages.data(), (int32_t)ws.size(), dims.data(), ws.data(),
-        bs.data(), relus.data(), y.data());
+    const int status =
+        u8 ? ag_conv_dense_chain_forward_u8(x.device(), x.dtype(), u8->ptr, u8->alpha, x.dim(0),
+                                            x.dim(1), x.dim(2), x.dim(3), (int32_t)stages.size(),
+                                            stages.data(), (int32_t)ws.size(), dims.data(),
+                                            ws.data(), bs.data(), relus.data(), y.data())
+           : ag_conv_dense_chain_forward(x.device(), x.dtype(), x.data(), x.dim(0), x.dim(1),
+                                         x.dim(2), x.dim(3), (int32_t)stages.size(), stages.data(),
+                                         (int32_t)ws.size(), dims.data(), ws.data(), bs.data(),
+                                         relus.data(), y.data());
     if (status == AG_ERR_UNSUPPORTED) {
         m->whole_network = false;  // decided by the layer sizes: do not ask again
         return false;
@@ -775,6 +787,39 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
 
 }  // namespace
 
+// u8 host images -> logits on the host (blocking); see ag_model_infer_u8.
+void infer_u8(ag_model *m, const uint8_t *x_host, int64_t bs, int64_t c, int64_t h, int64_t w,
+              float alpha, void *logits_host) {
+    cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
+    auto sync = [&]() {
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess)
+            throw Error(AG_ERR_CUDA, std::string("cudaStreamSynchronize failed: ") + cudaGetErrorString(e));
+    };
+    const size_t n = (size_t)(bs * c * h * w);
+    // One-kernel network on pinned buffers: the kernel reads the u8 images over PCIe,
+    // scales them while staging, and writes the logits into the caller's buffer.
+    void *x_dev = pinned_device_pointer(x_host);
+    void *out_dev = pinned_device_pointer(logits_host);
+    if (m->whole_network && m->zero_copy_enabled && x_dev && out_dev) {
+        U8Images u8{(const uint8_t *)x_dev, alpha};
+        Tensor shape_only = Tensor::external(m->dev, x_dev, {bs, c, h, w}, m->dtype);
+        Variable y;
+        if (forward_whole_network(m, Variable{shape_only, nullptr}, &y, out_dev, &u8)) {
+            sync();
+            return;
+        }
+    }
+    // General path: upload the bytes, scaled_cast on the device, then the usual pass.
+    Tensor raw = Tensor::uninit(m->pool, {(int64_t)n}, AG_U8);
+    check(ag_upload(m->dev, raw.data(), x_host, n));
+    Tensor x = Tensor::uninit(m->pool, {bs, c, h, w}, m->dtype);
+    check(ag_scaled_cast_u8(m->dev, m->dtype, alpha, (const uint8_t *)raw.data(), x.data(),
+                            (int64_t)n));
+    Variable y = forward_chain(m, Variable{x, nullptr});
+    check(ag_download(m->dev, logits_host, y.value.data(), y.value.nbytes()));
+}
+
 #define AG_HOST_GUARD(body)                                         \
     try {                                                           \
         body                                                        \
@@ -892,6 +937,17 @@ int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, i
         cudaError_t e = cudaStreamSynchronize((cudaStream_t)ag_device_stream(model->dev));
         if (e != cudaSuccess)
             throw Error(AG_ERR_CUDA, std::string("cudaStreamSynchronize failed: ") + cudaGetErrorString(e));
+    })
+}
+
+int ag_model_infer_u8(ag_model *model, const uint8_t *x_host, int64_t bs, int64_t c, int64_t h,
+                      int64_t w, float alpha, void *logits_host) {
+    AG_REQUIRE(model && logits_host, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({
+        if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+        if (!x_host && bs > 0) throw Error(AG_ERR_INVALID, "input pointer is null");
+        if (bs > 0) infer_u8(model, x_host, bs, c, h, w, alpha, logits_host);
     })
 }
 

@@ -294,6 +294,33 @@ __global__ void max_pool2_backward_staged_kernel(T *__restrict__ dx, const T *__
     }
 }
 
+// ---- u8 images -> float ----------------------------------------------------------
+// y = alpha * x in the output type (alpha rounded to T first, one rounding of the product).
+// A thread converts 16 bytes when both pointers allow 16-byte accesses.
+template <class T>
+__global__ void scaled_cast_u8_kernel(const uint8_t *__restrict__ x, T *__restrict__ y, int64_t n,
+                                      float alpha) {
+    const float a = to_f32(from_f32<T>(alpha));
+    const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    const int64_t nvec = vec ? n / 16 : 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 q = reinterpret_cast<const uint4 *>(x)[i];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        __align__(16) T out[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            out[j] = from_f32<T>(a * (float)((w[j >> 2] >> (8 * (j & 3))) & 0xffu));
+        uint4 *dst = reinterpret_cast<uint4 *>(y + i * 16);
+        const uint4 *src = reinterpret_cast<const uint4 *>(out);
+#pragma unroll
+        for (int j = 0; j < (int)(16 * sizeof(T) / 16); ++j) dst[j] = src[j];
+    }
+    for (int64_t i = nvec * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        y[i] = from_f32<T>(a * (float)x[i]);
+}
+
 // ---- bias ---------------------------------------------------------------------
 template <class T>
 __global__ void bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias, int64_t total,
@@ -440,6 +467,21 @@ using namespace ag;
     } while (0)
 
 extern "C" {
+
+int ag_scaled_cast_u8(ag_device *dev, ag_dtype dtype, float alpha, const uint8_t *x, void *y,
+                      int64_t n) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "scaled_cast to %d unimplemented", (int)dtype);
+    AG_REQUIRE(n >= 0, AG_ERR_SHAPE, "negative length");
+    if (n == 0) return AG_OK;
+    AG_REQUIRE(x && y, AG_ERR_INVALID, "null tensor pointer");
+    const int threads = 256;
+    const unsigned grid = grid_for(ceil_div(n, 16), threads, dev->sm_count);
+    AG_DISPATCH_FLOAT(dtype, T,
+        scaled_cast_u8_kernel<T><<<grid, threads, 0, dev->stream>>>(x, (T *)y, n, alpha););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
 
 int ag_relu(ag_device *dev, ag_dtype dtype, const void *x, void *y, int64_t n) {
     AG_ENTER(dev);

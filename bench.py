@@ -475,6 +475,22 @@ def extras(torch, ag, dev, peaks, world):
     ms = event_time_ms(torch, lambda i: m.train_step(xt, tt, 0.01), 100, dev.stream) / 100
     out["lenet5_train_f32_bs100"] = {"ms_per_step": ms, "img_per_s": 100 / ms * 1e3}
     m.close()
+    # The reference's own input pipeline (u8 images scaled by 1/255 on the device,
+    # examples/neural-network-mnist/src/main.rs:236-243) end to end: pinned u8 images in, logits out.
+    mi = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)
+    x8 = [torch.randint(0, 256, (BATCH, 1, 28, 28), dtype=torch.uint8).pin_memory() for _ in range(4)]
+    o8 = [torch.empty((BATCH, 10), dtype=torch.float32).pin_memory() for _ in range(4)]
+    for i in range(8):
+        mi.infer_u8(x8[i % 4], out_host=o8[i % 4])
+    t0 = time.perf_counter()
+    n8 = 500
+    for i in range(n8):
+        mi.infer_u8(x8[i % 4], out_host=o8[i % 4])
+    ms = (time.perf_counter() - t0) * 1e3 / n8
+    out["lenet5_infer_f32_bs1000_e2e_u8_images"] = {
+        "img_per_s": BATCH / ms * 1e3, "ms_per_step": ms, "h2d_bytes_per_step": BATCH * 784,
+        "d2h_bytes_per_step": BATCH * 40, "timing": "host wall clock over blocking calls"}
+    mi.close()
     if world == 1:
         # configs[3]: the wider conv stack, bf16, batch 256: forward + backward + SGD update.
         # FLOPs of one step: 2 * MACs of (conv1, conv2, dense1, dense2), forward once and

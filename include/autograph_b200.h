@@ -209,6 +209,18 @@ AG_API int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const voi
                                        const int64_t *dims, const void *const *weights,
                                        const void *const *biases, const int32_t *relu, void *y);
 
+/* The same network on u8 images: the scaled_cast above (x = alpha * u8) is done while the images
+ * are staged in shared memory, so a quarter of the bytes cross PCIe / HBM and no float copy of the
+ * batch is ever written.  ≙ images_to_device_and_scale followed by the model's forward
+ * (examples/neural-network-mnist/src/main.rs:236-243, 275-300).  Equals ag_scaled_cast_u8 followed
+ * by ag_conv_dense_chain_forward bit for bit. */
+AG_API int ag_conv_dense_chain_forward_u8(ag_device *dev, ag_dtype dtype, const uint8_t *x,
+                                          float alpha, int64_t bs, int64_t ic, int64_t ih,
+                                          int64_t iw, int32_t n_conv, const ag_conv_stage *stages,
+                                          int32_t n_dense, const int64_t *dims,
+                                          const void *const *weights, const void *const *biases,
+                                          const int32_t *relu, void *y);
+
 /* dx = col2im(dy . Wmat): replaces the input edge of conv2_im2col
  * (layer.rs:976-988) = dot + kernels::col2im_conv2_<T> (src/tensor/ops.rs:1602-1667).
  * dy [bs,oc,oh,ow] (NCHW, as the autograd edge receives it), dx [bs,ic,ih,iw]. */
@@ -256,6 +268,15 @@ AG_API int ag_max_pool2(ag_device *dev, ag_dtype dtype, const void *x, int64_t b
 AG_API int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, int64_t c,
                                  int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh,
                                  int32_t sw, const void *dy);
+
+/* ----------------------------------------------------------- input pipeline */
+
+/* y = alpha * x with x u8 and y f32 / bf16: ≙ Tensor::scaled_cast (src/tensor/ops.rs:209-218 ->
+ * assign, :295), the step that turns u8 images into network input
+ * (examples/neural-network-mnist/src/main.rs:236-243, alpha = 1/255).  Cast and product are in
+ * the output type: alpha is rounded to it first and the product is rounded once. */
+AG_API int ag_scaled_cast_u8(ag_device *dev, ag_dtype dtype, float alpha, const uint8_t *x, void *y,
+                             int64_t n);
 
 /* ------------------------------------------------------------------- relu */
 
@@ -372,6 +393,13 @@ AG_API int ag_model_set_grad_scale(ag_model *model, float scale);
  * (blocking). */
 AG_API int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, int64_t h,
                           int64_t w, void *logits_host);
+/* The same from u8 images, as the reference's MNIST example feeds its model
+ * (examples/neural-network-mnist/src/main.rs:236-243): x = alpha * u8 in the model's dtype, then
+ * the forward pass.  A one-kernel network reads the u8 images itself (from pinned host memory:
+ * a quarter of the PCIe bytes of the float path); any other network runs ag_scaled_cast_u8 on the
+ * device first.  Blocking. */
+AG_API int ag_model_infer_u8(ag_model *model, const uint8_t *x_host, int64_t bs, int64_t c,
+                             int64_t h, int64_t w, float alpha, void *logits_host);
 /* Forward only, device-resident input and output (no host copies, no sync). */
 AG_API int ag_model_forward_device(ag_model *model, const void *x_dev, int64_t bs, int64_t c,
                                    int64_t h, int64_t w, void *logits_dev);

@@ -89,6 +89,15 @@ def round_bf16(x: np.ndarray) -> np.ndarray:
     return y
 
 
+def scaled_cast_u8(x: np.ndarray, alpha: float, bf16=False) -> np.ndarray:
+    """Tensor::scaled_cast for u8 input (src/tensor/ops.rs:209-218): alpha * x in the output type."""
+    x = np.ascontiguousarray(x, dtype=np.uint8)
+    y = np.empty(x.shape, np.float32)
+    lib().orc_scaled_cast_u8(x.ctypes.data_as(ctypes.c_void_p), _f(y), ctypes.c_int64(x.size),
+                             ctypes.c_float(alpha), int(bf16))
+    return y
+
+
 def conv2_output_shape(ih, iw, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
     oh = (ih + 2 * padding[0] - dilation[0] * (filter[0] - 1) - 1) // stride[0] + 1
     ow = (iw + 2 * padding[1] - dilation[1] * (filter[1] - 1) - 1) // stride[1] + 1

@@ -51,6 +51,17 @@ ORC_API void orc_round_bf16(float *x, int64_t n) {
     for (int64_t i = 0; i < n; ++i) x[i] = bf16_round(x[i]);
 }
 
+/* scaled_cast of u8 images (src/tensor/ops.rs:209-218 -> assign, :295: y = alpha * x.cast()):
+ * the cast and the product are in the output type, so for bf16 alpha is first rounded to
+ * bf16 and the product rounded once (examples/neural-network-mnist/src/main.rs:196-199). */
+ORC_API void orc_scaled_cast_u8(const unsigned char *x, float *y, int64_t n, float alpha, int bf16) {
+    if (bf16) alpha = bf16_round(alpha);
+    for (int64_t i = 0; i < n; ++i) {
+        float v = alpha * (float)x[i];
+        y[i] = bf16 ? bf16_round(v) : v;
+    }
+}
+
 /* Overrides OMP_NUM_THREADS (launchers such as torchrun set it to 1). */
 ORC_API void orc_set_num_threads(int n) {
 #ifdef _OPENMP
