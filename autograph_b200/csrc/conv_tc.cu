@@ -96,6 +96,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint64_t *tmem_empty_bar = bars + 2 * STAGES + 2;
     uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_slot + 1);
+    // bias of this CTA's output channels as f32 (zero where there is none): read from
+    // shared memory in the epilogue instead of one global load per element
+    __shared__ float s_bias[BLOCK_N];
 
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
@@ -122,6 +125,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tmem_alloc(smem_u32(tmem_base_slot), C::TMEM_COLS);
         tmem_relinquish();
     }
+    // one output-channel block per CTA keeps its bias resident; with several blocks the
+    // epilogue reads the bias from global memory
+    const bool bias_resident = p.n_blocks == 1;
+    if (bias_resident)
+        for (int i = threadIdx.x; i < BLOCK_N; i += NUM_THREADS)
+            s_bias[i] = (p.bias != nullptr && i < p.OC) ? __bfloat162float(p.bias[i]) : 0.f;
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -238,21 +247,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 const int oc0 = t.n_blk * BLOCK_N + chunk * 32;
                 if (valid && oc0 < p.OCp) {
                     uint32_t packed[16];
+                    const bool has_bias = p.bias != nullptr;
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        float v[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int oc = oc0 + j + e;
-                            float x = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j + e])));
-                            if (p.bias != nullptr && oc < p.OC)
-                                x = __bfloat162float(
-                                    __float2bfloat16_rn(x + __bfloat162float(p.bias[oc])));
-                            if (p.relu) x = x >= 0.f ? x : 0.f;
-                            v[e] = x;
+                        const int oc = oc0 + j;
+                        float b0 = 0.f, b1 = 0.f;
+                        if (has_bias) {
+                            if (bias_resident) {
+                                b0 = s_bias[oc];
+                                b1 = s_bias[oc + 1];
+                            } else {
+                                b0 = oc < p.OC ? __bfloat162float(p.bias[oc]) : 0.f;
+                                b1 = oc + 1 < p.OC ? __bfloat162float(p.bias[oc + 1]) : 0.f;
+                            }
                         }
-                        __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
-                        packed[j / 2] = *reinterpret_cast<uint32_t *>(&h);
+                        packed[j / 2] = bf16_pair_epilogue(r[j], r[j + 1], b0, b1, has_bias, p.relu != 0);
                     }
                     uint4 *d4 = reinterpret_cast<uint4 *>(dst + oc0);
 #pragma unroll
@@ -285,14 +294,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 }
 
 // ------------------------------------------------------- layout conversions
-// x [B][C][HW] -> out [B][HW][Cp] (Cp a multiple of 64, channels >= C are zero).
+// x [B][C][H*W] -> out [B][Hp][Wp][Cp] (Cp a multiple of 64, channels >= C are zero), the
+// image placed at (pad_h, pad_w) of the Hp x Wp frame (the frame itself is cleared by
+// the caller when it is larger than the image).
 // A thread owns 16 channels of one pixel: 16 independent 2-byte loads, each
 // coalesced across the warp (lanes are consecutive pixels of one channel plane),
 // then one full 32-byte sector of the channels-last copy.  No shared memory.
 // grid (ceil(HW / 256), Cp / 16, B), 256 threads.
 __global__ void __launch_bounds__(256)
     nchw_to_nhwc_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ out, int C,
-                        int HW, int Cp) {
+                        int HW, int Cp, int W, int Hp, int Wp, int pad_h, int pad_w) {
     const int px = blockIdx.x * 256 + threadIdx.x;
     if (px >= HW) return;
     const int c0 = blockIdx.y * 16;
@@ -307,7 +318,9 @@ __global__ void __launch_bounds__(256)
     lo.z = v[4] | ((uint32_t)v[5] << 16);   lo.w = v[6] | ((uint32_t)v[7] << 16);
     hi.x = v[8] | ((uint32_t)v[9] << 16);   hi.y = v[10] | ((uint32_t)v[11] << 16);
     hi.z = v[12] | ((uint32_t)v[13] << 16); hi.w = v[14] | ((uint32_t)v[15] << 16);
-    uint4 *dst = reinterpret_cast<uint4 *>(out + ((int64_t)b * HW + px) * Cp + c0);
+    const int yy = px / W, xx = px - yy * W;
+    const int64_t row = ((int64_t)b * Hp + yy + pad_h) * Wp + xx + pad_w;
+    uint4 *dst = reinterpret_cast<uint4 *>(out + row * Cp + c0);
     dst[0] = lo;
     dst[1] = hi;
 }
@@ -398,10 +411,32 @@ bool tc_conv_enabled() {
 
 static int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
+static bool halo_enabled() {
+    static int v = []() {
+        const char *e = getenv("AG_CONV_HALO");
+        return (e && e[0] == '0') ? 0 : 1;
+    }();
+    return v != 0;
+}
+
 int to_nhwc(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64_t hw, int64_t cp,
             __nv_bfloat16 *out) {
+    // no border: the frame is the image, any width gives the same row index
     nchw_to_nhwc_kernel<<<dim3((unsigned)ceil_div(hw, 256), (unsigned)(cp / 16), (unsigned)bs), 256,
-                          0, dev->stream>>>(x, out, (int)c, (int)hw, (int)cp);
+                          0, dev->stream>>>(x, out, (int)c, (int)hw, (int)cp, (int)hw, 1, (int)hw, 0,
+                                            0);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+int to_nhwc_framed(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64_t h,
+                   int64_t w, int64_t cp, int pad_h, int pad_w, __nv_bfloat16 *out) {
+    const int64_t hp = h + 2 * pad_h, wp = w + 2 * pad_w;
+    if (pad_h || pad_w)
+        AG_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)(bs * hp * wp * cp * 2), dev->stream));
+    nchw_to_nhwc_kernel<<<dim3((unsigned)ceil_div(h * w, 256), (unsigned)(cp / 16), (unsigned)bs),
+                          256, 0, dev->stream>>>(x, out, (int)c, (int)(h * w), (int)cp, (int)w,
+                                                 (int)hp, (int)wp, pad_h, pad_w);
     AG_CHECK_LAUNCH();
     return AG_OK;
 }
@@ -466,7 +501,14 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
                const __nv_bfloat16 *bias, bool relu, __nv_bfloat16 *y) {
     const int64_t cp = round_up(c_in, 64);
     const int taps = fh * fw;
-    const int64_t act_bytes = round_up(bs * in_h * in_w * cp * 2, 1024);
+    // Resident-filter kernel (conv_tc_halo.cu) when the filter bank and two activation
+    // boxes fit in shared memory; it works on the zero-framed image.
+    int hb_n = 0, hb_rows = 0, hb_stages = 0, hb_smem = 0;
+    const int64_t hp = in_h + 2 * pad_h, wp = in_w + 2 * pad_w;
+    const bool halo = halo_enabled() &&
+                      halo_plan(bs, cp, hp, wp, c_out, fh, fw, &hb_n, &hb_rows, &hb_stages, &hb_smem);
+    const int64_t act_bytes =
+        round_up((halo ? bs * hp * wp : bs * in_h * in_w) * cp * 2, 1024);
     const int64_t wk_elems = c_out * taps * cp;
     const int64_t wk_bytes = round_up(wk_elems * 2, 1024);
     const int64_t ocp = round_up(c_out, 64);
@@ -477,7 +519,10 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
     __nv_bfloat16 *wk = (__nv_bfloat16 *)((char *)ws + act_bytes);
     __nv_bfloat16 *out_nhwc = (__nv_bfloat16 *)((char *)ws + act_bytes + wk_bytes);
 
-    AG_TRY(to_nhwc(dev, act, bs, c_in, in_h * in_w, cp, act_nhwc));
+    if (halo)
+        AG_TRY(to_nhwc_framed(dev, act, bs, c_in, in_h, in_w, cp, pad_h, pad_w, act_nhwc));
+    else
+        AG_TRY(to_nhwc(dev, act, bs, c_in, in_h * in_w, cp, act_nhwc));
     const unsigned rgrid = (unsigned)ceil_div(wk_elems, 256);
     if (transposed)
         repack_filters_transposed_kernel<<<rgrid, 256, 0, dev->stream>>>(w, wk, (int)w_oc, (int)w_ic,
@@ -486,6 +531,16 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
         repack_filters_kernel<<<rgrid, 256, 0, dev->stream>>>(w, wk, (int)w_oc, (int)w_ic, taps,
                                                               (int)cp);
     AG_CHECK_LAUNCH();
+    const int64_t out_hw = out_h * out_w;
+    if (halo) {
+        AG_TRY(run_halo(dev, act_nhwc, wk, bs, cp, hp, wp, fh, fw, c_out, out_h, out_w, bias, relu,
+                        out_nhwc));
+        nhwc_to_nchw_kernel<<<dim3((unsigned)ceil_div(out_hw, NCHW_PIX),
+                                   (unsigned)ceil_div(c_out, 16), (unsigned)bs),
+                              256, 0, dev->stream>>>(out_nhwc, y, (int)c_out, (int)out_hw, (int)ocp);
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
 
     // Pixel tile: the TH x TW rectangle (TH * TW = 128) that wastes the fewest pixels.
     int best_shift = 3;
@@ -536,7 +591,6 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
         AG_TRY(launch<128>(dev, tx, tw, p));
     else
         AG_TRY(launch<256>(dev, tx, tw, p));
-    const int64_t out_hw = out_h * out_w;
     nhwc_to_nchw_kernel<<<dim3((unsigned)ceil_div(out_hw, NCHW_PIX), (unsigned)ceil_div(c_out, 16),
                                (unsigned)bs),
                           256, 0, dev->stream>>>(out_nhwc, y, (int)c_out, (int)out_hw, (int)ocp);

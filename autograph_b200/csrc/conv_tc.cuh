@@ -33,6 +33,19 @@ bool tc_conv_enabled();
 int to_nhwc(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64_t hw, int64_t cp,
             __nv_bfloat16 *out);
 
+// The same copy into the middle of a zero frame of pad_h rows / pad_w columns on every side.
+int to_nhwc_framed(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64_t h,
+                   int64_t w, int64_t cp, int pad_h, int pad_w, __nv_bfloat16 *out);
+
+// Resident-filter variant (conv_tc_halo.cu): plan (false when the shape does not fit: more
+// than 128 output channels, a box of more than 256 rows, or too little shared memory) and run
+// on the framed channels-last activation [bs][hp][wp][cp] and the repacked filter bank.
+bool halo_plan(int64_t bs, int64_t cp, int64_t hp, int64_t wp, int64_t c_out, int fh, int fw,
+               int *block_n, int *halo_rows, int *stages, int *smem_bytes);
+int run_halo(ag_device *dev, const __nv_bfloat16 *act_rows, const __nv_bfloat16 *wk, int64_t bs,
+             int64_t cp, int64_t hp, int64_t wp, int fh, int fw, int64_t c_out, int64_t out_h,
+             int64_t out_w, const __nv_bfloat16 *bias, bool relu, __nv_bfloat16 *out_nhwc);
+
 // True when the tensor-core weight-gradient kernel takes the problem: stride 1,
 // dilation 1, at least 32 output channels, filter width up to 8, at least 4096
 // output pixels.  Few input channels are zero-padded to 64.

@@ -155,6 +155,30 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, 
     return d;
 }
 
+// Two accumulator values -> one packed bf16 pair with the layer's epilogue:
+// round the sums to bf16, add the bias in f32 and round again, ReLU (x >= 0 ? x : 0).
+// Conversions are the slow instructions of an epilogue, so the pair is rounded with
+// one packed conversion, unpacked with shifts, and packed again only when a bias
+// changed the values.
+__device__ __forceinline__ uint32_t bf16_pair_epilogue(uint32_t acc0, uint32_t acc1, float b0,
+                                                       float b1, bool has_bias, bool relu) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(acc0), __uint_as_float(acc1));
+    uint32_t u = *reinterpret_cast<uint32_t *>(&h);
+    if (!has_bias && !relu) return u;
+    float x0 = __uint_as_float(u << 16), x1 = __uint_as_float(u & 0xffff0000u);
+    if (has_bias) {
+        h = __floats2bfloat162_rn(x0 + b0, x1 + b1);
+        u = *reinterpret_cast<uint32_t *>(&h);
+        if (!relu) return u;
+        x0 = __uint_as_float(u << 16);
+        x1 = __uint_as_float(u & 0xffff0000u);
+    }
+    // ReLU on exact bf16 values: clear a half whose value is negative (or NaN)
+    const uint32_t lo = (x0 >= 0.f) ? (u & 0x0000ffffu) : 0u;
+    const uint32_t hi = (x1 >= 0.f) ? (u & 0xffff0000u) : 0u;
+    return lo | hi;
+}
+
 // Instruction descriptor for kind::f16: f32 accumulate, bf16 A and B.
 __host__ __device__ constexpr uint32_t make_idesc(bool a_mn_major, bool b_mn_major, int m, int n) {
     return (1u << 4)                         // D format: f32
