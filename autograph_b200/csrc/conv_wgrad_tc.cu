@@ -140,7 +140,11 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(true, true, WG_BLOCK_M, NT);
+            // The x tiles of the taps of a filter row lie one after the other in the stage and
+            // their accumulators one after the other in TMEM, so several taps are ONE operand
+            // of up to 256 columns: one tcgen05.mma per k step covers them all, which moves
+            // far fewer operand bytes per flop than one 64-column instruction per tap.
+            const int taps_per_mma = min(p.FW, 256 / NT);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -153,16 +157,18 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
                 tc_fence_after();
                 const uint32_t a_base = smem_u32(smem + stage * p.stage_bytes);
                 const uint32_t b_base = a_base + WG_A_BYTES;
-                for (int g = 0; g < p.FW; ++g) {
+                for (int g0 = 0; g0 < p.FW; g0 += taps_per_mma) {
+                    const int n_cols = min(taps_per_mma, p.FW - g0) * NT;
+                    const uint32_t idesc = make_idesc(true, true, WG_BLOCK_M, n_cols);
 #pragma unroll
                     for (int k = 0; k < WG_CHUNK / WG_UMMA_K; ++k) {
                         // 16 pixel rows of 128 bytes per k step
                         const uint64_t a_desc =
                             make_smem_desc(a_base + k * WG_UMMA_K * 128, WG_ATOM_BYTES, 1024);
                         const uint64_t b_desc =
-                            make_smem_desc(b_base + g * ATOMS_N * WG_ATOM_BYTES + k * WG_UMMA_K * 128,
+                            make_smem_desc(b_base + g0 * ATOMS_N * WG_ATOM_BYTES + k * WG_UMMA_K * 128,
                                            WG_ATOM_BYTES, 1024);
-                        umma_bf16(tmem_base + (uint32_t)(g * NT), a_desc, b_desc, idesc,
+                        umma_bf16(tmem_base + (uint32_t)(g0 * NT), a_desc, b_desc, idesc,
                                   (c > c_begin || k > 0) ? 1u : 0u);
                     }
                 }

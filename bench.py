@@ -407,7 +407,7 @@ def gemm_sweep(torch, ag, dev, peaks, sampler):
     results = []
     roof = None
     for dtype, name in [(torch.bfloat16, "bf16"), (torch.float32, "f32")]:
-        for n in [1024, 4096, 8192]:
+        for n in [256, 1024, 4096, 8192]:
             layouts = ["nn", "tn", "nt"] if n == 4096 else ["nn"]
             a = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
             b = (torch.rand((n, n), device=dev.torch_device) * 2 - 1).to(dtype)
@@ -433,7 +433,10 @@ def gemm_sweep(torch, ag, dev, peaks, sampler):
                 if name == "bf16" and n == 4096 and layout == "nn":
                     roof = {"bound": "tensor", "kernel": "gemm_bf16_tc2_kernel (tcgen05, cta_group::2), 4096^3 nn",
                             "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": tf / peaks["bf16_tflops"], "traffic": None,
+                            "frac": tf / peaks["bf16_tflops"],
+                            # dram bytes of one launch from the ncu capture summarised in
+                            # profiles/gemm_bf16_tcgen05_4096_nn.md (A + B + C = 100.7 MB algorithmic)
+                            "traffic": 90.0e6,
                             "peak_source": peaks["source"] + " (burst: kernel timed alone)"}
             del a, b, c
     return results, roof
