@@ -19,6 +19,7 @@
 
 #include <cstdlib>
 
+#include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "tc_ptx.cuh"
 
@@ -46,6 +47,11 @@ struct Params {
     __nv_bfloat16 *C;
     int *status;       // device status word (0 = ok)
     uint32_t lbo_k;    // leading byte offset used for K-major operands
+    // split-k: a work item is (output tile, k slice); slices write f32 partial tiles to
+    // partial[slice][M][N] and a second kernel adds them in slice order
+    float *partial;    // null: one slice, results go to C
+    int splits;
+    int kb_per_split;  // 64-wide k blocks per slice
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int &m_blk, int &n_blk) {
@@ -81,8 +87,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     const int num_m = (p.M + BLOCK_M - 1) / BLOCK_M;
     const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
-    const int num_tiles = num_m * num_n;
-    const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int out_tiles = num_m * num_n;
+    const int num_tiles = out_tiles * p.splits;
+    const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_a);
@@ -116,8 +123,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 int m_blk, n_blk;
-                tile_coords(tile, num_m, num_n, m_blk, n_blk);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int split = tile / out_tiles;
+                tile_coords(tile - split * out_tiles, num_m, num_n, m_blk, n_blk);
+                const int kb0 = split * p.kb_per_split;
+                const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
                         atomicExch(p.status, 101);
                         ok = false;
@@ -171,6 +181,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                const int split = tile / out_tiles;
+                const int num_kb = min(total_kb, (split + 1) * p.kb_per_split) - split * p.kb_per_split;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) {
                         atomicExch(p.status, 103);
@@ -208,7 +220,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             int m_blk, n_blk;
-            tile_coords(tile, num_m, num_n, m_blk, n_blk);
+            const int split = tile / out_tiles;
+            tile_coords(tile - split * out_tiles, num_m, num_n, m_blk, n_blk);
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag)) {
                 if (lane == 0) atomicExch(p.status, 104);
                 break;
@@ -224,7 +237,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tmem_ld_32x32(taddr + chunk * 32, r);
                 tmem_ld_wait();
                 const int col0 = n_blk * BLOCK_N + chunk * 32;
-                if (row < p.M && col0 < p.N) {
+                if (p.partial != nullptr) {
+                    // raw f32 sums of this k slice
+                    if (row < p.M && col0 < p.N) {
+                        float *prow = p.partial + ((int64_t)split * p.M + row) * p.N + col0;
+                        if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                reinterpret_cast<uint4 *>(prow)[j] =
+                                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                                prow[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                } else if (row < p.M && col0 < p.N) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const int col = col0 + g * 8;
@@ -364,7 +391,7 @@ static int launch(ag_device *dev, const CUtensorMap &ta, const CUtensorMap &tb, 
                                          SMEM_BYTES));
         configured = true;
     }
-    const int tiles = (int)(ceil_div(p.M, BLOCK_M) * ceil_div(p.N, BLOCK_N));
+    const int tiles = (int)(ceil_div(p.M, BLOCK_M) * ceil_div(p.N, BLOCK_N)) * p.splits;
     const int grid = tiles < dev->sm_count ? tiles : dev->sm_count;
     kernel<<<grid, NUM_THREADS, SMEM_BYTES, dev->stream>>>(ta, tb, p);
     AG_CHECK_LAUNCH();
@@ -375,7 +402,19 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
               int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
               float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc) {
     (void)csc;
-    if (gemm_bf16_pair_enabled() && m >= 256 && n >= 256)
+    // Few output tiles and a long k (a Dense layer with tens of thousands of inputs at a
+    // small batch): slices of k become work items so that the whole GPU is used.
+    const int out_tiles = (int)(ceil_div(m, BLOCK_M) * ceil_div(n, BLOCK_N));
+    const int total_kb = (int)ceil_div(k, BLOCK_K);
+    int splits = 1, kb_per_split = total_kb;
+    if (out_tiles * 2 <= dev->sm_count && total_kb >= 16) {
+        splits = dev->sm_count / out_tiles;
+        if (splits > total_kb / 4) splits = total_kb / 4;  // at least four k blocks per slice
+        if (splits < 1) splits = 1;
+        kb_per_split = (int)ceil_div(total_kb, splits);
+        splits = (int)ceil_div(total_kb, kb_per_split);
+    }
+    if (splits == 1 && gemm_bf16_pair_enabled() && m >= 256 && n >= 256)
         return gemm_bf16_pair(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta, c, rsc, csc);
     const bool a_mn = !(csa == 1 && rsa % 8 == 0 && rsa >= k);  // else contiguous along m
     const bool b_mn = !(rsb == 1 && csb % 8 == 0 && csb >= k);  // else contiguous along n
@@ -398,10 +437,32 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
     p.C = c;
     p.status = dev->status_dev;
     p.lbo_k = 0;
-    if (a_mn && b_mn) return launch<true, true>(dev, ta, tb, p);
-    if (a_mn) return launch<true, false>(dev, ta, tb, p);
-    if (b_mn) return launch<false, true>(dev, ta, tb, p);
-    return launch<false, false>(dev, ta, tb, p);
+    p.partial = nullptr;
+    p.splits = splits;
+    p.kb_per_split = kb_per_split;
+    if (splits > 1) {
+        void *ws = nullptr;
+        AG_TRY(workspace(dev, sizeof(float) * (size_t)splits * (size_t)m * (size_t)n, &ws));
+        p.partial = (float *)ws;
+    }
+    if (a_mn && b_mn)
+        AG_TRY((launch<true, true>(dev, ta, tb, p)));
+    else if (a_mn)
+        AG_TRY((launch<true, false>(dev, ta, tb, p)));
+    else if (b_mn)
+        AG_TRY((launch<false, true>(dev, ta, tb, p)));
+    else
+        AG_TRY((launch<false, false>(dev, ta, tb, p)));
+    if (splits > 1) {
+        // fixed slice order: the result does not depend on scheduling
+        using Epi = simt::StridedEpilogue<__nv_bfloat16>;
+        Epi E{c, rsc, 1, alpha, beta, false, n};
+        const int64_t plane = (int64_t)m * n;
+        simt::splitk_reduce_kernel<Epi><<<(unsigned)ceil_div(plane, 256), 256, 0, dev->stream>>>(
+            p.partial, plane, splits, m, n, E);
+        AG_CHECK_LAUNCH();
+    }
+    return AG_OK;
 }
 
 }  // namespace tc

@@ -433,15 +433,71 @@ __global__ void sgd_momentum_kernel(T *__restrict__ w, const T *__restrict__ g, 
     }
 }
 
+// Any window, any width: a CTA stages a run of whole planes in shared memory with
+// 16-byte loads (the staged copy keeps the alignment of the global run) and takes the
+// window maxima from there; consecutive threads write consecutive outputs.
+template <class T>
+__global__ void max_pool2_staged_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t planes,
+                                        int ih, int iw, int oh, int ow, int h, int w, int sh,
+                                        int sw, int per_cta) {
+    extern __shared__ __align__(16) unsigned char staged_raw[];
+    T *s = reinterpret_cast<T *>(staged_raw);
+    constexpr int V = 16 / (int)sizeof(T);
+    const int plane_len = ih * iw;
+    for (int64_t p0 = (int64_t)blockIdx.x * per_cta; p0 < planes;
+         p0 += (int64_t)gridDim.x * per_cta) {
+        const int np = (int)min((int64_t)per_cta, planes - p0);
+        const int n = np * plane_len;
+        const T *base = x + p0 * plane_len;
+        const int shift = (int)((reinterpret_cast<uintptr_t>(base) & 15) / sizeof(T));
+        const int head = min(n, (V - shift) % V);
+        const int nv = (n - head) / V;
+        const int tail0 = head + nv * V;
+        for (int i = threadIdx.x; i < head; i += blockDim.x) s[shift + i] = base[i];
+        for (int v = threadIdx.x; v < nv; v += blockDim.x)
+            *reinterpret_cast<uint4 *>(s + shift + head + v * V) =
+                *reinterpret_cast<const uint4 *>(base + head + v * V);
+        for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) s[shift + i] = base[i];
+        __syncthreads();
+        const int outs = np * oh * ow;
+        T *dst = y + p0 * oh * ow;
+        for (int i = threadIdx.x; i < outs; i += blockDim.x) {
+            const int wid = i % ow;
+            const int t = i / ow;
+            const int hid = t % oh, plane = t / oh;
+            const T *win = s + shift + plane * plane_len + hid * sh * iw + wid * sw;
+            float m = to_f32(win[0]);
+            for (int fi = 0; fi < h; ++fi)
+                for (int fj = 0; fj < w; ++fj) {
+                    const float v = to_f32(win[fi * iw + fj]);
+                    if (v > m) m = v;  // the first maximum wins; NaNs never win after the first cell
+                }
+            dst[i] = from_f32<T>(m);
+        }
+        __syncthreads();
+    }
+}
+
 template <class T>
 static int pool_forward(ag_device *dev, const T *x, T *y, int64_t planes, int ih, int iw, int oh,
                         int ow, int h, int w, int sh, int sw) {
     const int threads = 256;
     constexpr int V = Vec16<T>::N;
+    const int64_t plane_bytes = (int64_t)ih * iw * (int64_t)sizeof(T);
     if (h == 2 && w == 2 && sh == 2 && sw == 2 && iw % V == 0 && aligned16(x)) {
         const int64_t items = planes * oh * (iw / V);
         max_pool2_2x2_kernel<T><<<grid_for(items, threads, dev->sm_count), threads, 0,
                                   dev->stream>>>(x, y, planes, ih, iw, oh, ow);
+    } else if (plane_bytes <= 40 * 1024 && planes >= dev->sm_count) {
+        // a run of whole planes per CTA, about four CTAs per SM
+        int per_cta = (int)((40 * 1024) / plane_bytes);
+        const int64_t spread = ceil_div(planes, (int64_t)dev->sm_count * 4);
+        if (per_cta > spread) per_cta = (int)(spread < 1 ? 1 : spread);
+        const size_t smem = (size_t)per_cta * (size_t)plane_bytes + 16;
+        const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(planes, per_cta),
+                                                          (int64_t)dev->sm_count * 8);
+        max_pool2_staged_kernel<T><<<grid, threads, smem, dev->stream>>>(x, y, planes, ih, iw, oh, ow,
+                                                                         h, w, sh, sw, per_cta);
     } else {
         const int64_t items = planes * oh * ow;
         max_pool2_kernel<T><<<grid_for(items, threads, dev->sm_count), threads, 0, dev->stream>>>(

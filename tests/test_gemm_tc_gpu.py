@@ -85,3 +85,30 @@ def test_bf16_4096_sampled(dev, layout):
     cols = rng.choice(n, 32, replace=False)
     ref = av.astype(np.float64) @ bv[:, cols].astype(np.float64)
     _check(c[:, cols], ref)
+
+
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+@pytest.mark.parametrize("shape", [(256, 25088, 512), (130, 4100, 264)])
+def test_bf16_split_k(dev, layout, shape):
+    """Few output tiles and a long k: slices of k become work items (f32 partial tiles, added
+    in a fixed order).  Within 1e-2 of an f64 product, identical from run to run, and exact
+    with alpha / beta on small integers."""
+    m, k, n = shape
+    rng = np.random.default_rng(4000 + m)
+    a, b = _operands(rng, m, k, n, layout)
+    av, bv = _views(a, b, layout)
+    ref = av.astype(np.float64) @ bv.astype(np.float64)
+    ad, bd = dev.tensor(a, torch.bfloat16), dev.tensor(b, torch.bfloat16)
+    c1 = dev.dot(*_views(ad, bd, layout))
+    c2 = dev.dot(*_views(ad, bd, layout))
+    dev.wait()
+    assert torch.equal(c1, c2)
+    _check(c1.float().cpu().numpy(), ref)
+    ai = rng.integers(-1, 2, a.shape).astype(np.float32)
+    bi = rng.integers(-1, 2, b.shape).astype(np.float32)
+    c0 = rng.integers(-4, 5, (m, n)).astype(np.float32)
+    aiv, biv = _views(ai, bi, layout)
+    cd = dev.tensor(c0, torch.bfloat16)
+    dev.gemm(0.5, *_views(dev.tensor(ai, torch.bfloat16), dev.tensor(bi, torch.bfloat16), layout), 2.0, cd)
+    want = oracle.round_bf16((0.5 * (aiv @ biv) + 2.0 * c0).astype(np.float32))
+    assert np.array_equal(cd.float().cpu().numpy(), want)
