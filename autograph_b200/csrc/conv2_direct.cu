@@ -76,7 +76,11 @@ __global__ void __launch_bounds__(256, 2)
 
     const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
     GlobalOut<T> out{y, b0, p.oc, p.pool ? oh / 2 : oh, p.pool ? ow / 2 : ow};
-    compute_items<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
+    if (p.split > 1)
+        compute_items_split<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg,
+                                       s_bias + p.ocp + 4, p.split, out);
+    else
+        compute_items<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
 }
 
 static bool filter_supported(int fh, int fw) {
@@ -99,6 +103,21 @@ bool eligible(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int64_t oc,
     return bytes <= 96 * 1024;
 }
 
+// One image per CTA and few work items (a small batch of a small layer): several threads
+// share a work item, each taking a range of input channels.
+static int channel_split(int group, int items_per_img, int ic) {
+    if (group != 1 || ic < 2 || items_per_img * 2 > 256) return 1;
+    int split = 256 / items_per_img;
+    if (split > ic) split = ic;
+    if (split > 8) split = 8;
+    const int chunk = (ic + split - 1) / split;
+    return (ic + chunk - 1) / chunk;  // no empty ranges
+}
+
+static size_t split_bytes(int split, int items_per_img) {
+    return split > 1 ? (size_t)(split - 1) * items_per_img * (PBH * PBW * OC_T) * sizeof(float) : 0;
+}
+
 template <class T, int FH, int FW, bool BWD>
 static int launch(ag_device *dev, const T *x, const T *w, const T *bias, T *y, const Params &p,
                   size_t smem, int items_per_img) {
@@ -106,7 +125,7 @@ static int launch(ag_device *dev, const T *x, const T *w, const T *bias, T *y, c
     if (smem > 48 * 1024)
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
-    int threads = ((p.group * items_per_img + 31) / 32) * 32;
+    int threads = ((p.group * items_per_img * p.split + 31) / 32) * 32;
     if (threads > 256) threads = 256;
     if (threads < 64) threads = 64;
     const unsigned grid = (unsigned)ceil_div(p.bs, p.group);
@@ -135,6 +154,9 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
     if (group < 1) group = 1;
     while (group > 1 && (int64_t)group * img_bytes + w_bytes > 100 * 1024) --group;
     p.group = group;
+    // no channel split in the forward direction: its sums must keep the order of the
+    // whole-network kernel and of the fused conv + pool call (bit-for-bit equality)
+    p.split = 1;
     const size_t smem = (size_t)(((group * p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes;
     if (fh == 5) return launch<T, 5, 5, false>(dev, x, w, bias, y, p, smem, items_per_img);
     return launch<T, 3, 3, false>(dev, x, w, bias, y, p, smem, items_per_img);
@@ -175,7 +197,9 @@ int backward_input(ag_device *dev, const T *w, int64_t oc, int64_t ic, const T *
     if (group < 1) group = 1;
     while (group > 1 && (int64_t)group * img_bytes + w_bytes > 100 * 1024) --group;
     p.group = group;
-    const size_t smem = (size_t)(((group * p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes;
+    p.split = channel_split(group, items_per_img, p.ic);
+    const size_t smem = (size_t)(((group * p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes +
+                        split_bytes(p.split, items_per_img);
     if (fh == 5) return launch<T, 5, 5, true>(dev, dy, w, nullptr, dx, p, smem, items_per_img);
     return launch<T, 3, 3, true>(dev, dy, w, nullptr, dx, p, smem, items_per_img);
 }

@@ -34,6 +34,7 @@ struct Params {
     int group;       // images per CTA
     int ocp;         // oc rounded up to a multiple of 2 (weight row pitch in shared memory)
     bool relu, pool;
+    int split;       // threads per work item (ranges of input channels), stand-alone kernel only
 };
 
 constexpr int OC_T = 2;  // output channels per thread
@@ -64,40 +65,150 @@ __device__ __forceinline__ void stage_filters(const T *__restrict__ w, const T *
         s_bias[i] = (bias != nullptr && i < oc) ? to_f32(bias[i]) : 0.f;
 }
 
-// The work of one CTA once images, filters and bias are in shared memory.
-// Work item = (image, 2x4 pixel block, pair of output channels); consecutive
-// threads take consecutive channel pairs of one block, so a filter tap is one
-// 8-byte shared-memory load per thread (contiguous across the channel pairs)
-// and the input patch loads broadcast.  Per input channel a thread keeps the
-// (FH+1) x (FW+3) patch in registers: 16 FFMAs per weight load.
-//
+// One work item = (image, 2x4 pixel block, pair of output channels).
+struct Item {
+    int g, oc0, y0, x0;
+};
+
+__device__ __forceinline__ Item decode_item(int item, int items_per_img, int n_ocg, int nbx) {
+    Item it;
+    it.g = item / items_per_img;
+    const int r = item - it.g * items_per_img;
+    const int blk = r / n_ocg, ocg = r - blk * n_ocg;
+    const int by = blk / nbx, bx = blk - by * nbx;
+    it.oc0 = ocg * OC_T;
+    it.y0 = by * PBH;
+    it.x0 = bx * PBW;
+    return it;
+}
+
+// acc += the contribution of input channels [ci0, ci1) to the item's 2x4x2 outputs.
+// Per input channel a thread keeps the (FH+1) x (FW+3) patch in registers: 16 FFMAs per
+// 8-byte weight load; the patch rows are read with 16-byte loads when the row length
+// allows it.
+template <int FH, int FW>
+__device__ __forceinline__ void accumulate_item(float (&acc)[PBH][PBW][OC_T], const float *s_img,
+                                                const float *s_w, const Params &p, const Item &it,
+                                                int ci0, int ci1) {
+    const int img_elems = p.ic * p.ih * p.iw;
+    // Blocks at the right edge may hang over by two pixels (ow is even but not always
+    // a multiple of four): clamp their reads, drop their results.
+    const int col_max = p.iw - 1 - it.x0;
+    const float *img = s_img + it.g * img_elems + it.y0 * p.iw + it.x0;
+    // Rows whose length is a multiple of four floats keep every patch row 16-byte
+    // aligned (x0 is a multiple of four): two or three 16-byte loads per row.  A block
+    // at the right edge may then read a few floats past its row (the next row, or the
+    // buffer that follows the images); only outputs that are dropped use them.
+    const bool vec_rows = (p.iw & 3) == 0;
+    for (int ci = ci0; ci < ci1; ++ci) {
+        constexpr int PW = FW + PBW - 1;
+        float patch[FH + PBH - 1][PW];
+        const float *pi = img + ci * p.ih * p.iw;
+        if (vec_rows) {
+#pragma unroll
+            for (int a = 0; a < FH + PBH - 1; ++a) {
+                const float4 *prow = reinterpret_cast<const float4 *>(pi + a * p.iw);
+#pragma unroll
+                for (int q = 0; q < (PW + 3) / 4; ++q) {
+                    const float4 v = prow[q];
+                    if (4 * q + 0 < PW) patch[a][4 * q + 0] = v.x;
+                    if (4 * q + 1 < PW) patch[a][4 * q + 1] = v.y;
+                    if (4 * q + 2 < PW) patch[a][4 * q + 2] = v.z;
+                    if (4 * q + 3 < PW) patch[a][4 * q + 3] = v.w;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int a = 0; a < FH + PBH - 1; ++a) {
+                const float *prow = pi + a * p.iw;
+#pragma unroll
+                for (int b = 0; b < PW; ++b) patch[a][b] = prow[min(b, col_max)];
+            }
+        }
+        const float *wc = s_w + ci * FH * FW * p.ocp + it.oc0;
+#pragma unroll
+        for (int fi = 0; fi < FH; ++fi)
+#pragma unroll
+            for (int fj = 0; fj < FW; ++fj) {
+                const float2 wv = *reinterpret_cast<const float2 *>(wc + (fi * FW + fj) * p.ocp);
+#pragma unroll
+                for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                    for (int b = 0; b < PBW; ++b) {
+                        acc[a][b][0] = fmaf(patch[fi + a][fj + b], wv.x, acc[a][b][0]);
+                        acc[a][b][1] = fmaf(patch[fi + a][fj + b], wv.y, acc[a][b][1]);
+                    }
+            }
+    }
+}
+
+// Epilogue of one item: round to T, bias, relu, optional 2x2 max pool.
 // Results leave through `out`:
 //   out.pooled(g, oc, py, px, v)  one value of the 2x2 / stride-2 max pool (p.pool)
 //   out.plain(g, oc, y, x, v)     one convolution output                  (!p.pool)
 // v has been rounded to T (after the sum and again after the bias) like a
 // store / reload of the layer's output would.
 template <class T, int FH, int FW, class Out>
+__device__ __forceinline__ void finish_item(const float (&acc)[PBH][PBW][OC_T],
+                                            const float *s_bias, bool has_bias, const Params &p,
+                                            const Item &it, Out out) {
+    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;  // both even
+#pragma unroll
+    for (int o = 0; o < OC_T; ++o) {
+        const int oc = it.oc0 + o;
+        if (oc >= p.oc) break;
+        float v[PBH][PBW];
+#pragma unroll
+        for (int a = 0; a < PBH; ++a)
+#pragma unroll
+            for (int b = 0; b < PBW; ++b) {
+                float t = to_f32(from_f32<T>(acc[a][b][o]));
+                if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
+                if (p.relu) t = (t >= 0.f) ? t : 0.f;
+                v[a][b] = t;
+            }
+        if (p.pool) {
+            const int ph = oh / 2, pw = ow / 2;
+#pragma unroll
+            for (int wy = 0; wy < PBH / 2; ++wy)
+#pragma unroll
+                for (int wx = 0; wx < PBW / 2; ++wx) {
+                    const int py = it.y0 / 2 + wy, px = it.x0 / 2 + wx;
+                    if (py < ph && px < pw) {
+                        // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
+                        float m = v[2 * wy][2 * wx];
+                        if (v[2 * wy][2 * wx + 1] > m) m = v[2 * wy][2 * wx + 1];
+                        if (v[2 * wy + 1][2 * wx] > m) m = v[2 * wy + 1][2 * wx];
+                        if (v[2 * wy + 1][2 * wx + 1] > m) m = v[2 * wy + 1][2 * wx + 1];
+                        out.pooled(it.g, oc, py, px, m);
+                    }
+                }
+        } else {
+#pragma unroll
+            for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                for (int b = 0; b < PBW; ++b)
+                    if (it.y0 + a < oh && it.x0 + b < ow)
+                        out.plain(it.g, oc, it.y0 + a, it.x0 + b, v[a][b]);
+        }
+    }
+}
+
+// The work of one CTA once images, filters and bias are in shared memory.
+// Consecutive threads take consecutive channel pairs of one pixel block, so a filter
+// tap is one 8-byte shared-memory load per thread (contiguous across the channel
+// pairs) and the input patch loads broadcast.
+template <class T, int FH, int FW, class Out>
 __device__ __forceinline__ void compute_items(const float *s_img, const float *s_w,
                                               const float *s_bias, bool has_bias, const Params &p,
                                               int nimg, Out out) {
-    const int img_elems = p.ic * p.ih * p.iw;
-    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;  // both even
+    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
     const int nby = oh / PBH, nbx = (ow + PBW - 1) / PBW;
     const int n_ocg = p.ocp / OC_T;
     const int items_per_img = n_ocg * nby * nbx;
     const int items = nimg * items_per_img;
-
     for (int item = threadIdx.x; item < items; item += blockDim.x) {
-        const int g = item / items_per_img;
-        int r = item - g * items_per_img;
-        const int blk = r / n_ocg, ocg = r - blk * n_ocg;
-        const int by = blk / nbx, bx = blk - by * nbx;
-        const int oc0 = ocg * OC_T;
-        const int y0 = by * PBH, x0 = bx * PBW;
-        // Blocks at the right edge may hang over by two pixels (ow is even but not always
-        // a multiple of four): clamp their reads, drop their results.
-        const int col_max = p.iw - 1 - x0;
-
+        const Item it = decode_item(item, items_per_img, n_ocg, nbx);
         float acc[PBH][PBW][OC_T];
 #pragma unroll
         for (int a = 0; a < PBH; ++a)
@@ -105,93 +216,63 @@ __device__ __forceinline__ void compute_items(const float *s_img, const float *s
             for (int b = 0; b < PBW; ++b)
 #pragma unroll
                 for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
+        accumulate_item<FH, FW>(acc, s_img, s_w, p, it, 0, p.ic);
+        finish_item<T, FH, FW>(acc, s_bias, has_bias, p, it, out);
+    }
+}
 
-        const float *img = s_img + g * img_elems + y0 * p.iw + x0;
-        // Rows whose length is a multiple of four floats keep every patch row 16-byte
-        // aligned (x0 is a multiple of four): two or three 16-byte loads per row.  A block
-        // at the right edge may then read a few floats past its row (the next row, or the
-        // buffer that follows the images); only outputs that are dropped use them.
-        const bool vec_rows = (p.iw & 3) == 0;
-        for (int ci = 0; ci < p.ic; ++ci) {
-            constexpr int PW = FW + PBW - 1;
-            float patch[FH + PBH - 1][PW];
-            const float *pi = img + ci * p.ih * p.iw;
-            if (vec_rows) {
+// The same for a CTA with few work items (one image of a small layer): `split` threads
+// share an item, each taking a contiguous range of input channels; the partial sums meet
+// in shared memory (red: [split][items][16] floats) and are added in range order by the
+// thread of the first range, which also runs the epilogue.  Needs items * split <= blockDim.x;
+// all threads of the CTA must call it.
+template <class T, int FH, int FW, class Out>
+__device__ __forceinline__ void compute_items_split(const float *s_img, const float *s_w,
+                                                    const float *s_bias, bool has_bias,
+                                                    const Params &p, int nimg, float *red, int split,
+                                                    Out out) {
+    constexpr int NACC = PBH * PBW * OC_T;
+    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
+    const int nby = oh / PBH, nbx = (ow + PBW - 1) / PBW;
+    const int n_ocg = p.ocp / OC_T;
+    const int items_per_img = n_ocg * nby * nbx;
+    const int items = nimg * items_per_img;
+    const int item = threadIdx.x % items, part = threadIdx.x / items;
+    const bool active = part < split;
+    const Item it = decode_item(item, items_per_img, n_ocg, nbx);
+    float acc[PBH][PBW][OC_T];
 #pragma unroll
-                for (int a = 0; a < FH + PBH - 1; ++a) {
-                    const float4 *prow = reinterpret_cast<const float4 *>(pi + a * p.iw);
+    for (int a = 0; a < PBH; ++a)
 #pragma unroll
-                    for (int q = 0; q < (PW + 3) / 4; ++q) {
-                        const float4 v = prow[q];
-                        if (4 * q + 0 < PW) patch[a][4 * q + 0] = v.x;
-                        if (4 * q + 1 < PW) patch[a][4 * q + 1] = v.y;
-                        if (4 * q + 2 < PW) patch[a][4 * q + 2] = v.z;
-                        if (4 * q + 3 < PW) patch[a][4 * q + 3] = v.w;
-                    }
-                }
-            } else {
+        for (int b = 0; b < PBW; ++b)
 #pragma unroll
-                for (int a = 0; a < FH + PBH - 1; ++a) {
-                    const float *prow = pi + a * p.iw;
-#pragma unroll
-                    for (int b = 0; b < PW; ++b) patch[a][b] = prow[min(b, col_max)];
-                }
-            }
-            const float *wc = s_w + ci * FH * FW * p.ocp + oc0;
-#pragma unroll
-            for (int fi = 0; fi < FH; ++fi)
-#pragma unroll
-                for (int fj = 0; fj < FW; ++fj) {
-                    const float2 wv = *reinterpret_cast<const float2 *>(wc + (fi * FW + fj) * p.ocp);
-#pragma unroll
-                    for (int a = 0; a < PBH; ++a)
-#pragma unroll
-                        for (int b = 0; b < PBW; ++b) {
-                            acc[a][b][0] = fmaf(patch[fi + a][fj + b], wv.x, acc[a][b][0]);
-                            acc[a][b][1] = fmaf(patch[fi + a][fj + b], wv.y, acc[a][b][1]);
-                        }
-                }
-        }
-
-        // ---- epilogue: round to T, bias, relu, optional 2x2 max pool ---------------
-#pragma unroll
-        for (int o = 0; o < OC_T; ++o) {
-            const int oc = oc0 + o;
-            if (oc >= p.oc) break;
-            float v[PBH][PBW];
+            for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
+    if (active) {
+        const int chunk = (p.ic + split - 1) / split;
+        const int ci0 = part * chunk, ci1 = min(p.ic, ci0 + chunk);
+        accumulate_item<FH, FW>(acc, s_img, s_w, p, it, ci0, ci1);
+        if (part > 0) {
+            float *dst = red + ((part - 1) * items + item) * NACC;
 #pragma unroll
             for (int a = 0; a < PBH; ++a)
 #pragma unroll
-                for (int b = 0; b < PBW; ++b) {
-                    float t = to_f32(from_f32<T>(acc[a][b][o]));
-                    if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
-                    if (p.relu) t = (t >= 0.f) ? t : 0.f;
-                    v[a][b] = t;
-                }
-            if (p.pool) {
-                const int ph = oh / 2, pw = ow / 2;
+                for (int b = 0; b < PBW; ++b)
 #pragma unroll
-                for (int wy = 0; wy < PBH / 2; ++wy)
-#pragma unroll
-                    for (int wx = 0; wx < PBW / 2; ++wx) {
-                        const int py = y0 / 2 + wy, px = x0 / 2 + wx;
-                        if (py < ph && px < pw) {
-                            // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
-                            float m = v[2 * wy][2 * wx];
-                            if (v[2 * wy][2 * wx + 1] > m) m = v[2 * wy][2 * wx + 1];
-                            if (v[2 * wy + 1][2 * wx] > m) m = v[2 * wy + 1][2 * wx];
-                            if (v[2 * wy + 1][2 * wx + 1] > m) m = v[2 * wy + 1][2 * wx + 1];
-                            out.pooled(g, oc, py, px, m);
-                        }
-                    }
-            } else {
-#pragma unroll
-                for (int a = 0; a < PBH; ++a)
-#pragma unroll
-                    for (int b = 0; b < PBW; ++b)
-                        if (y0 + a < oh && x0 + b < ow) out.plain(g, oc, y0 + a, x0 + b, v[a][b]);
-            }
+                    for (int o = 0; o < OC_T; ++o) dst[(a * PBW + b) * OC_T + o] = acc[a][b][o];
         }
+    }
+    __syncthreads();
+    if (active && part == 0) {
+        for (int s = 1; s < split; ++s) {
+            const float *src = red + ((s - 1) * items + item) * NACC;
+#pragma unroll
+            for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                for (int b = 0; b < PBW; ++b)
+#pragma unroll
+                    for (int o = 0; o < OC_T; ++o) acc[a][b][o] += src[(a * PBW + b) * OC_T + o];
+        }
+        finish_item<T, FH, FW>(acc, s_bias, has_bias, p, it, out);
     }
 }
 

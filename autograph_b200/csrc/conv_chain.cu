@@ -168,6 +168,7 @@ static size_t make_plan(Plan *pl, int64_t bs, int64_t ic, int64_t ih, int64_t iw
         sp.p.group = ROWS;
         sp.p.relu = cs.relu != 0;
         sp.p.pool = pool;
+        sp.p.split = 1;
         sp.w_off = take((int64_t)c * f * f * sp.p.ocp);
         sp.bias_off = take(sp.p.ocp);
         const int64_t oh = h - f + 1, ow = w - f + 1;

@@ -51,6 +51,8 @@ struct TrainEntry {
     int64_t bs = 0, c = 0, h = 0, w = 0;
     float lr = 0.f, momentum = 0.f, grad_scale = 1.f;
     bool use_momentum = false;
+    bool with_update = true;   // the optimizer step is part of the graph
+    bool from_device = false;  // inputs are device buffers (copied device to device)
     Tensor x_stage, t_stage;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -678,15 +680,20 @@ void apply_update(ag_model *m, float lr) {
 // call with the same shape and optimizer scalars on.  Returns false when the step has to
 // run eagerly (pageable host memory, graphs disabled, capture failed).
 bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, int64_t bs, int64_t c,
-                      int64_t h, int64_t w, float lr, float *loss_host) {
-    if (!m->graphs_enabled || bs <= 0 || !is_pinned_host(x_host) || !is_pinned_host(t_host))
-        return false;
+                      int64_t h, int64_t w, float lr, float *loss_host, bool with_update = true,
+                      bool from_device = false) {
+    // x_host / t_host are device pointers when from_device is set (the data-parallel path:
+    // forward and backward only, the caller all-reduces the gradient bucket and updates).
+    if (!m->graphs_enabled || bs <= 0) return false;
+    if (!from_device && (!is_pinned_host(x_host) || !is_pinned_host(t_host))) return false;
+    const cudaMemcpyKind kin = from_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
     cudaStream_t stream = (cudaStream_t)ag_device_stream(m->dev);
     TrainEntry *e = nullptr;
     for (auto &t : m->train_graphs)
         if (t.bs == bs && t.c == c && t.h == h && t.w == w && t.lr == lr &&
             t.momentum == m->momentum && t.use_momentum == m->use_momentum &&
-            t.grad_scale == m->grad_scale)
+            t.grad_scale == m->grad_scale && t.with_update == with_update &&
+            t.from_device == from_device)
             e = &t;
     if (!e) {
         if (m->train_graphs.size() >= 8) {
@@ -698,6 +705,8 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
         e->bs = bs; e->c = c; e->h = h; e->w = w;
         e->lr = lr; e->momentum = m->momentum; e->use_momentum = m->use_momentum;
         e->grad_scale = m->grad_scale;
+        e->with_update = with_update;
+        e->from_device = from_device;
         e->x_stage = Tensor::uninit(m->pool, {bs, c, h, w}, m->dtype);
         e->t_stage = Tensor::uninit(m->pool, {bs}, AG_U8);
     }
@@ -717,10 +726,10 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
     };
     if (e->exec) {
         cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->x_node, e->x_stage.data(), x_host,
-                                                    e->x_stage.nbytes(), cudaMemcpyHostToDevice),
+                                                    e->x_stage.nbytes(), kin),
                 "graph input update");
         cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->t_node, e->t_stage.data(), t_host,
-                                                    e->t_stage.nbytes(), cudaMemcpyHostToDevice),
+                                                    e->t_stage.nbytes(), kin),
                 "graph label update");
         cuda_ok(cudaGraphLaunch(e->exec, stream), "cudaGraphLaunch");
         ::ag::count_launches(e->kernels);
@@ -728,12 +737,12 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
         return true;
     }
     auto pass = [&]() {
-        cuda_ok(cudaMemcpyAsync(e->x_stage.data(), x_host, e->x_stage.nbytes(),
-                                cudaMemcpyHostToDevice, stream), "input copy");
-        cuda_ok(cudaMemcpyAsync(e->t_stage.data(), t_host, e->t_stage.nbytes(),
-                                cudaMemcpyHostToDevice, stream), "label copy");
+        cuda_ok(cudaMemcpyAsync(e->x_stage.data(), x_host, e->x_stage.nbytes(), kin, stream),
+                "input copy");
+        cuda_ok(cudaMemcpyAsync(e->t_stage.data(), t_host, e->t_stage.nbytes(), kin, stream),
+                "label copy");
         forward_backward(m, e->x_stage, e->t_stage, (float *)m->loss_dev.data());
-        apply_update(m, lr);
+        if (with_update) apply_update(m, lr);
         cuda_ok(cudaMemcpyAsync(m->loss_pinned, m->loss_dev.data(), sizeof(float),
                                 cudaMemcpyDeviceToHost, stream), "loss copy");
     };
@@ -985,9 +994,13 @@ int ag_model_train_forward_backward(ag_model *model, const void *x_dev, const ui
     AG_REQUIRE(model && t_dev && loss_host, AG_ERR_INVALID, "null argument");
     AG_ENTER(model->dev);
     AG_HOST_GUARD({
-        Tensor x = input_tensor(model, x_dev, false, bs, c, h, w);
-        Tensor t = Tensor::external(model->dev, const_cast<uint8_t *>(t_dev), {bs}, AG_U8);
-        *loss_host = forward_backward(model, x, t);
+        if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+        if (!x_dev && bs > 0) throw Error(AG_ERR_INVALID, "input pointer is null");
+        if (!train_step_graph(model, x_dev, t_dev, bs, c, h, w, 0.f, loss_host, false, true)) {
+            Tensor x = input_tensor(model, x_dev, false, bs, c, h, w);
+            Tensor t = Tensor::external(model->dev, const_cast<uint8_t *>(t_dev), {bs}, AG_U8);
+            *loss_host = forward_backward(model, x, t);
+        }
         if (grad_bucket) *grad_bucket = model->grads.data();
         if (grad_len) *grad_len = model->bucket_len;
     })
