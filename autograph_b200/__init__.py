@@ -218,6 +218,37 @@ class Device:
                                                  rl, _ptr(y)))
         return y
 
+    # ---- 1-D wrappers: ≙ Conv1 / MaxPool1 (layer.rs:1007-1033, 1173-1191), which reshape
+    # [n, c, l] to [n, c, l, 1] and call the 2-D operators
+    def conv1_forward(self, x, w, bias=None, padding=0, stride=1, dilation=1, relu=False):
+        n, c, l = x.shape
+        oc, ic, f = w.shape
+        y = self.conv2_forward(x.reshape(n, c, l, 1), w.reshape(oc, ic, f, 1), bias=bias,
+                               padding=(padding, 0), stride=(stride, 1), dilation=(dilation, 1),
+                               relu=relu)
+        return y.reshape(n, oc, y.shape[2])
+
+    def conv1_backward_input(self, w, dy, length, padding=0, stride=1, dilation=1):
+        oc, ic, f = w.shape
+        n = dy.shape[0]
+        dx = self.conv2_backward_input(w.reshape(oc, ic, f, 1), dy.reshape(n, oc, dy.shape[2], 1),
+                                       (length, 1), padding=(padding, 0), stride=(stride, 1),
+                                       dilation=(dilation, 1))
+        return dx.reshape(n, ic, length)
+
+    def conv1_backward_weight(self, x, dy, filter, padding=0, stride=1, dilation=1):
+        n, c, l = x.shape
+        oc = dy.shape[1]
+        dw = self.conv2_backward_weight(x.reshape(n, c, l, 1), dy.reshape(n, oc, dy.shape[2], 1),
+                                        (filter, 1), padding=(padding, 0), stride=(stride, 1),
+                                        dilation=(dilation, 1))
+        return dw.reshape(oc, c, filter)
+
+    def max_pool1(self, x, size=2, stride=None):
+        n, c, l = x.shape
+        y = self.max_pool2(x.reshape(n, c, l, 1), (size, 1), (stride or size, 1))
+        return y.reshape(n, c, y.shape[2])
+
     def scaled_cast_u8(self, x_u8, alpha, dtype):
         """≙ Tensor::scaled_cast for u8 input: alpha * x in `dtype` (f32 or bf16)."""
         y = self.empty(tuple(x_u8.shape), dtype)
@@ -552,6 +583,22 @@ class Model:
         _capi.check(lib().ag_model_infer_u8(self._h, _ptr(x_host_u8), bs, c, h, w,
                                             ctypes.c_float(alpha), _ptr(out_host)))
         return out_host
+
+    def to_serde_json(self, field_names) -> str:
+        """The model as serde_json text in the reference's layout (one field name per layer,
+        as in the user's model struct); see serde_format."""
+        from . import serde_format as sf
+        params = [self.get_parameter(i) for i in range(len(self.parameter_lens))]
+        bf16 = self.dtype == _torch().bfloat16
+        return sf.dumps(sf.model_to_value(self.spec, params, field_names, bf16=bf16))
+
+    def load_serde_json(self, text: str):
+        """Loads the parameters of a stack written by to_serde_json or by the reference."""
+        from . import serde_format as sf
+        params = sf.model_from_value(sf.loads(text))
+        if [p.size for p in params] != list(self.parameter_lens):
+            raise AgError(_capi.AG_ERR_SHAPE, "checkpoint does not match the model's parameters")
+        self.set_parameters(params)
 
     def forward_device(self, x_dev, out_dev=None):
         bs, c, h, w = x_dev.shape

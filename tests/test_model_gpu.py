@@ -152,3 +152,19 @@ def test_default_initialiser_distribution(dev):
             assert abs(w.mean()) < 0.05 * a and abs(w.std() - a / np.sqrt(3)) < 0.05 * a
     for m in (m1, m2, m3):
         m.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_checkpoint_round_trip_in_the_reference_layout(dev, dtype):
+    """to_serde_json / load_serde_json: a second model loaded from the text gives the same logits."""
+    import autograph_b200 as ag
+    names = ["conv1", "relu1", "pool1", "conv2", "relu2", "pool2", "flatten", "dense1", "relu3",
+             "dense2", "relu4", "dense3"]
+    a = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=21)
+    b = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=22)
+    x = torch.rand((64, 1, 28, 28)).to(dtype).to(dev.torch_device)
+    assert not torch.equal(a.forward_device(x), b.forward_device(x))
+    b.load_serde_json(a.to_serde_json(names))
+    assert torch.equal(a.forward_device(x), b.forward_device(x))
+    a.close()
+    b.close()
