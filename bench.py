@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--quick]
 
 A step is one LeNet5 forward pass over one batch of 1000 synthetic images in f32
-(BASELINE configs[0], the configuration the metric "LeNet5 infer img/s (bs1000)" is
+(benchmark configuration 0, the one the metric "LeNet5 infer img/s (bs1000)" is
 quoted on).  With N > 1 every rank (one process per GPU, launched by torchrun) runs the
 same step on its own 1000-image shard: inference shards by batch with no collective, so
 scaling is weak and `value` is the images all ranks processed divided by the slowest
@@ -159,7 +159,7 @@ def run_reference(args):
         "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "LeNet5 inference f32, batch 1000 per step (BASELINE configs[0])",
+        "config": {"workload": "LeNet5 inference f32, batch 1000 per step (benchmark configuration 0)",
                    "note": "CPU restatement of the reference's host path (oracle/); the reference "
                            "itself is Rust and cannot be built on this box"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
@@ -257,7 +257,7 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "LeNet5 inference f32, batch 1000 per step per GPU (BASELINE configs[0])",
+        "config": {"workload": "LeNet5 inference f32, batch 1000 per step per GPU (benchmark configuration 0)",
                    "global_batch": BATCH * world, "parallelism": f"dp{world} (batch shards, no collective)",
                    "l2": f"inputs rotate over {ROTATE} batches (200 MB > 126 MB L2)",
                    "peaks": peaks["source"]},
@@ -391,7 +391,7 @@ def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):
     roof = {"bound": "hbm", "kernel": name, "achieved": st["gbs"], "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": st["gbs"] / peaks["hbm_gbs"],
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch at batch 1000, from the
-            # ncu capture summarised in profiles/lenet5_infer_f32_kernels.md
+            # ncu capture of this kernel (one launch, batch 1000)
             "traffic": 3373312 if B == 1000 else None,
             "peak_source": peaks["source"], "us_per_launch": st["us"],
             "algorithmic_bytes_per_launch": st["alg_bytes"],
@@ -435,7 +435,7 @@ def gemm_sweep(torch, ag, dev, peaks, sampler):
                             "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                             "frac": tf / peaks["bf16_tflops"],
                             # dram bytes of one launch from the ncu capture summarised in
-                            # profiles/gemm_bf16_tcgen05_4096_nn.md (A + B + C = 100.7 MB algorithmic)
+                            # ncu capture of this kernel (A + B + C = 100.7 MB algorithmic)
                             "traffic": 90.0e6,
                             "peak_source": peaks["source"] + " (burst: kernel timed alone)"}
             del a, b, c

@@ -21,7 +21,7 @@ def _rel(got, ref):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_lenet5_inference_bs1000(dev, dtype):
-    """BASELINE config 0: x [1000,1,28,28] U[0,1) seed 1000, default-init weights seed 2000."""
+    """Benchmark configuration 0: x [1000,1,28,28] U[0,1) seed 1000, default-init weights seed 2000."""
     import autograph_b200 as ag
     bf = dtype == torch.bfloat16
     P = _params(models.LENET5, 2000, bf)
@@ -60,7 +60,7 @@ def test_lenet5_inference_bs1000(dev, dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("momentum", [None, 0.01])
 def test_lenet5_train_step_bs100(dev, dtype, momentum):
-    """BASELINE config 2: x [100,1,28,28] seed 4000, labels seed 4001, lr 0.01."""
+    """Benchmark configuration 2: x [100,1,28,28] seed 4000, labels seed 4001, lr 0.01."""
     import autograph_b200 as ag
     bf = dtype == torch.bfloat16
     P = _params(models.LENET5, 2000, bf)
@@ -94,7 +94,7 @@ def test_lenet5_train_step_bs100(dev, dtype, momentum):
 
 
 def test_wide_stack_bf16_forward_backward(dev):
-    """BASELINE config 3 at batch 8 (the oracle's naive loops finish in seconds), bf16."""
+    """Benchmark configuration 3 at batch 8 (the oracle's naive loops finish in seconds), bf16."""
     import autograph_b200 as ag
     dtype = torch.bfloat16
     P = _params(models.WIDE_STACK, 5100, True)
