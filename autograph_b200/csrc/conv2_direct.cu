@@ -83,6 +83,118 @@ __global__ void __launch_bounds__(256, 2)
         compute_items<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
 }
 
+// ---- many output channels: results staged per band of rows ------------------------
+// With 32 or more output channels the lanes of a warp are 32 channel pairs of ONE pixel
+// block, so a direct store scatters 2- or 4-byte values over 64 channel planes.  Here a CTA
+// (one image) walks bands of PBH output rows: every thread computes its items of the band
+// into a shared-memory buffer [oc][rows][width], and the band is then written out with
+// consecutive threads on consecutive addresses (for one channel the rows of a band are one
+// contiguous run of the NCHW output).
+template <class T>
+__device__ __forceinline__ void store4_from_f32(T *dst, const float4 &v);
+template <>
+__device__ __forceinline__ void store4_from_f32<float>(float *dst, const float4 &v) {
+    *reinterpret_cast<float4 *>(dst) = v;
+}
+template <>
+__device__ __forceinline__ void store4_from_f32<__nv_bfloat16>(__nv_bfloat16 *dst, const float4 &v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 q;
+    q.x = *reinterpret_cast<uint32_t *>(&lo);
+    q.y = *reinterpret_cast<uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(dst) = q;
+}
+
+struct BandOut {
+    float *buf;   // [oc][rows][width] of the current band
+    int rows, width, y0;  // band geometry in output (or pooled output) coordinates
+    __device__ __forceinline__ void pooled(int, int c, int py, int px, float v) const {
+        buf[(c * rows + (py - y0)) * width + px] = v;
+    }
+    __device__ __forceinline__ void plain(int g, int c, int yy, int xx, float v) const {
+        pooled(g, c, yy, xx, v);
+    }
+};
+
+// grid.x = bs; dynamic shared memory:
+//   float img[ic][ih][iw]; float wts[ic][FH][FW][ocp]; float bias[ocp + 4]; float band[oc][rows][width]
+template <class T, int FH, int FW>
+__global__ void __launch_bounds__(256, 2)
+    conv2_direct_banded_kernel(const T *__restrict__ x, const T *__restrict__ w,
+                               const T *__restrict__ bias, T *__restrict__ y, const Params p) {
+    extern __shared__ __align__(16) float smem[];
+    const int img_elems = p.ic * p.ih * p.iw;
+    const int taps = p.ic * FH * FW;
+    const int b = blockIdx.x;
+    float *s_img = smem;
+    float *s_w = smem + ((img_elems + 3) & ~3);
+    float *s_bias = s_w + taps * p.ocp;
+    float *s_band = s_bias + p.ocp + 4;
+    stage_contiguous<T>(x + (int64_t)b * img_elems, s_img, img_elems);
+    stage_filters<T>(w, bias, s_w, s_bias, p.oc, p.ocp, taps);
+    __syncthreads();
+
+    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
+    const int nby = oh / PBH, nbx = (ow + PBW - 1) / PBW;
+    const int n_ocg = p.ocp / OC_T;
+    const int out_h = p.pool ? oh / 2 : oh, out_w = p.pool ? ow / 2 : ow;
+    const int band_rows = p.pool ? PBH / 2 : PBH;
+    const int band_items = nbx * n_ocg;
+    const int band_elems = band_rows * out_w;  // per channel
+    T *yb = y + (int64_t)b * p.oc * out_h * out_w;
+    for (int by = 0; by < nby; ++by) {
+        BandOut out{s_band, band_rows, out_w, by * band_rows};
+        for (int i = threadIdx.x; i < band_items; i += blockDim.x) {
+            Item it;
+            it.g = 0;
+            const int bx = i / n_ocg;
+            it.oc0 = (i - bx * n_ocg) * OC_T;
+            it.y0 = by * PBH;
+            it.x0 = bx * PBW;
+            float acc[PBH][PBW][OC_T];
+#pragma unroll
+            for (int a = 0; a < PBH; ++a)
+#pragma unroll
+                for (int c = 0; c < PBW; ++c)
+#pragma unroll
+                    for (int o = 0; o < OC_T; ++o) acc[a][c][o] = 0.f;
+            accumulate_item<FH, FW>(acc, s_img, s_w, p, it, 0, p.ic);
+            finish_item<T, FH, FW>(acc, s_bias, bias != nullptr, p, it, out);
+        }
+        __syncthreads();
+        const int total = p.oc * band_elems;
+        // four elements per thread when every channel's run starts on a 4-element boundary
+        const bool vec4 = (band_elems & 3) == 0 && ((out_h * out_w) & 3) == 0 &&
+                          (reinterpret_cast<uintptr_t>(yb) % (4 * sizeof(T))) == 0 &&
+                          (reinterpret_cast<uintptr_t>(s_band) & 15) == 0;
+        if (vec4) {
+            for (int i = threadIdx.x * 4; i < total; i += blockDim.x * 4) {
+                const int c = i / band_elems, r = i - c * band_elems;
+                const float4 v = *reinterpret_cast<const float4 *>(s_band + i);
+                store4_from_f32<T>(yb + ((int64_t)c * out_h + by * band_rows) * out_w + r, v);
+            }
+        } else {
+            for (int i = threadIdx.x; i < total; i += blockDim.x) {
+                const int c = i / band_elems, r = i - c * band_elems;
+                yb[((int64_t)c * out_h + by * band_rows) * out_w + r] = from_f32<T>(s_band[i]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <class T, int FH, int FW>
+static int launch_banded(ag_device *dev, const T *x, const T *w, const T *bias, T *y,
+                         const Params &p, size_t smem) {
+    auto kernel = conv2_direct_banded_kernel<T, FH, FW>;
+    if (smem > 48 * 1024)
+        AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    kernel<<<(unsigned)p.bs, 256, smem, dev->stream>>>(x, w, bias, y, p);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
 static bool filter_supported(int fh, int fw) {
     return (fh == 5 && fw == 5) || (fh == 3 && fw == 3);
 }
@@ -157,6 +269,17 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
     // no channel split in the forward direction: its sums must keep the order of the
     // whole-network kernel and of the fused conv + pool call (bit-for-bit equality)
     p.split = 1;
+    // Many output channels, one image per CTA anyway: the banded kernel (coalesced stores).
+    if (oc >= 32 && group == 1 && bs <= 2147483647) {
+        const int out_w = pool ? ow / 2 : ow;
+        const int band_rows = pool ? PBH / 2 : PBH;
+        const size_t smem_b = (size_t)(((p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes +
+                              (size_t)p.oc * band_rows * out_w * 4;
+        if (smem_b <= 100 * 1024) {
+            if (fh == 5) return launch_banded<T, 5, 5>(dev, x, w, bias, y, p, smem_b);
+            return launch_banded<T, 3, 3>(dev, x, w, bias, y, p, smem_b);
+        }
+    }
     const size_t smem = (size_t)(((group * p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes;
     if (fh == 5) return launch<T, 5, 5, false>(dev, x, w, bias, y, p, smem, items_per_img);
     return launch<T, 3, 3, false>(dev, x, w, bias, y, p, smem, items_per_img);

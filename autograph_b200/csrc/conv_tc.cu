@@ -446,7 +446,7 @@ int to_nhwc_framed(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c
 static bool shape_ok(int64_t bs, int64_t c_in, int64_t in_h, int64_t in_w, int64_t c_out,
                      int64_t out_h, int64_t out_w, int fh, int fw) {
     if (!tc_conv_enabled() || encode_tiled_fn() == nullptr) return false;
-    if (bs <= 0 || c_in < 1 || c_out < 32 || out_h <= 0 || out_w <= 0) return false;
+    if (bs <= 0 || c_in < 16 || c_out < 32 || out_h <= 0 || out_w <= 0) return false;
     if (fh < 1 || fw < 1 || fh * fw > 49) return false;
     if (bs * out_h * out_w < 4096) return false;  // too little work for 128-pixel tiles
     if (in_h > 32768 || in_w > 32768 || bs > 65535) return false;

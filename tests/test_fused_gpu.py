@@ -19,6 +19,8 @@ CONV_SHAPES = [
     (37, 1, 28, 28, 6, 5, 5, (2, 2)), (37, 6, 12, 12, 16, 5, 5, (2, 2)),
     (3, 3, 64, 64, 64, 3, 3, (2, 2)), (1000, 1, 28, 28, 6, 5, 5, (2, 2)),
     (2, 64, 31, 31, 128, 3, 3, (2, 2)), (3, 5, 9, 11, 7, 3, 2, (2, 3)), (4, 2, 10, 10, 8, 3, 3, (3, 3)),
+    # many output channels: the banded direct kernel, with and without aligned runs
+    (5, 3, 20, 22, 34, 3, 3, (2, 2)), (3, 2, 16, 16, 48, 5, 5, (2, 2)),
 ]
 
 
