@@ -372,6 +372,18 @@ class Device:
                                                 _ptr(dy.contiguous())))
         return dx
 
+    def max_pool2_backward_from_input(self, x, dy, size=(2, 2), strides=None):
+        """The same result in one pass: x is read, the gradient written (no clone)."""
+        strides = strides or size
+        x = x.contiguous()
+        dx = self.empty(x.shape, x.dtype)
+        bs, c, ih, iw = x.shape
+        self._sync_in()
+        _capi.check(lib().ag_max_pool2_backward_from_input(
+            self._h, _dtype_code(x.dtype), _ptr(x), bs, c, ih, iw, size[0], size[1], strides[0],
+            strides[1], _ptr(dy.contiguous()), _ptr(dx)))
+        return dx
+
     def relu(self, x, inplace=False):
         x = x.contiguous()
         y = x if inplace else self.empty(x.shape, x.dtype)

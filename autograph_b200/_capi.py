@@ -101,6 +101,8 @@ _SIGNATURES = {
                                 POINTER(ConvOptions), _P]),
     "ag_max_pool2": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                              c_int32, c_int32, _P]),
+    "ag_max_pool2_backward_from_input": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
+                                                 c_int32, c_int32, c_int32, c_int32, _P, _P]),
     "ag_max_pool2_backward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, c_int32,
                                       c_int32, c_int32, c_int32, _P]),
     "ag_relu": (c_int, [_P, c_int, _P, _P, c_int64]),

@@ -182,11 +182,10 @@ static size_t make_plan(Plan *pl, int64_t bs, int64_t ic, int64_t ih, int64_t iw
         if (!dense_small::eligible(ROWS, layers[i].inputs, layers[i].outputs)) return 0;
         if (i > 0 && layers[i].inputs != layers[i - 1].outputs) return 0;
     }
-    const size_t chain_floats = dense_small::plan_chain(&pl->chain, (int)bs, n_dense, layers);
+    dense_small::plan_chain(&pl->chain, (int)bs, n_dense, layers);
     pl->xa_off = take((int64_t)pl->chain.max_k * ROWS);
     pl->xb_off = take((int64_t)pl->chain.max_k * ROWS);
     pl->red_off = take(pl->chain.red_floats);
-    (void)chain_floats;
     const size_t bytes = (size_t)off * sizeof(float);
     return bytes <= 200 * 1024 ? bytes : 0;
 }

@@ -329,9 +329,9 @@ class MaxPool2 : public Layer {
             Tensor xv = x;
             builder.edge(input.node, [=](const Tensor &dy, Tensor *) {
                 Tensor dx = Tensor::uninit(*pp, xv.shape(), xv.dtype());
-                check(ag_copy(xv.device(), dx.data(), xv.data(), xv.nbytes()));
-                check(ag_max_pool2_backward(dx.device(), dx.dtype(), dx.data(), bs, c, ih, iw, f0,
-                                            f1, s0, s1, dy.data()));
+                // clone of the input + in-place backward of the reference, in one pass
+                check(ag_max_pool2_backward_from_input(xv.device(), xv.dtype(), xv.data(), bs, c, ih,
+                                                       iw, f0, f1, s0, s1, dy.data(), dx.data()));
                 return dx;
             });
         }

@@ -170,7 +170,7 @@ __global__ void max_pool2_2x2_kernel(const T *__restrict__ x, T *__restrict__ y,
 template <class T>
 __global__ void max_pool2_backward_kernel(T *__restrict__ dx, const T *__restrict__ dy,
                                           int64_t planes, int ih, int iw, int oh, int ow, int h,
-                                          int w, int sh, int sw) {
+                                          int w, int sh, int sw) {  // in place only
     const int64_t total = planes * oh * ow;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -197,7 +197,7 @@ __global__ void max_pool2_backward_kernel(T *__restrict__ dx, const T *__restric
 // 2x2 window, stride 2, width a multiple of the vector length, 16-byte aligned rows:
 // each thread owns V/2 adjacent windows, reads and rewrites two 16-byte row segments.
 template <class T>
-__global__ void max_pool2_backward_2x2_kernel(T *__restrict__ dx, const T *__restrict__ dy,
+__global__ void max_pool2_backward_2x2_kernel(const T *src, T *dx, const T *__restrict__ dy,
                                               int64_t planes, int ih, int iw, int oh, int ow) {
     constexpr int V = Vec16<T>::N;
     const int vec_per_row = iw / V;
@@ -208,11 +208,12 @@ __global__ void max_pool2_backward_2x2_kernel(T *__restrict__ dx, const T *__res
         int64_t t = i / vec_per_row;
         int hid = (int)(t % oh);
         int64_t plane = t / oh;
-        T *r0 = dx + (plane * ih + 2 * (int64_t)hid) * iw + vx * V;
+        const int64_t off = (plane * ih + 2 * (int64_t)hid) * iw + vx * V;
+        T *r0 = dx + off;
         const T *g = dy + (plane * oh + hid) * (int64_t)ow + vx * (V / 2);
         Vec16<T> a, b, oa, ob;
-        a.raw = *reinterpret_cast<const uint4 *>(r0);
-        b.raw = *reinterpret_cast<const uint4 *>(r0 + iw);
+        a.raw = *reinterpret_cast<const uint4 *>(src + off);
+        b.raw = *reinterpret_cast<const uint4 *>(src + off + iw);
         oa.raw = make_uint4(0, 0, 0, 0);
         ob.raw = make_uint4(0, 0, 0, 0);
 #pragma unroll
@@ -242,7 +243,7 @@ __global__ void max_pool2_backward_2x2_kernel(T *__restrict__ dx, const T *__res
 // global run), works on the windows there, and writes the run back with 16-byte
 // stores, so the 2- and 4-byte window accesses never reach global memory.
 template <class T>
-__global__ void max_pool2_backward_staged_kernel(T *__restrict__ dx, const T *__restrict__ dy,
+__global__ void max_pool2_backward_staged_kernel(const T *src, T *dx, const T *__restrict__ dy,
                                                  int64_t planes, int ih, int iw, int oh, int ow,
                                                  int h, int w, int sh, int sw, int per_cta) {
     extern __shared__ __align__(16) unsigned char staged_raw[];
@@ -253,16 +254,21 @@ __global__ void max_pool2_backward_staged_kernel(T *__restrict__ dx, const T *__
          p0 += (int64_t)gridDim.x * per_cta) {
         const int np = (int)min((int64_t)per_cta, planes - p0);
         const int n = np * plane_len;
+        const T *in = src + p0 * plane_len;
         T *base = dx + p0 * plane_len;
-        const int shift = (int)((reinterpret_cast<uintptr_t>(base) & 15) / sizeof(T));
+        // the staged copy keeps the 16-byte phase of the source run; the run is written back
+        // with 16-byte stores when the destination run has the same phase (always, in place)
+        const int shift = (int)((reinterpret_cast<uintptr_t>(in) & 15) / sizeof(T));
+        const bool same_phase =
+            shift == (int)((reinterpret_cast<uintptr_t>(base) & 15) / sizeof(T));
         const int head = min(n, (V - shift) % V);
         const int nv = (n - head) / V;
         const int tail0 = head + nv * V;
-        for (int i = threadIdx.x; i < head; i += blockDim.x) s[shift + i] = base[i];
+        for (int i = threadIdx.x; i < head; i += blockDim.x) s[shift + i] = in[i];
         for (int v = threadIdx.x; v < nv; v += blockDim.x)
             *reinterpret_cast<uint4 *>(s + shift + head + v * V) =
-                *reinterpret_cast<const uint4 *>(base + head + v * V);
-        for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) s[shift + i] = base[i];
+                *reinterpret_cast<const uint4 *>(in + head + v * V);
+        for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) s[shift + i] = in[i];
         __syncthreads();
         const int windows = np * oh * ow;
         const T *g = dy + p0 * oh * ow;
@@ -285,11 +291,15 @@ __global__ void max_pool2_backward_staged_kernel(T *__restrict__ dx, const T *__
             win[am] = from_f32<T>(__fadd_rn(0.f, to_f32(g[i])));
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < head; i += blockDim.x) base[i] = s[shift + i];
-        for (int v = threadIdx.x; v < nv; v += blockDim.x)
-            *reinterpret_cast<uint4 *>(base + head + v * V) =
-                *reinterpret_cast<const uint4 *>(s + shift + head + v * V);
-        for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) base[i] = s[shift + i];
+        if (same_phase) {
+            for (int i = threadIdx.x; i < head; i += blockDim.x) base[i] = s[shift + i];
+            for (int v = threadIdx.x; v < nv; v += blockDim.x)
+                *reinterpret_cast<uint4 *>(base + head + v * V) =
+                    *reinterpret_cast<const uint4 *>(s + shift + head + v * V);
+            for (int i = tail0 + threadIdx.x; i < n; i += blockDim.x) base[i] = s[shift + i];
+        } else {
+            for (int i = threadIdx.x; i < n; i += blockDim.x) base[i] = s[shift + i];
+        }
         __syncthreads();
     }
 }
@@ -588,9 +598,10 @@ int ag_max_pool2(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int6
     AG_DISPATCH_FLOAT(dtype, T, return pool_forward<T>(dev, (const T *)x, (T *)y, bs * c, (int)ih, (int)iw, oh, ow, h, w, sh, sw););
 }
 
-int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, int64_t c,
-                          int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh, int32_t sw,
-                          const void *dy) {
+// dx = max_pool2_backward(copy of x, dy); x == dx is the in-place form of the reference.
+static int pool_backward(ag_device *dev, ag_dtype dtype, const void *x, void *dx, int64_t bs,
+                         int64_t c, int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh,
+                         int32_t sw, const void *dy) {
     AG_ENTER(dev);
     AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "max_pool2_backward %d unimplemented",
                (int)dtype);
@@ -603,15 +614,15 @@ int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, 
     const int oh = (int)((ih - h) / sh + 1), ow = (int)((iw - w) / sw + 1);
     const int64_t planes = bs * c;
     if (planes == 0) return AG_OK;
-    AG_REQUIRE(dx && dy, AG_ERR_INVALID, "null tensor pointer");
+    AG_REQUIRE(x && dx && dy, AG_ERR_INVALID, "null tensor pointer");
     const int threads = 256;
     const int vlen = dtype == AG_F32 ? 4 : 8;
     if (h == 2 && w == 2 && sh == 2 && sw == 2 && iw % vlen == 0 &&
-        (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {
+        (reinterpret_cast<uintptr_t>(dx) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         const unsigned grid2 = grid_for(planes * oh * (iw / vlen), threads, dev->sm_count);
         AG_DISPATCH_FLOAT(dtype, T,
             max_pool2_backward_2x2_kernel<T><<<grid2, threads, 0, dev->stream>>>(
-                (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow););
+                (const T *)x, (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow););
         AG_CHECK_LAUNCH();
         return AG_OK;
     }
@@ -626,16 +637,32 @@ int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, 
                                                            (int64_t)dev->sm_count * 8);
         AG_DISPATCH_FLOAT(dtype, T,
             max_pool2_backward_staged_kernel<T><<<gridp, threads, smem, dev->stream>>>(
-                (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow, h, w, sh, sw, per_cta););
+                (const T *)x, (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow, h, w, sh, sw, per_cta););
         AG_CHECK_LAUNCH();
         return AG_OK;
     }
+    // planes too large to stage: copy first (when out of place), then the in-place kernel
+    if (x != dx)
+        AG_CUDA_TRY(cudaMemcpyAsync(dx, x, (size_t)(planes * ih * iw) * dtype_size(dtype),
+                                    cudaMemcpyDeviceToDevice, dev->stream));
     const unsigned grid = grid_for(planes * oh * ow, threads, dev->sm_count);
     AG_DISPATCH_FLOAT(dtype, T,
         max_pool2_backward_kernel<T><<<grid, threads, 0, dev->stream>>>(
             (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow, h, w, sh, sw););
     AG_CHECK_LAUNCH();
     return AG_OK;
+}
+
+int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, int64_t c,
+                          int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh, int32_t sw,
+                          const void *dy) {
+    return pool_backward(dev, dtype, dx, dx, bs, c, ih, iw, h, w, sh, sw, dy);
+}
+
+int ag_max_pool2_backward_from_input(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                     int64_t c, int64_t ih, int64_t iw, int32_t h, int32_t w,
+                                     int32_t sh, int32_t sw, const void *dy, void *dx) {
+    return pool_backward(dev, dtype, x, dx, bs, c, ih, iw, h, w, sh, sw, dy);
 }
 
 int ag_bias_add(ag_device *dev, ag_dtype dtype, void *y, const void *bias, int64_t rows,

@@ -268,6 +268,13 @@ AG_API int ag_max_pool2(ag_device *dev, ag_dtype dtype, const void *x, int64_t b
 AG_API int ag_max_pool2_backward(ag_device *dev, ag_dtype dtype, void *dx, int64_t bs, int64_t c,
                                  int64_t ih, int64_t iw, int32_t h, int32_t w, int32_t sh,
                                  int32_t sw, const void *dy);
+/* The same result without the caller's copy: dx = max_pool2_backward(copy of x, dy) in one
+ * pass (x is read, dx written; x == dx is the in-place form above).  ≙ the input edge of
+ * MaxPool2::forward (layer.rs:1203-1212: clone the input, then max_pool2_backward on the clone). */
+AG_API int ag_max_pool2_backward_from_input(ag_device *dev, ag_dtype dtype, const void *x,
+                                            int64_t bs, int64_t c, int64_t ih, int64_t iw,
+                                            int32_t h, int32_t w, int32_t sh, int32_t sw,
+                                            const void *dy, void *dx);
 
 /* ----------------------------------------------------------- input pipeline */
 

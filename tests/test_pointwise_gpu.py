@@ -65,6 +65,7 @@ def test_max_pool2_golden(dev, golden, dtype):
             dy = oracle.round_bf16(dy)
             want = oracle.max_pool2_backward(x, dy)
         assert np.array_equal(_np(dev.max_pool2_backward(xd, dev.tensor(dy, dtype))), want)
+        assert np.array_equal(_np(dev.max_pool2_backward_from_input(xd, dev.tensor(dy, dtype))), want)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -81,6 +82,13 @@ def test_max_pool2_random(dev, dtype, case):
     assert np.array_equal(_np(y), want)
     dy = _prep(rng.standard_normal(want.shape), dtype)
     dx = dev.max_pool2_backward(xd, dev.tensor(dy, dtype), size, strides)
+    assert np.array_equal(_np(dx), oracle.max_pool2_backward(x, dy, size, strides))
+    dx = dev.max_pool2_backward_from_input(xd, dev.tensor(dy, dtype), size, strides)
+    assert np.array_equal(_np(dx), oracle.max_pool2_backward(x, dy, size, strides))
+    # an input that does not start on a 16-byte boundary (the staged copy keeps the source phase)
+    flat = dev.empty((x.size + 3,), dtype)
+    flat[3:].copy_(xd.reshape(-1))
+    dx = dev.max_pool2_backward_from_input(flat[3:].reshape(xd.shape), dev.tensor(dy, dtype), size, strides)
     assert np.array_equal(_np(dx), oracle.max_pool2_backward(x, dy, size, strides))
 
 
