@@ -238,6 +238,85 @@ __global__ void max_pool2_backward_2x2_kernel(const T *src, T *dx, const T *__re
     }
 }
 
+// 2x2 window, stride 2, even width and height, rows that keep pairs aligned (4 bytes for
+// bf16, 8 for f32): a thread owns one window and reads each of its two rows as one pair;
+// consecutive threads read consecutive pairs, so every load instruction covers a contiguous
+// 128 / 256 bytes.
+template <class T>
+__device__ __forceinline__ void load_pair(const T *p, float &a, float &b);
+template <>
+__device__ __forceinline__ void load_pair<float>(const float *p, float &a, float &b) {
+    const float2 v = *reinterpret_cast<const float2 *>(p);
+    a = v.x;
+    b = v.y;
+}
+template <>
+__device__ __forceinline__ void load_pair<__nv_bfloat16>(const __nv_bfloat16 *p, float &a, float &b) {
+    const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+    a = __uint_as_float(v << 16);
+    b = __uint_as_float(v & 0xffff0000u);
+}
+template <class T>
+__device__ __forceinline__ void store_pair(T *p, float a, float b);
+template <>
+__device__ __forceinline__ void store_pair<float>(float *p, float a, float b) {
+    *reinterpret_cast<float2 *>(p) = make_float2(a, b);
+}
+template <>
+__device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16 *p, float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    *reinterpret_cast<uint32_t *>(p) = *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <class T>
+__global__ void max_pool2_2x2_pair_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t planes,
+                                          int ih, int iw, int oh, int ow) {
+    const int64_t total = planes * oh * ow;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int wid = (int)(i % ow);
+        const int64_t t = i / ow;
+        const int hid = (int)(t % oh);
+        const int64_t plane = t / oh;
+        const T *r0 = x + (plane * ih + 2 * (int64_t)hid) * iw + 2 * wid;
+        float a0, a1, b0, b1;
+        load_pair<T>(r0, a0, a1);
+        load_pair<T>(r0 + iw, b0, b1);
+        float m = a0;  // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
+        if (a1 > m) m = a1;
+        if (b0 > m) m = b0;
+        if (b1 > m) m = b1;
+        y[i] = from_f32<T>(m);
+    }
+}
+
+// Gradient of the same: src holds the forward input, dx receives dy at the first maximum
+// of every window and zero elsewhere (every cell belongs to a window).  src may be dx.
+template <class T>
+__global__ void max_pool2_backward_2x2_pair_kernel(const T *src, T *dx, const T *__restrict__ dy,
+                                                   int64_t planes, int ih, int iw, int oh, int ow) {
+    const int64_t total = planes * oh * ow;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int wid = (int)(i % ow);
+        const int64_t t = i / ow;
+        const int hid = (int)(t % oh);
+        const int64_t plane = t / oh;
+        const int64_t off = (plane * ih + 2 * (int64_t)hid) * iw + 2 * wid;
+        float a0, a1, b0, b1;
+        load_pair<T>(src + off, a0, a1);
+        load_pair<T>(src + off + iw, b0, b1);
+        float m = a0;
+        int am = 0;
+        if (a1 > m) { m = a1; am = 1; }
+        if (b0 > m) { m = b0; am = 2; }
+        if (b1 > m) { m = b1; am = 3; }
+        const float g = __fadd_rn(0.f, to_f32(dy[i]));
+        store_pair<T>(dx + off, am == 0 ? g : 0.f, am == 1 ? g : 0.f);
+        store_pair<T>(dx + off + iw, am == 2 ? g : 0.f, am == 3 ? g : 0.f);
+    }
+}
+
 // Any non-overlapping window, any width: a CTA stages a run of whole planes in
 // shared memory with 16-byte loads (the staged copy keeps the alignment of the
 // global run), works on the windows there, and writes the run back with 16-byte
@@ -498,6 +577,10 @@ static int pool_forward(ag_device *dev, const T *x, T *y, int64_t planes, int ih
         const int64_t items = planes * oh * (iw / V);
         max_pool2_2x2_kernel<T><<<grid_for(items, threads, dev->sm_count), threads, 0,
                                   dev->stream>>>(x, y, planes, ih, iw, oh, ow);
+    } else if (h == 2 && w == 2 && sh == 2 && sw == 2 && (iw & 1) == 0 && (ih & 1) == 0 &&
+               (reinterpret_cast<uintptr_t>(x) % (2 * sizeof(T))) == 0) {
+        max_pool2_2x2_pair_kernel<T><<<grid_for(planes * oh * ow, threads, dev->sm_count), threads, 0,
+                                       dev->stream>>>(x, y, planes, ih, iw, oh, ow);
     } else if (plane_bytes <= 40 * 1024 && planes >= dev->sm_count) {
         // a run of whole planes per CTA, about four CTAs per SM
         int per_cta = (int)((40 * 1024) / plane_bytes);
@@ -618,10 +701,22 @@ static int pool_backward(ag_device *dev, ag_dtype dtype, const void *x, void *dx
     const int threads = 256;
     const int vlen = dtype == AG_F32 ? 4 : 8;
     if (h == 2 && w == 2 && sh == 2 && sw == 2 && iw % vlen == 0 &&
-        (reinterpret_cast<uintptr_t>(dx) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        (reinterpret_cast<uintptr_t>(dx) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+        ((ih & 1) == 0 || x == dx)) {  // out of place, a last row no window covers must be copied
         const unsigned grid2 = grid_for(planes * oh * (iw / vlen), threads, dev->sm_count);
         AG_DISPATCH_FLOAT(dtype, T,
             max_pool2_backward_2x2_kernel<T><<<grid2, threads, 0, dev->stream>>>(
+                (const T *)x, (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow););
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
+    const size_t pair_bytes = 2 * dtype_size(dtype);
+    if (h == 2 && w == 2 && sh == 2 && sw == 2 && (iw & 1) == 0 && (ih & 1) == 0 &&
+        reinterpret_cast<uintptr_t>(dx) % pair_bytes == 0 &&
+        reinterpret_cast<uintptr_t>(x) % pair_bytes == 0) {
+        const unsigned gridp = grid_for(planes * oh * ow, threads, dev->sm_count);
+        AG_DISPATCH_FLOAT(dtype, T,
+            max_pool2_backward_2x2_pair_kernel<T><<<gridp, threads, 0, dev->stream>>>(
                 (const T *)x, (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow););
         AG_CHECK_LAUNCH();
         return AG_OK;

@@ -71,7 +71,10 @@ def test_max_pool2_golden(dev, golden, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", [((3, 6, 24, 24), (2, 2), None), ((2, 16, 8, 8), (2, 2), None),
                                   ((2, 4, 62, 62), (2, 2), None), ((2, 3, 29, 29), (2, 2), None),
-                                  ((2, 2, 13, 17), (3, 2), None), ((1, 2, 20, 21), (2, 3), (3, 4))])
+                                  ((2, 2, 13, 17), (3, 2), None), ((1, 2, 20, 21), (2, 3), (3, 4)),
+                                  # a last row no window covers (keeps x), vector / staged paths
+                                  ((2, 3, 9, 16), (2, 2), None), ((2, 3, 7, 10), (2, 2), None),
+                                  ((2, 3, 10, 10), (2, 2), None), ((700, 5, 12, 14), (2, 2), None)])
 def test_max_pool2_random(dev, dtype, case):
     shape, size, strides = case
     rng = np.random.default_rng(2)
