@@ -59,9 +59,9 @@ int launch_any(ag_device *dev, CfgId id, int M, int N, int K, int splits, int k_
 // Number of k splits for a problem that would otherwise leave most SMs idle.
 // max_splits bounds the workspace (0 = never split).
 inline int pick_splits(int64_t tiles, int K, int sms, int max_splits) {
-    if (max_splits <= 1 || K < 512 || tiles * 2 > sms) return 1;
+    if (max_splits <= 1 || K < 256 || tiles * 2 > sms) return 1;
     int64_t want = ceil_div((int64_t)sms * 2, tiles);
-    int64_t by_k = K / 128;  // at least 128 k per split
+    int64_t by_k = K / 64;  // at least 64 k per split
     int64_t s = want < by_k ? want : by_k;
     if (s > max_splits) s = max_splits;
     return s < 1 ? 1 : (int)s;
