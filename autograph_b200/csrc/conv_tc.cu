@@ -479,7 +479,9 @@ template <int BLOCK_N>
 static int launch(ag_device *dev, const CUtensorMap &tx, const CUtensorMap &tw, const Params &p) {
     using C = Cfg<BLOCK_N>;
     auto kernel = conv2_bf16_tc_kernel<BLOCK_N>;
-    static bool configured = false;  // per instantiation
+    // the attribute belongs to the (kernel, GPU) pair: remembered per instantiation and GPU
+    static bool configured_on[64] = {};
+    bool &configured = configured_on[dev->ordinal & 63];
     if (!configured) {
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES));

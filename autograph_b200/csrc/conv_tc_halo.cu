@@ -267,7 +267,10 @@ template <int BLOCK_N>
 int launch_halo(ag_device *dev, const CUtensorMap &tx, const CUtensorMap &tw, const HaloParams &p,
                 int smem) {
     auto kernel = conv2_bf16_tc_halo_kernel<BLOCK_N>;
-    static int configured = 0;  // per instantiation: largest size set so far
+    // the attribute belongs to the (kernel, GPU) pair: largest size set so far, per
+    // instantiation and GPU
+    static int configured_on[64] = {};
+    int &configured = configured_on[dev->ordinal & 63];
     if (smem > configured) {
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = smem;

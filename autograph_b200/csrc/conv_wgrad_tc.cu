@@ -248,7 +248,10 @@ int launch_wgrad(ag_device *dev, const CUtensorMap &tdy, const CUtensorMap &tx, 
                  int grid) {
     auto kernel = conv2_wgrad_bf16_tc_kernel<NT>;
     const int smem = p.stages * p.stage_bytes + 1024 + 256;
-    static int configured = 0;  // per instantiation: largest size set so far
+    // the attribute belongs to the (kernel, GPU) pair: largest size set so far, per
+    // instantiation and GPU
+    static int configured_on[64] = {};
+    int &configured = configured_on[dev->ordinal & 63];
     if (smem > configured) {
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = smem;

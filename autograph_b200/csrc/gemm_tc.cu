@@ -385,7 +385,9 @@ bool gemm_bf16_eligible(int64_t m, int64_t k, int64_t n, const __nv_bfloat16 *a,
 template <bool A_MN, bool B_MN>
 static int launch(ag_device *dev, const CUtensorMap &ta, const CUtensorMap &tb, const Params &p) {
     auto kernel = gemm_bf16_tc_kernel<A_MN, B_MN>;
-    static bool configured = false;  // per instantiation
+    // the attribute belongs to the (kernel, GPU) pair: remembered per instantiation and GPU
+    static bool configured_on[64] = {};
+    bool &configured = configured_on[dev->ordinal & 63];
     if (!configured) {
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SMEM_BYTES));
