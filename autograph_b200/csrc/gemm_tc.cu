@@ -409,7 +409,7 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
     const int out_tiles = (int)(ceil_div(m, BLOCK_M) * ceil_div(n, BLOCK_N));
     const int total_kb = (int)ceil_div(k, BLOCK_K);
     int splits = 1, kb_per_split = total_kb;
-    if (out_tiles * 2 <= dev->sm_count && total_kb >= 16) {
+    if (out_tiles * 4 <= dev->sm_count && total_kb >= 64) {
         splits = dev->sm_count / out_tiles;
         if (splits > total_kb / 4) splits = total_kb / 4;  // at least four k blocks per slice
         if (splits < 1) splits = 1;
