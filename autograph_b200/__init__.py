@@ -384,6 +384,26 @@ class Device:
             strides[1], _ptr(dy.contiguous()), _ptr(dx)))
         return dx
 
+    def relu_max_pool2(self, x):
+        """max_pool2(relu(x)) with a 2x2 window and stride in one pass (even planes)."""
+        x = x.contiguous()
+        bs, c, ih, iw = x.shape
+        y = self.empty((bs, c, ih // 2, iw // 2), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_relu_max_pool2_forward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
+                                                    ih, iw, _ptr(y)))
+        return y
+
+    def relu_max_pool2_backward(self, x, dy):
+        """Gradient of relu_max_pool2 at x: the pool's and the Relu's backward in one pass."""
+        x = x.contiguous()
+        bs, c, ih, iw = x.shape
+        dx = self.empty(x.shape, x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_relu_max_pool2_backward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
+                                                     ih, iw, _ptr(dy.contiguous()), _ptr(dx)))
+        return dx
+
     def relu(self, x, inplace=False):
         x = x.contiguous()
         y = x if inplace else self.empty(x.shape, x.dtype)

@@ -103,6 +103,9 @@ _SIGNATURES = {
                              c_int32, c_int32, _P]),
     "ag_max_pool2_backward_from_input": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
                                                  c_int32, c_int32, c_int32, c_int32, _P, _P]),
+    "ag_relu_max_pool2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P]),
+    "ag_relu_max_pool2_backward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P,
+                                           _P]),
     "ag_max_pool2_backward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, c_int32,
                                       c_int32, c_int32, c_int32, _P]),
     "ag_relu": (c_int, [_P, c_int, _P, _P, c_int64]),

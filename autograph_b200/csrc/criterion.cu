@@ -58,6 +58,38 @@ __global__ void sum_rows_kernel(const float *__restrict__ v, int64_t n, float *_
     if (threadIdx.x == 0) out[0] = part[0];
 }
 
+// Both steps in one CTA for bs <= 1024: a warp per row, the row losses stay in shared
+// memory and are added by the same tree as sum_rows_kernel (the result is identical).
+template <class T, class L>
+__global__ void __launch_bounds__(1024)
+    ce_loss_small_kernel(const T *__restrict__ x, const L *__restrict__ t, int bs, int classes,
+                         float *__restrict__ out) {
+    __shared__ float part[1024];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    part[threadIdx.x] = 0.f;
+    __syncthreads();
+    for (int r = warp; r < bs; r += 32) {
+        const T *row = x + (int64_t)r * classes;
+        float m = -INFINITY;
+        for (int i = lane; i < classes; i += 32) m = fmaxf(m, to_f32(row[i]));
+        m = warp_max(m);
+        float s = 0.f;
+        for (int i = lane; i < classes; i += 32) s += expf(to_f32(row[i]) - m);
+        s = warp_sum(s);
+        if (lane == 0) {
+            uint32_t tt = label_at(t, r);
+            float xt = tt < (uint32_t)classes ? to_f32(row[tt]) : 0.f;
+            part[r] = logf(s) - (xt - m);
+        }
+    }
+    __syncthreads();
+    for (int off = 512; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) part[threadIdx.x] += part[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[0] = part[0];
+}
+
 template <class T, class L>
 __global__ void ce_backward_kernel(const T *__restrict__ x, const L *__restrict__ t, int64_t bs,
                                    int classes, float dy, T *__restrict__ dx) {
@@ -109,6 +141,11 @@ static unsigned warp_grid(int64_t rows, int threads, int sms) {
 template <class T, class L>
 static int ce_loss_device(ag_device *dev, const T *x, const L *t, int64_t bs, int classes,
                           float *loss_dev) {
+    if (bs <= 1024) {
+        ce_loss_small_kernel<T, L><<<1, 1024, 0, dev->stream>>>(x, t, (int)bs, classes, loss_dev);
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
     void *ws;
     AG_TRY(workspace(dev, sizeof(float) * (size_t)bs, &ws));
     const int threads = 256;

@@ -350,6 +350,104 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_BLOCKS)
     }
 }
 
+// ------------------------------------------------------- short reductions
+// k <= kSmallK and few output tiles (the Dense gradients of a small batch): the
+// tile engine above spends its time on the latency of one global -> shared round
+// per k tile with two warps per CTA.  Here a CTA of 256 threads owns a 32 x 32 tile
+// of C, stages the WHOLE k range of both operands with one round of loads, and its
+// four groups of 64 threads each accumulate a quarter of the k range for the full
+// tile (4 x 4 outputs per thread); the quarters are added in group order, so the
+// result is reproducible.
+constexpr int kSmallK = 128;
+constexpr int kSmallPitch = 36;  // floats per staged k row: 16-byte rows, see small_k_slot
+
+// Element of an 8-k slab (32 rows/columns x 8 k) this thread moves.  Contiguous-in-k
+// operands: a warp takes 4 rows x 8 k (four 32-byte segments; with the pitch of 36 the
+// 32 stores fall into 32 banks).  Otherwise a warp takes 32 consecutive rows of one k.
+template <class Op>
+__device__ __forceinline__ void small_k_slot(int tid, int &mn, int &kb) {
+    if (Op::kFastK) {
+        kb = tid & 7;
+        mn = ((tid >> 3) & 3) + 4 * (tid >> 5);
+    } else {
+        mn = tid & 31;
+        kb = tid >> 5;
+    }
+}
+
+template <class AOp, class BOp, class Epi>
+__global__ void __launch_bounds__(256)
+    gemm_small_k_kernel(int M, int N, int K, AOp A, BOp B, Epi E) {
+    __shared__ __align__(16) float As[kSmallK][kSmallPitch];
+    __shared__ __align__(16) float Bs[kSmallK][kSmallPitch];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.x * 32, n0 = blockIdx.y * 32;
+    constexpr int SLABS = kSmallK / 8;
+
+    int amn, akb, bmn, bkb;
+    small_k_slot<AOp>(tid, amn, akb);
+    small_k_slot<BOp>(tid, bmn, bkb);
+    float ra[SLABS], rb[SLABS];
+#pragma unroll
+    for (int i = 0; i < SLABS; ++i)
+        if (i * 8 < K) {
+            ra[i] = A.at(m0 + amn, i * 8 + akb);
+            rb[i] = B.at(n0 + bmn, i * 8 + bkb);
+        }
+#pragma unroll
+    for (int i = 0; i < SLABS; ++i)
+        if (i * 8 < K) {
+            As[i * 8 + akb][amn] = ra[i];
+            Bs[i * 8 + bkb][bmn] = rb[i];
+        }
+    __syncthreads();
+
+    const int kg = tid >> 6, t = tid & 63, tx = t & 7, ty = t >> 3;
+    const int kp = (K + 7) & ~7;           // staged rows (zeros beyond K)
+    const int kq = (kp / 8 + 3) / 4 * 8;   // k per group: whole slabs
+    const int k0 = min(kp, kg * kq), k1 = min(kp, k0 + kq);
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+    for (int k = k0; k < k1; ++k) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(&As[k][ty * 4]);
+        const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4]);
+        const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();  // the staged operands are no longer read
+    float *red = &As[0][0];  // [3 groups][16 values][64 threads]
+    if (kg > 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) red[((kg - 1) * 16 + i) * 64 + t] = acc[i / 4][i % 4];
+    }
+    __syncthreads();
+    if (kg > 0) return;
+#pragma unroll
+    for (int g = 0; g < 3; ++g)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i / 4][i % 4] += red[(g * 16 + i) * 64 + t];
+
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i, n = n0 + tx * 4;
+        if (m >= M || n >= N) continue;
+        if (E.can4(m, n)) {
+            E.store4(m, n, acc[i]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (n + j < N) E.store(m, n + j, acc[i][j]);
+        }
+    }
+}
+
 // out[i] = alpha * sum_z ws[z][i] + beta * out[i] written through an epilogue
 // (fixed summation order: deterministic).
 template <class Epi>

@@ -74,6 +74,12 @@ template <class AOp, class BOp, class Epi>
 int gemm(ag_device *dev, int M, int N, int K, const AOp &A, const BOp &B, const Epi &E,
          bool allow_split, void *scratch = nullptr, size_t scratch_bytes = 0) {
     if (M <= 0 || N <= 0) return AG_OK;
+    if (K >= 1 && K <= kSmallK && ceil_div(M, 32) * ceil_div(N, 32) <= dev->sm_count) {
+        dim3 grid((unsigned)ceil_div(M, 32), (unsigned)ceil_div(N, 32));
+        gemm_small_k_kernel<AOp, BOp, Epi><<<grid, 256, 0, dev->stream>>>(M, N, K, A, B, E);
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
     CfgId id = pick_cfg(M, N, dev->sm_count);
     int bm, bn;
     cfg_dims(id, bm, bn);

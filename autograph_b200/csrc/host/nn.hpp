@@ -365,6 +365,34 @@ class Relu : public Layer {
     }
 };
 
+// Relu followed by a 2x2 / stride 2 MaxPool2 over even planes as one kernel each way: the
+// Relu's output is never stored and the single backward edge produces the gradient at the
+// Relu's input (the values are those of the two layers run one after the other).
+inline bool relu_pool_fusable(const Variable &input, const MaxPool2 &mp) {
+    const Tensor &x = input.value;
+    return mp.filter[0] == 2 && mp.filter[1] == 2 && mp.stride[0] == 2 && mp.stride[1] == 2 &&
+           x.ndim() == 4 && x.is_standard_layout() && x.dim(2) >= 2 && x.dim(3) >= 2 &&
+           x.dim(2) % 2 == 0 && x.dim(3) % 2 == 0;
+}
+inline Variable relu_pool_forward(Pool &pool, const Variable &input) {
+    const Tensor &x = input.value;
+    const int64_t bs = x.dim(0), c = x.dim(1), ih = x.dim(2), iw = x.dim(3);
+    Tensor y = Tensor::uninit(pool, {bs, c, ih / 2, iw / 2}, x.dtype());
+    check(ag_relu_max_pool2_forward(x.device(), x.dtype(), x.data(), bs, c, ih, iw, y.data()));
+    VariableBuilder builder;
+    Pool *pp = &pool;
+    if (input.node) {
+        Tensor xv = x;
+        builder.edge(input.node, [=](const Tensor &dy, Tensor *) {
+            Tensor dx = Tensor::uninit(*pp, xv.shape(), xv.dtype());
+            check(ag_relu_max_pool2_backward(xv.device(), xv.dtype(), xv.data(), bs, c, ih, iw,
+                                             dy.data(), dx.data()));
+            return dx;
+        });
+    }
+    return builder.build(y);
+}
+
 // Flatten (layer.rs:1224-1231): reshape to [batch, rest]; the edge reshapes back.
 class Flatten : public Layer {
    public:

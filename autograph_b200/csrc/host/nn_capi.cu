@@ -388,6 +388,14 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                 continue;
             }
         }
+        if (dynamic_cast<Relu *>(l) && i + 1 < n) {
+            auto *mp = dynamic_cast<MaxPool2 *>(m->layers[i + 1].get());
+            if (mp && relu_pool_fusable(v, *mp)) {
+                v = relu_pool_forward(m->pool, v);
+                i += 1;
+                continue;
+            }
+        }
         v = l->forward(m->pool, v);
     }
     return v;

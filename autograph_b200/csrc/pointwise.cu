@@ -268,7 +268,8 @@ __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16 *p, floa
     *reinterpret_cast<uint32_t *>(p) = *reinterpret_cast<uint32_t *>(&h);
 }
 
-template <class T>
+// RELU: the window is taken over relu(x) (x >= 0 ? x : 0), i.e. Relu followed by the pool.
+template <class T, bool RELU = false>
 __global__ void max_pool2_2x2_pair_kernel(const T *__restrict__ x, T *__restrict__ y, int64_t planes,
                                           int ih, int iw, int oh, int ow) {
     const int64_t total = planes * oh * ow;
@@ -282,6 +283,12 @@ __global__ void max_pool2_2x2_pair_kernel(const T *__restrict__ x, T *__restrict
         float a0, a1, b0, b1;
         load_pair<T>(r0, a0, a1);
         load_pair<T>(r0 + iw, b0, b1);
+        if (RELU) {
+            a0 = a0 >= 0.f ? a0 : 0.f;
+            a1 = a1 >= 0.f ? a1 : 0.f;
+            b0 = b0 >= 0.f ? b0 : 0.f;
+            b1 = b1 >= 0.f ? b1 : 0.f;
+        }
         float m = a0;  // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
         if (a1 > m) m = a1;
         if (b0 > m) m = b0;
@@ -292,7 +299,9 @@ __global__ void max_pool2_2x2_pair_kernel(const T *__restrict__ x, T *__restrict
 
 // Gradient of the same: src holds the forward input, dx receives dy at the first maximum
 // of every window and zero elsewhere (every cell belongs to a window).  src may be dx.
-template <class T>
+// RELU: src is the input of a Relu whose output was pooled; the result is the gradient at
+// that input (the pool's gradient gated by src >= 0, as Relu's backward gates it).
+template <class T, bool RELU = false>
 __global__ void max_pool2_backward_2x2_pair_kernel(const T *src, T *dx, const T *__restrict__ dy,
                                                    int64_t planes, int ih, int iw, int oh, int ow) {
     const int64_t total = planes * oh * ow;
@@ -306,14 +315,19 @@ __global__ void max_pool2_backward_2x2_pair_kernel(const T *src, T *dx, const T 
         float a0, a1, b0, b1;
         load_pair<T>(src + off, a0, a1);
         load_pair<T>(src + off + iw, b0, b1);
+        bool p0 = true, p1 = true, p2 = true, p3 = true;  // Relu lets the gradient pass
+        if (RELU) {
+            p0 = a0 >= 0.f; p1 = a1 >= 0.f; p2 = b0 >= 0.f; p3 = b1 >= 0.f;
+            a0 = p0 ? a0 : 0.f; a1 = p1 ? a1 : 0.f; b0 = p2 ? b0 : 0.f; b1 = p3 ? b1 : 0.f;
+        }
         float m = a0;
         int am = 0;
         if (a1 > m) { m = a1; am = 1; }
         if (b0 > m) { m = b0; am = 2; }
         if (b1 > m) { m = b1; am = 3; }
         const float g = __fadd_rn(0.f, to_f32(dy[i]));
-        store_pair<T>(dx + off, am == 0 ? g : 0.f, am == 1 ? g : 0.f);
-        store_pair<T>(dx + off + iw, am == 2 ? g : 0.f, am == 3 ? g : 0.f);
+        store_pair<T>(dx + off, (am == 0 && p0) ? g : 0.f, (am == 1 && p1) ? g : 0.f);
+        store_pair<T>(dx + off + iw, (am == 2 && p2) ? g : 0.f, (am == 3 && p3) ? g : 0.f);
     }
 }
 
@@ -429,7 +443,8 @@ __global__ void bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias, i
 // the contiguous inner positions of one channel.
 template <class T>
 __global__ void bias_grad_cols_kernel(const T *__restrict__ x, float *__restrict__ partial,
-                                      int64_t rows, int64_t cols, int64_t rows_per_chunk) {
+                                      int64_t rows, int64_t cols, int64_t rows_per_chunk,
+                                      T *__restrict__ y, float beta) {
     __shared__ float part[8][33];
     const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;  // 32 columns x 8 row lanes
     const int64_t c = (int64_t)blockIdx.x * 32 + cx;
@@ -444,7 +459,12 @@ __global__ void bias_grad_cols_kernel(const T *__restrict__ x, float *__restrict
         float t = 0.f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) t += part[k][cx];
-        partial[(int64_t)blockIdx.y * cols + c] = t;
+        if (y != nullptr) {  // a single chunk: this is the whole sum
+            if (beta != 0.f) t = __fadd_rn(t, __fmul_rn(beta, to_f32(y[c])));
+            y[c] = from_f32<T>(t);
+        } else {
+            partial[(int64_t)blockIdx.y * cols + c] = t;
+        }
     }
 }
 
@@ -490,15 +510,23 @@ static int bias_grad_run(ag_device *dev, const T *x, int64_t rows, int64_t cols,
     if (chunks > rows) chunks = rows;
     if (chunks > 1024) chunks = 1024;
     if (chunks < 1) chunks = 1;
+    // Few rows (a Dense layer's small batch): one launch, no second pass.
+    if (inner == 1 && rows <= 1024) chunks = 1;
     const int64_t rows_per_chunk = ceil_div(rows > 0 ? rows : 1, chunks);
     chunks = rows > 0 ? ceil_div(rows, rows_per_chunk) : 1;
+    if (inner == 1 && chunks == 1) {
+        bias_grad_cols_kernel<T><<<(unsigned)col_blocks, 256, 0, dev->stream>>>(
+            x, nullptr, rows, cols, rows_per_chunk, y, beta);
+        AG_CHECK_LAUNCH();
+        return AG_OK;
+    }
     void *ws = nullptr;
     AG_TRY(workspace(dev, sizeof(float) * (size_t)chunks * (size_t)cols, &ws));
     dim3 grid((unsigned)col_blocks, (unsigned)chunks);
     AG_REQUIRE(col_blocks < (1ll << 31), AG_ERR_LIMIT, "too many columns");
     if (inner == 1)
         bias_grad_cols_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols,
-                                                                rows_per_chunk);
+                                                                rows_per_chunk, nullptr, 0.f);
     else
         bias_grad_inner_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols, inner,
                                                                  rows_per_chunk);
@@ -758,6 +786,55 @@ int ag_max_pool2_backward_from_input(ag_device *dev, ag_dtype dtype, const void 
                                      int64_t c, int64_t ih, int64_t iw, int32_t h, int32_t w,
                                      int32_t sh, int32_t sw, const void *dy, void *dx) {
     return pool_backward(dev, dtype, x, dx, bs, c, ih, iw, h, w, sh, sw, dy);
+}
+
+// Relu followed by a 2x2 / stride 2 pool over planes of even height and width, and the
+// gradient of the pair at the Relu's input.
+static int relu_pool_check(ag_device *dev, ag_dtype dtype, int64_t bs, int64_t c, int64_t ih,
+                           int64_t iw, const void *a, const void *b, const void *d) {
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "relu_max_pool2 %d unimplemented", (int)dtype);
+    AG_REQUIRE(bs >= 0 && c >= 0 && ih >= 2 && iw >= 2, AG_ERR_SHAPE,
+               "pool window [2,2] does not fit input [%lld,%lld]", (long long)ih, (long long)iw);
+    AG_REQUIRE((ih & 1) == 0 && (iw & 1) == 0, AG_ERR_UNSUPPORTED,
+               "relu_max_pool2 needs even height and width");
+    AG_REQUIRE(ih < (1 << 30) && iw < (1 << 30), AG_ERR_LIMIT, "image too large");
+    if (bs * c == 0) return AG_OK;
+    AG_REQUIRE(a && b && d, AG_ERR_INVALID, "null tensor pointer");
+    const size_t pair_bytes = 2 * dtype_size(dtype);
+    AG_REQUIRE(reinterpret_cast<uintptr_t>(a) % pair_bytes == 0 &&
+                   reinterpret_cast<uintptr_t>(b) % pair_bytes == 0,
+               AG_ERR_UNSUPPORTED, "relu_max_pool2 needs element-pair aligned tensors");
+    return AG_OK;
+}
+
+int ag_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs, int64_t c,
+                              int64_t ih, int64_t iw, void *y) {
+    AG_ENTER(dev);
+    AG_TRY(relu_pool_check(dev, dtype, bs, c, ih, iw, x, x, y));
+    const int64_t planes = bs * c;
+    if (planes == 0) return AG_OK;
+    const int oh = (int)(ih / 2), ow = (int)(iw / 2), threads = 256;
+    const unsigned grid = grid_for(planes * oh * ow, threads, dev->sm_count);
+    AG_DISPATCH_FLOAT(dtype, T,
+        (max_pool2_2x2_pair_kernel<T, true><<<grid, threads, 0, dev->stream>>>(
+            (const T *)x, (T *)y, planes, (int)ih, (int)iw, oh, ow)););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+int ag_relu_max_pool2_backward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                               int64_t c, int64_t ih, int64_t iw, const void *dy, void *dx) {
+    AG_ENTER(dev);
+    AG_TRY(relu_pool_check(dev, dtype, bs, c, ih, iw, x, dx, dy));
+    const int64_t planes = bs * c;
+    if (planes == 0) return AG_OK;
+    const int oh = (int)(ih / 2), ow = (int)(iw / 2), threads = 256;
+    const unsigned grid = grid_for(planes * oh * ow, threads, dev->sm_count);
+    AG_DISPATCH_FLOAT(dtype, T,
+        (max_pool2_backward_2x2_pair_kernel<T, true><<<grid, threads, 0, dev->stream>>>(
+            (const T *)x, (T *)dx, (const T *)dy, planes, (int)ih, (int)iw, oh, ow)););
+    AG_CHECK_LAUNCH();
+    return AG_OK;
 }
 
 int ag_bias_add(ag_device *dev, ag_dtype dtype, void *y, const void *bias, int64_t rows,

@@ -276,6 +276,18 @@ AG_API int ag_max_pool2_backward_from_input(ag_device *dev, ag_dtype dtype, cons
                                             int32_t h, int32_t w, int32_t sh, int32_t sw,
                                             const void *dy, void *dx);
 
+/* Relu::forward followed by MaxPool2::forward with a 2x2 window and stride (layer.rs:1254-1298,
+ * 1193-1216) as one pass over x [bs,c,ih,iw] (ih, iw even): y = max_pool2(relu(x)); the Relu's
+ * output is not materialised.  AG_ERR_UNSUPPORTED for odd planes or tensors that are not
+ * element-pair aligned. */
+AG_API int ag_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                     int64_t c, int64_t ih, int64_t iw, void *y);
+/* The two backward edges of that pair in one pass: dx = relu_backward(x, max_pool2_backward(copy of
+ * relu(x), dy)) — the gradient lands on the first maximum of relu(x) in every window and passes
+ * where x >= 0 (layer.rs:1203-1212, 1283-1296, 1526-1540). */
+AG_API int ag_relu_max_pool2_backward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                      int64_t c, int64_t ih, int64_t iw, const void *dy, void *dx);
+
 /* ----------------------------------------------------------- input pipeline */
 
 /* y = alpha * x with x u8 and y f32 / bf16: ≙ Tensor::scaled_cast (src/tensor/ops.rs:209-218 ->

@@ -107,6 +107,27 @@ def test_split_k_and_skinny_shapes(dev, dtype):
         assert _rel_err(c, ref) <= tol, (m, k, n, layout)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
+def test_short_reductions_all_layouts(dev, dtype, layout):
+    """k <= 128 with few output tiles takes the kernel that stages the whole k range."""
+    rng = np.random.default_rng(61)
+    for m, k, n in [(1, 1, 1), (33, 7, 5), (100, 8, 84), (97, 33, 130), (84, 100, 10),
+                    (256, 128, 128), (130, 127, 31)]:
+        a = rng.uniform(-1, 1, (m, k) if layout[0] == "n" else (k, m)).astype(np.float32)
+        b = rng.uniform(-1, 1, (k, n) if layout[1] == "n" else (n, k)).astype(np.float32)
+        if dtype == torch.bfloat16:
+            a, b = oracle.round_bf16(a), oracle.round_bf16(b)
+        av, bv = _views(a, b, *layout)
+        ref = av.astype(np.float64) @ bv.astype(np.float64)
+        ad, bd = dev.tensor(a, dtype), dev.tensor(b, dtype)
+        c1 = dev.dot(*_views(ad, bd, *layout)).float().cpu().numpy()
+        c2 = dev.dot(*_views(ad, bd, *layout)).float().cpu().numpy()
+        tol = 1e-5 * np.sqrt(k) if dtype == torch.float32 else 1e-2
+        assert _rel_err(c1, ref) <= tol, (m, k, n)
+        assert np.array_equal(c1, c2)
+
+
 def test_split_k_is_deterministic(dev):
     rng = np.random.default_rng(7)
     a = dev.tensor(rng.uniform(-1, 1, (16, 6400)).astype(np.float32))

@@ -95,6 +95,36 @@ def test_max_pool2_random(dev, dtype, case):
     assert np.array_equal(_np(dx), oracle.max_pool2_backward(x, dy, size, strides))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(100, 6, 24, 24), (100, 16, 8, 8), (3, 5, 2, 2), (2, 3, 6, 10),
+                                   (0, 4, 8, 8)])
+def test_relu_max_pool2_equals_the_two_layers(dev, dtype, shape):
+    """One pass gives what Relu then MaxPool2 give, forward and backward (ties, zeros, -0.0)."""
+    rng = np.random.default_rng(21)
+    x = _prep(rng.integers(-3, 4, shape).astype(np.float32) * 0.5, dtype)
+    if x.size:
+        x.reshape(-1)[::7] = -0.0
+    xd = dev.tensor(x, dtype)
+    y = dev.relu_max_pool2(xd)
+    want = oracle.max_pool2(oracle.relu(x)) if x.size else np.zeros(y.shape, np.float32)
+    assert np.array_equal(_np(y), want)
+    dy = _prep(rng.standard_normal(want.shape), dtype)
+    dx = dev.relu_max_pool2_backward(xd, dev.tensor(dy, dtype))
+    if x.size:
+        want_dx = oracle.relu_backward(x, oracle.max_pool2_backward(oracle.relu(x), dy))
+        assert np.array_equal(_np(dx), want_dx)
+        # and bit for bit what the separate kernels give
+        r = dev.relu(xd)
+        sep = dev.relu_backward(xd, dev.max_pool2_backward_from_input(r, dev.tensor(dy, dtype)))
+        assert np.array_equal(_np(dx).view(np.uint32), _np(sep).view(np.uint32))
+
+
+def test_relu_max_pool2_rejects_odd_planes(dev):
+    import autograph_b200 as ag
+    with pytest.raises(ag.AgError, match="even"):
+        dev.relu_max_pool2(dev.empty((1, 1, 5, 4), torch.float32))
+
+
 def test_max_pool2_errors(dev):
     import autograph_b200 as ag
     with pytest.raises(ag.AgError):
