@@ -79,6 +79,8 @@ __global__ void __launch_bounds__(256, 2)
     if (p.split > 1)
         compute_items_split<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg,
                                        s_bias + p.ocp + 4, p.split, out);
+    else if (p.fine)
+        compute_items_fine<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
     else
         compute_items<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
 }
@@ -238,6 +240,7 @@ static int launch(ag_device *dev, const T *x, const T *w, const T *bias, T *y, c
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
     int threads = ((p.group * items_per_img * p.split + 31) / 32) * 32;
+    if (p.fine) threads *= 8;
     if (threads > 256) threads = 256;
     if (threads < 64) threads = 64;
     const unsigned grid = (unsigned)ceil_div(p.bs, p.group);
@@ -269,6 +272,9 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
     // no channel split in the forward direction: its sums must keep the order of the
     // whole-network kernel and of the fused conv + pool call (bit-for-bit equality)
     p.split = 1;
+    // One image per CTA with fewer than 128 work items and no pool: finer items instead
+    // (the same sums in the same order on more threads).
+    p.fine = !pool && group == 1 && items_per_img < 128 && (ow & 1) == 0;
     // Many output channels, one image per CTA anyway: the banded kernel (coalesced stores).
     if (oc >= 32 && group == 1 && bs <= 2147483647) {
         const int out_w = pool ? ow / 2 : ow;

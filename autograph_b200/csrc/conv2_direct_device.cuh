@@ -35,6 +35,7 @@ struct Params {
     int ocp;         // oc rounded up to a multiple of 2 (weight row pitch in shared memory)
     bool relu, pool;
     int split;       // threads per work item (ranges of input channels), stand-alone kernel only
+    bool fine = false;  // 1x2-pixel work items (compute_items_fine), stand-alone kernel only
 };
 
 constexpr int OC_T = 2;  // output channels per thread
@@ -218,6 +219,60 @@ __device__ __forceinline__ void compute_items(const float *s_img, const float *s
                 for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
         accumulate_item<FH, FW>(acc, s_img, s_w, p, it, 0, p.ic);
         finish_item<T, FH, FW>(acc, s_bias, has_bias, p, it, out);
+    }
+}
+
+// Plain convolution output (no pool) for a CTA with few work items (one image of a small
+// layer): an item is 1 x 2 pixels x OC_T channels, eight times as many threads as above.
+// Every output is the same chain of FFMAs in the same (channel, row, column) order as in
+// accumulate_item, so the values are identical.  Needs an even output width.
+template <class T, int FH, int FW, class Out>
+__device__ __forceinline__ void compute_items_fine(const float *s_img, const float *s_w,
+                                                   const float *s_bias, bool has_bias,
+                                                   const Params &p, int nimg, Out out) {
+    const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
+    const int nbx = ow / 2, n_ocg = p.ocp / OC_T;
+    const int items_per_img = n_ocg * oh * nbx;
+    const int img_elems = p.ic * p.ih * p.iw;
+    for (int item = threadIdx.x; item < nimg * items_per_img; item += blockDim.x) {
+        const int g = item / items_per_img;
+        const int r = item - g * items_per_img;
+        const int blk = r / n_ocg, oc0 = (r - blk * n_ocg) * OC_T;
+        const int y0 = blk / nbx, x0 = (blk - y0 * nbx) * 2;
+        float acc[2][OC_T] = {{0.f, 0.f}, {0.f, 0.f}};
+        const float *img = s_img + g * img_elems + y0 * p.iw + x0;
+        for (int ci = 0; ci < p.ic; ++ci) {
+            float patch[FH][FW + 1];
+            const float *pi = img + ci * p.ih * p.iw;
+#pragma unroll
+            for (int a = 0; a < FH; ++a)
+#pragma unroll
+                for (int b = 0; b < FW + 1; ++b) patch[a][b] = pi[a * p.iw + b];
+            const float *wc = s_w + ci * FH * FW * p.ocp + oc0;
+#pragma unroll
+            for (int fi = 0; fi < FH; ++fi)
+#pragma unroll
+                for (int fj = 0; fj < FW; ++fj) {
+                    const float2 wv = *reinterpret_cast<const float2 *>(wc + (fi * FW + fj) * p.ocp);
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        acc[b][0] = fmaf(patch[fi][fj + b], wv.x, acc[b][0]);
+                        acc[b][1] = fmaf(patch[fi][fj + b], wv.y, acc[b][1]);
+                    }
+                }
+        }
+#pragma unroll
+        for (int o = 0; o < OC_T; ++o) {
+            const int oc = oc0 + o;
+            if (oc >= p.oc) break;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                float t = to_f32(from_f32<T>(acc[b][o]));
+                if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
+                if (p.relu) t = (t >= 0.f) ? t : 0.f;
+                out.plain(g, oc, y0, x0 + b, t);
+            }
+        }
     }
 }
 

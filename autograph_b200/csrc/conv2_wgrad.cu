@@ -94,27 +94,37 @@ __global__ void __launch_bounds__(1024)
     }
 }
 
-// dw[i] = beta * dw[i] + sum over CTAs (in CTA order) of partial[cta][i]
+// dw[i] = beta * dw[i] + sum over CTAs of partial[cta][i].  A CTA takes 32 outputs; its eight
+// warps each add every eighth plane (loads of one warp are independent, so the planes' L2
+// latencies overlap), and the eight sums are added in warp order: a fixed order.
 template <class T>
-__global__ void conv2_wgrad_reduce_kernel(const float *__restrict__ partial, int planes, int len,
-                                          float beta, T *__restrict__ dw) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= len) return;
+__global__ void __launch_bounds__(256)
+    conv2_wgrad_reduce_kernel(const float *__restrict__ partial, int planes, int len, float beta,
+                              T *__restrict__ dw) {
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + lane;
     float s = 0.f;
-    int z = 0;
-    for (; z + 4 <= planes; z += 4) {
-        const float a = partial[(int64_t)z * len + i];
-        const float b = partial[(int64_t)(z + 1) * len + i];
-        const float c = partial[(int64_t)(z + 2) * len + i];
-        const float d = partial[(int64_t)(z + 3) * len + i];
-        s += a;
-        s += b;
-        s += c;
-        s += d;
+    if (i < len) {
+        int z = grp;
+        for (; z + 56 < planes; z += 64) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = partial[(int64_t)(z + 8 * j) * len + i];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += v[j];
+        }
+        for (; z < planes; z += 8) s += partial[(int64_t)z * len + i];
     }
-    for (; z < planes; ++z) s += partial[(int64_t)z * len + i];
-    if (beta != 0.f) s = fmaf(beta, to_f32(dw[i]), s);
-    dw[i] = from_f32<T>(s);
+    part[grp][lane] = s;
+    __syncthreads();
+    if (grp == 0 && i < len) {
+        float t = part[0][lane];
+#pragma unroll
+        for (int g = 1; g < 8; ++g) t += part[g][lane];
+        if (beta != 0.f) t = fmaf(beta, to_f32(dw[i]), t);
+        dw[i] = from_f32<T>(t);
+    }
 }
 
 static int wgrad_slices(int items, int oh) {
@@ -160,7 +170,7 @@ static int launch_wgrad(ag_device *dev, const T *x, const T *dy, const WgradPara
     const int threads = ((p.items * p.slices + 31) / 32) * 32;
     kernel<<<ctas, threads, smem, dev->stream>>>(x, dy, (float *)ws, p);
     AG_CHECK_LAUNCH();
-    conv2_wgrad_reduce_kernel<T><<<(unsigned)ceil_div(len, 128), 128, 0, dev->stream>>>(
+    conv2_wgrad_reduce_kernel<T><<<(unsigned)ceil_div(len, 32), 256, 0, dev->stream>>>(
         (const float *)ws, ctas, len, beta, dw);
     AG_CHECK_LAUNCH();
     return AG_OK;
