@@ -218,6 +218,27 @@ class Device:
                                                  rl, _ptr(y)))
         return y
 
+    def dense_chain_forward_keep(self, x, weights, biases=None, relus=None):
+        """The same run for a pass that records gradients: returns (pre, act), the outputs of
+        every Dense and (where relus[i]) of the Relu after it; act[i] is None without a Relu."""
+        n = len(weights)
+        biases = biases or [None] * n
+        relus = relus or [False] * n
+        dims = (ctypes.c_int64 * (n + 1))(x.shape[1], *[w.shape[1] for w in weights])
+        ws = (ctypes.c_void_p * n)(*[w.contiguous().data_ptr() for w in weights])
+        bs = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
+        rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
+        pre = [self.empty((x.shape[0], w.shape[1]), x.dtype) for w in weights]
+        act = [self.empty((x.shape[0], w.shape[1]), x.dtype) if r else None
+               for w, r in zip(weights, relus)]
+        pp = (ctypes.c_void_p * n)(*[_ptr(t) for t in pre])
+        ap = (ctypes.c_void_p * n)(*[(_ptr(t) if t is not None else None) for t in act])
+        self._sync_in()
+        _capi.check(lib().ag_dense_chain_forward_keep(self._h, _dtype_code(x.dtype),
+                                                      _ptr(x.contiguous()), x.shape[0], n, dims, ws,
+                                                      bs, rl, pp, ap))
+        return pre, act
+
     # ---- 1-D wrappers: ≙ Conv1 / MaxPool1 (layer.rs:1007-1033, 1173-1191), which reshape
     # [n, c, l] to [n, c, l, 1] and call the 2-D operators
     def conv1_forward(self, x, w, bias=None, padding=0, stride=1, dilation=1, relu=False):

@@ -24,8 +24,13 @@ struct ChainLayer {
     const void *bias;  // [outputs] or null
     int inputs, outputs;
     int relu;
+    // Optional copies for a training pass: the layer's output before the relu
+    // ([m, outputs]) and after it.
+    void *pre_out = nullptr;
+    void *act_out = nullptr;
 };
 bool chain_eligible(int64_t m, int n_layers, const ChainLayer *layers);
+// y may be null when every value wanted leaves through pre_out / act_out.
 template <class T>
 int chain_forward(ag_device *dev, const T *x, int m, int n_layers, const ChainLayer *layers, T *y);
 

@@ -12,6 +12,7 @@ constexpr int ROWS = 8;  // rows of x a CTA owns
 struct ChainStep {
     const void *w, *bias;
     int K, N, np, slices, kchunk, relu;
+    void *pre, *act;  // optional [M, N] copies of the output before / after the relu
 };
 struct ChainParams {
     ChainStep s[kMaxChain];
@@ -45,6 +46,8 @@ inline size_t plan_chain(ChainParams *p, int m, int n_layers, const ChainLayer *
         st.K = layers[i].inputs;
         st.N = layers[i].outputs;
         st.relu = layers[i].relu;
+        st.pre = layers[i].pre_out;
+        st.act = layers[i].act_out;
         plan_step(st.K, st.N, &st.np, &st.slices, &st.kchunk);
         if (st.K > p->max_k) p->max_k = st.K;
         if (st.N > p->max_k) p->max_k = st.N;  // a layer's output is the next layer's input
@@ -147,9 +150,13 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
             for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
             float v = to_f32(from_f32<T>(s));
             if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
+            if (st.pre != nullptr && r < rows)
+                reinterpret_cast<T *>(st.pre)[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
             if (st.relu) v = (v >= 0.f) ? v : 0.f;
+            if (st.act != nullptr && r < rows)
+                reinterpret_cast<T *>(st.act)[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
             if (last) {
-                if (r < rows) y[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
+                if (y != nullptr && r < rows) y[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
             } else {
                 xb[c * ROWS + r] = v;  // already rounded to T: equals storing and reloading it
             }

@@ -151,6 +151,55 @@ extern "C" int ag_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void
     return AG_OK;
 }
 
+extern "C" int ag_dense_chain_forward_keep(ag_device *dev, ag_dtype dtype, const void *x,
+                                           int64_t bs, int32_t n_layers, const int64_t *dims,
+                                           const void *const *weights, const void *const *biases,
+                                           const int32_t *relu, void *const *pre_out,
+                                           void *const *act_out) {
+    AG_ENTER(dev);
+    AG_REQUIRE(dtype == AG_F32 || dtype == AG_BF16, AG_ERR_DTYPE, "Dense %d not implemented",
+               (int)dtype);
+    AG_REQUIRE(n_layers >= 1 && dims && weights && relu && pre_out && act_out, AG_ERR_INVALID,
+               "null or empty chain");
+    AG_REQUIRE(bs >= 0, AG_ERR_SHAPE, "negative batch");
+    for (int i = 0; i <= n_layers; ++i)
+        AG_REQUIRE(dims[i] > 0 && dims[i] < (1ll << 31), AG_ERR_SHAPE, "bad layer width");
+    if (bs == 0) return AG_OK;
+    AG_REQUIRE(x, AG_ERR_INVALID, "null tensor pointer");
+    for (int i = 0; i < n_layers; ++i)
+        AG_REQUIRE(weights[i] && pre_out[i] && (!relu[i] || act_out[i]), AG_ERR_INVALID,
+                   "null weight or output pointer");
+    dense_small::ChainLayer layers[dense_small::kMaxChain];
+    bool fused = n_layers <= dense_small::kMaxChain;
+    if (fused) {
+        for (int i = 0; i < n_layers; ++i) {
+            layers[i] = {weights[i], biases ? biases[i] : nullptr, (int)dims[i], (int)dims[i + 1],
+                         relu[i]};
+            layers[i].pre_out = pre_out[i];
+            layers[i].act_out = relu[i] ? act_out[i] : nullptr;
+        }
+        fused = dense_small::chain_eligible(bs, n_layers, layers);
+    }
+    if (fused) {
+        if (dtype == AG_F32)
+            return dense_small::chain_forward<float>(dev, (const float *)x, (int)bs, n_layers,
+                                                     layers, nullptr);
+        return dense_small::chain_forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, (int)bs,
+                                                         n_layers, layers, nullptr);
+    }
+    const void *in = x;
+    for (int i = 0; i < n_layers; ++i) {
+        AG_TRY(ag_dense_forward(dev, dtype, in, bs, dims[i], weights[i], dims[i + 1],
+                                biases ? biases[i] : nullptr, 0, pre_out[i]));
+        in = pre_out[i];
+        if (relu[i]) {
+            AG_TRY(ag_relu(dev, dtype, pre_out[i], act_out[i], bs * dims[i + 1]));
+            in = act_out[i];
+        }
+    }
+    return AG_OK;
+}
+
 extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t n,
                        float alpha, const void *a, int64_t off_a, int64_t rsa, int64_t csa,
                        const void *b, int64_t off_b, int64_t rsb, int64_t csb, float beta,

@@ -275,6 +275,15 @@ class Dense : public Layer {
         Tensor y = Tensor::uninit(pool, {bs, outs}, x.dtype());
         check(ag_dense_forward(x.device(), x.dtype(), x.data(), bs, ins, w.value.data(), outs,
                                has_bias ? b.value.data() : nullptr, relu ? 1 : 0, y.data()));
+        return attach(pool, input, y);
+    }
+    // The layer's output variable around y = Dense(input) that the caller has computed:
+    // the three backward edges of Dense::forward.
+    Variable attach(Pool &pool, const Variable &input, const Tensor &y) {
+        const Tensor &x = input.value;
+        Variable w = weight.to_variable();
+        Variable b = has_bias ? bias.to_variable() : Variable{};
+        const int64_t bs = x.dim(0), outs = w.value.dim(1);
         VariableBuilder builder;
         Pool *pp = &pool;
         if (input.node) {
@@ -348,6 +357,13 @@ class Relu : public Layer {
     Variable forward(Pool &pool, const Variable &input) override {
         const Tensor &x = input.value;
         if (!x.is_standard_layout()) throw Error(AG_ERR_SHAPE, "Relu needs standard layout");
+        Tensor y = (!input.node && x.exclusive()) ? x : Tensor::uninit(pool, x.shape(), x.dtype());
+        check(ag_relu(x.device(), x.dtype(), x.data(), y.data(), x.len()));
+        return attach(pool, input, y);
+    }
+    // The output variable around y = relu(input) that the caller has computed.
+    static Variable attach(Pool &pool, const Variable &input, const Tensor &y) {
+        const Tensor &x = input.value;
         VariableBuilder builder;
         Pool *pp = &pool;
         if (input.node) {
@@ -359,8 +375,6 @@ class Relu : public Layer {
                 return dx;
             });
         }
-        Tensor y = (!input.node && x.exclusive()) ? x : Tensor::uninit(pool, x.shape(), x.dtype());
-        check(ag_relu(x.device(), x.dtype(), x.data(), y.data(), x.len()));
         return builder.build(y);
     }
 };

@@ -387,6 +387,52 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                 i += 1;
                 continue;
             }
+            // Recording gradients: the same run as one call that keeps every layer's values,
+            // then the layers' own backward edges around those values.
+            if (dense->records_gradient(v) && v.value.ndim() == 2 && v.value.is_standard_layout() &&
+                v.value.dim(1) == dense->weight.value.dim(0)) {
+                std::vector<Dense *> run;
+                std::vector<int32_t> relus;
+                size_t j = i;
+                while (j < n && run.size() < 4) {
+                    auto *d = dynamic_cast<Dense *>(m->layers[j].get());
+                    if (!d) break;
+                    if (!run.empty() && d->weight.value.dim(0) != run.back()->weight.value.dim(1)) break;
+                    const bool r = j + 1 < n && dynamic_cast<Relu *>(m->layers[j + 1].get());
+                    run.push_back(d);
+                    relus.push_back(r ? 1 : 0);
+                    j += r ? 2 : 1;
+                }
+                if (run.size() >= 2) {
+                    const int64_t bs = v.value.dim(0);
+                    std::vector<int64_t> dims = {v.value.dim(1)};
+                    std::vector<const void *> ws, bs_ptr;
+                    std::vector<Tensor> pre, act;
+                    std::vector<void *> pre_ptr, act_ptr;
+                    for (size_t k = 0; k < run.size(); ++k) {
+                        Dense *d = run[k];
+                        const int64_t outs = d->weight.value.dim(1);
+                        dims.push_back(outs);
+                        ws.push_back(d->weight.value.data());
+                        bs_ptr.push_back(d->has_bias ? d->bias.value.data() : nullptr);
+                        pre.push_back(Tensor::uninit(m->pool, {bs, outs}, v.value.dtype()));
+                        act.push_back(relus[k] ? Tensor::uninit(m->pool, {bs, outs}, v.value.dtype())
+                                               : Tensor{});
+                        pre_ptr.push_back(pre.back().data());
+                        act_ptr.push_back(relus[k] ? act.back().data() : nullptr);
+                    }
+                    check(ag_dense_chain_forward_keep(v.value.device(), v.value.dtype(), v.value.data(),
+                                                      bs, (int32_t)run.size(), dims.data(), ws.data(),
+                                                      bs_ptr.data(), relus.data(), pre_ptr.data(),
+                                                      act_ptr.data()));
+                    for (size_t k = 0; k < run.size(); ++k) {
+                        v = run[k]->attach(m->pool, v, pre[k]);
+                        if (relus[k]) v = Relu::attach(m->pool, v, act[k]);
+                    }
+                    i = j - 1;
+                    continue;
+                }
+            }
         }
         if (dynamic_cast<Relu *>(l) && i + 1 < n) {
             auto *mp = dynamic_cast<MaxPool2 *>(m->layers[i + 1].get());

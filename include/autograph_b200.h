@@ -156,6 +156,17 @@ AG_API int ag_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x,
                                   const void *const *weights, const void *const *biases,
                                   const int32_t *relu, void *y);
 
+/* The same chain for a pass that records gradients: every layer's values are kept, because the
+ * backward edges need them (Dense::forward keeps its input, layer.rs:1134-1143; Relu's edge gates
+ * on its input, layer.rs:1283-1296).  pre_out[i] [bs, dims[i+1]] receives Dense i's output,
+ * act_out[i] (read only where relu[i] != 0) the Relu's output; the chain's result is the last
+ * of them.  One kernel for small chains, else layer by layer; values equal the separate calls. */
+AG_API int ag_dense_chain_forward_keep(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                       int32_t n_layers, const int64_t *dims,
+                                       const void *const *weights, const void *const *biases,
+                                       const int32_t *relu, void *const *pre_out,
+                                       void *const *act_out);
+
 /* ------------------------------------------------------------ convolution */
 
 /* y = conv2(x, w) (+ bias) (then relu when fuse_relu != 0), NCHW.

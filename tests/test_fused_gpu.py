@@ -93,9 +93,16 @@ def test_dense_chain_equals_separate_calls(dev, dtype, case):
         relus.append(not last)
     xd = dev.tensor(x, dtype)
     fused = dev.dense_chain_forward(xd, ws, bs_, relus)
+    pre, act = dev.dense_chain_forward_keep(xd, ws, bs_, relus)
     h = xd
-    for w, b, r in zip(ws, bs_, relus):
+    for i, (w, b, r) in enumerate(zip(ws, bs_, relus)):
+        p = dev.dense_forward(h, w, bias=b, relu=False)
+        assert torch.equal(pre[i], p), i  # the values a gradient-recording pass keeps
         h = dev.dense_forward(h, w, bias=b, relu=r)
+        if r:
+            assert torch.equal(act[i], h), i
+        else:
+            assert act[i] is None
     assert torch.equal(fused, h)
 
 
