@@ -239,6 +239,30 @@ class Device:
                                                       bs, rl, pp, ap))
         return pre, act
 
+    def dense_chain_backward(self, x, weights, relus, pre, act, dy, has_bias=None, want_dx=True):
+        """Every gradient of a Dense (+ Relu) run from the values dense_chain_forward_keep kept.
+        Returns (dx or None, [dw], [db or None], [gradient at each Dense's output])."""
+        n = len(weights)
+        has_bias = has_bias or [False] * n
+        dt = x.dtype
+        dims = (ctypes.c_int64 * (n + 1))(x.shape[1], *[w.shape[1] for w in weights])
+        ins = [x.contiguous()] + [(act[i] if relus[i] else pre[i]) for i in range(n - 1)]
+        g = [self.empty(p.shape, dt) for p in pre]
+        dw = [self.empty(w.shape, dt) for w in weights]
+        db = [self.empty((w.shape[1],), dt) if b else None for w, b in zip(weights, has_bias)]
+        dx = self.empty(x.shape, dt) if want_dx else None
+        dy = dy.contiguous()
+        if not relus[-1]:
+            g[-1] = dy
+        arr = lambda ts: (ctypes.c_void_p * n)(*[(_ptr(t) if t is not None else None) for t in ts])
+        self._sync_in()
+        _capi.check(lib().ag_dense_chain_backward(
+            self._h, _dtype_code(dt), x.shape[0], n, dims, arr(ins),
+            arr([w.contiguous() for w in weights]), arr([pre[i] if relus[i] else None for i in range(n)]),
+            _ptr(dy), arr([g[i] if (i < n - 1 or relus[i]) else None for i in range(n)]),
+            _ptr(dx) if dx is not None else None, arr(dw), arr(db)))
+        return dx, dw, db, g
+
     # ---- 1-D wrappers: ≙ Conv1 / MaxPool1 (layer.rs:1007-1033, 1173-1191), which reshape
     # [n, c, l] to [n, c, l, 1] and call the 2-D operators
     def conv1_forward(self, x, w, bias=None, padding=0, stride=1, dilation=1, relu=False):

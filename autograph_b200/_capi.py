@@ -78,6 +78,9 @@ _SIGNATURES = {
     "ag_dense_chain_forward_keep": (c_int, [_P, c_int, _P, c_int64, c_int32, POINTER(c_int64),
                                             POINTER(_P), POINTER(_P), POINTER(c_int32),
                                             POINTER(_P), POINTER(_P)]),
+    "ag_dense_chain_backward": (c_int, [_P, c_int, c_int64, c_int32, POINTER(c_int64), POINTER(_P),
+                                        POINTER(_P), POINTER(_P), _P, POINTER(_P), _P, POINTER(_P),
+                                        POINTER(_P)]),
     "ag_conv_dense_chain_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
                                             c_int32, POINTER(ConvStage), c_int32, POINTER(c_int64),
                                             POINTER(_P), POINTER(_P), POINTER(c_int32), _P]),

@@ -50,11 +50,28 @@ __global__ void __launch_bounds__(256, 2)
         const int sh = p.ih - 2 * (FH - 1), sw = p.iw - 2 * (FW - 1);
         const T *src = x + (int64_t)b0 * p.ic * sh * sw;
         const int total = nimg * img_elems;
-        for (int i = threadIdx.x; i < total; i += blockDim.x) {
-            const int plane = i / (p.ih * p.iw), rem = i - plane * (p.ih * p.iw);
-            const int r = rem / p.iw - (FH - 1), c = rem % p.iw - (FW - 1);
-            const bool inside = r >= 0 && r < sh && c >= 0 && c < sw;
-            s_img[i] = inside ? to_f32(src[(plane * sh + r) * sw + c]) : 0.f;
+        if ((sw & 3) == 0 && reinterpret_cast<uintptr_t>(src) % (4 * sizeof(T)) == 0) {
+            // zero the frames with 16-byte stores, then copy dy four elements per load
+            float4 *z = reinterpret_cast<float4 *>(s_img);
+            for (int i = threadIdx.x; i < (total + 3) / 4; i += blockDim.x)
+                z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            __syncthreads();
+            const int qpr = sw / 4;  // loads per source row
+            for (int i = threadIdx.x; i < nimg * p.ic * sh * qpr; i += blockDim.x) {
+                const int q = i % qpr, row = i / qpr;
+                const int r = row % sh, plane = row / sh;
+                float v[4];
+                load4_to_f32<T>(src + (int64_t)row * sw + 4 * q, v);
+                float *dst = s_img + plane * (p.ih * p.iw) + (r + FH - 1) * p.iw + (FW - 1) + 4 * q;
+                dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+            }
+        } else {
+            for (int i = threadIdx.x; i < total; i += blockDim.x) {
+                const int plane = i / (p.ih * p.iw), rem = i - plane * (p.ih * p.iw);
+                const int r = rem / p.iw - (FH - 1), c = rem % p.iw - (FW - 1);
+                const bool inside = r >= 0 && r < sh && c >= 0 && c < sw;
+                s_img[i] = inside ? to_f32(src[(plane * sh + r) * sw + c]) : 0.f;
+            }
         }
         // w is [p.ic][p.oc][FH][FW] in memory (dy's channels outermost); staged as
         // [ci][FH][FW][ocp] with both spatial axes reversed

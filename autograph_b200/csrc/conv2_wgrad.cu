@@ -9,6 +9,7 @@
 // [CTA][oc*ic*FH*FW] scratch plane and a second kernel; every sum has a fixed
 // order, so the result does not depend on scheduling.
 #include "conv2_direct.cuh"
+#include "conv2_direct_device.cuh"
 
 namespace ag {
 namespace direct {
@@ -52,8 +53,8 @@ __global__ void __launch_bounds__(1024)
         __syncthreads();  // the previous image is no longer read
         const T *xg = x + (int64_t)(b0 + g) * x_elems;
         const T *dyg = dy + (int64_t)(b0 + g) * dy_elems;
-        for (int i = tid; i < x_elems; i += blockDim.x) xs[i] = to_f32(xg[i]);
-        for (int i = tid; i < dy_elems; i += blockDim.x) dys[i] = to_f32(dyg[i]);
+        stage_contiguous<T>(xg, xs, x_elems);  // 4 elements per load where aligned
+        stage_contiguous<T>(dyg, dys, dy_elems);
         __syncthreads();
         if (!active) continue;
         for (int hy = row0; hy < row1; ++hy) {

@@ -58,8 +58,8 @@ __global__ void sum_rows_kernel(const float *__restrict__ v, int64_t n, float *_
     if (threadIdx.x == 0) out[0] = part[0];
 }
 
-// Both steps in one CTA for bs <= 1024: a warp per row, the row losses stay in shared
-// memory and are added by the same tree as sum_rows_kernel (the result is identical).
+// Both steps in one CTA for bs <= 1024: the row losses stay in shared memory and are added
+// by the same tree as sum_rows_kernel.
 template <class T, class L>
 __global__ void __launch_bounds__(1024)
     ce_loss_small_kernel(const T *__restrict__ x, const L *__restrict__ t, int bs, int classes,
@@ -68,18 +68,36 @@ __global__ void __launch_bounds__(1024)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     part[threadIdx.x] = 0.f;
     __syncthreads();
-    for (int r = warp; r < bs; r += 32) {
-        const T *row = x + (int64_t)r * classes;
-        float m = -INFINITY;
-        for (int i = lane; i < classes; i += 32) m = fmaxf(m, to_f32(row[i]));
-        m = warp_max(m);
-        float s = 0.f;
-        for (int i = lane; i < classes; i += 32) s += expf(to_f32(row[i]) - m);
-        s = warp_sum(s);
-        if (lane == 0) {
-            uint32_t tt = label_at(t, r);
-            float xt = tt < (uint32_t)classes ? to_f32(row[tt]) : 0.f;
+    if (classes <= 32) {
+        // a thread per row: the rows' loads are all in flight together
+        const int r = threadIdx.x;
+        if (r < bs) {
+            const T *row = x + (int64_t)r * classes;
+            const uint32_t tt = label_at(t, r);
+            float m = -INFINITY;
+            for (int i = 0; i < classes; ++i) m = fmaxf(m, to_f32(row[i]));
+            float s = 0.f, xt = 0.f;
+            for (int i = 0; i < classes; ++i) {
+                const float v = to_f32(row[i]);
+                s += expf(v - m);
+                if ((uint32_t)i == tt) xt = v;
+            }
             part[r] = logf(s) - (xt - m);
+        }
+    } else {
+        for (int r = warp; r < bs; r += 32) {
+            const T *row = x + (int64_t)r * classes;
+            float m = -INFINITY;
+            for (int i = lane; i < classes; i += 32) m = fmaxf(m, to_f32(row[i]));
+            m = warp_max(m);
+            float s = 0.f;
+            for (int i = lane; i < classes; i += 32) s += expf(to_f32(row[i]) - m);
+            s = warp_sum(s);
+            if (lane == 0) {
+                uint32_t tt = label_at(t, r);
+                float xt = tt < (uint32_t)classes ? to_f32(row[tt]) : 0.f;
+                part[r] = logf(s) - (xt - m);
+            }
         }
     }
     __syncthreads();

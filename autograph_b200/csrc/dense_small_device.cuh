@@ -13,6 +13,10 @@ struct ChainStep {
     const void *w, *bias;
     int K, N, np, slices, kchunk, relu;
     void *pre, *act;  // optional [M, N] copies of the output before / after the relu
+    // Backward steps (dx = dy . w^T): w is read as [N][K] (the forward layer's [inputs, outputs])
+    // and the result is zeroed where gate[m][n] < 0 (the Relu in front of the forward layer).
+    int transposed;
+    const void *gate;
 };
 struct ChainParams {
     ChainStep s[kMaxChain];
@@ -48,7 +52,13 @@ inline size_t plan_chain(ChainParams *p, int m, int n_layers, const ChainLayer *
         st.relu = layers[i].relu;
         st.pre = layers[i].pre_out;
         st.act = layers[i].act_out;
+        st.transposed = layers[i].transposed;
+        st.gate = layers[i].gate;
         plan_step(st.K, st.N, &st.np, &st.slices, &st.kchunk);
+        if (st.transposed && st.K % 4 == 0) {  // whole groups of four weights per slice
+            st.kchunk = (st.kchunk + 3) & ~3;
+            st.slices = (st.K + st.kchunk - 1) / st.kchunk;
+        }
         if (st.K > p->max_k) p->max_k = st.K;
         if (st.N > p->max_k) p->max_k = st.N;  // a layer's output is the next layer's input
         if (st.slices * ROWS * st.np > p->red_floats) p->red_floats = st.slices * ROWS * st.np;
@@ -66,6 +76,16 @@ __device__ __forceinline__ void load2_to_f32(const __nv_bfloat16 *p, float &a, f
     const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
     a = __uint_as_float(v << 16);
     b = __uint_as_float(v & 0xffff0000u);
+}
+
+__device__ __forceinline__ void load4_w(const float *p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4 *>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+}
+__device__ __forceinline__ void load4_w(const __nv_bfloat16 *p, float (&v)[4]) {
+    const uint2 q = *reinterpret_cast<const uint2 *>(p);
+    v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xffff0000u);
+    v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xffff0000u);
 }
 
 // Runs every layer of the chain for the ROWS rows whose first-layer input is in
@@ -86,7 +106,51 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
         // for every output is the same either way (same k slices, same order).
         const bool pairs = (st.N % 2 == 0) &&
                            (reinterpret_cast<uintptr_t>(w) % (2 * sizeof(T)) == 0);
-        if (pairs) {
+        if (st.transposed) {
+            // Thread (n, k slice) walks row n of w, contiguous in k: four weights per load
+            // when the rows keep 4-element alignment.
+            const bool vec4 = (st.K % 4 == 0) && (st.kchunk % 4 == 0) &&
+                              (reinterpret_cast<uintptr_t>(w) % (4 * sizeof(T)) == 0);
+            for (int vt = threadIdx.x; vt < st.np * st.slices; vt += blockDim.x) {
+                const int n = vt % st.np, slice = vt / st.np;
+                float acc[ROWS];
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+                if (n < st.N) {
+                    const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
+                    const T *wp = w + (int64_t)n * st.K;
+                    if (vec4) {
+#pragma unroll 4
+                        for (int k = k0; k < k1; k += 4) {
+                            float wv[4];
+                            load4_w(wp + k, wv);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float4 a = *reinterpret_cast<const float4 *>(xa + (k + q) * ROWS);
+                                const float4 b = *reinterpret_cast<const float4 *>(xa + (k + q) * ROWS + 4);
+                                acc[0] = fmaf(a.x, wv[q], acc[0]); acc[1] = fmaf(a.y, wv[q], acc[1]);
+                                acc[2] = fmaf(a.z, wv[q], acc[2]); acc[3] = fmaf(a.w, wv[q], acc[3]);
+                                acc[4] = fmaf(b.x, wv[q], acc[4]); acc[5] = fmaf(b.y, wv[q], acc[5]);
+                                acc[6] = fmaf(b.z, wv[q], acc[6]); acc[7] = fmaf(b.w, wv[q], acc[7]);
+                            }
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int k = k0; k < k1; ++k) {
+                            const float wv = to_f32(wp[k]);
+                            const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
+                            const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
+                            acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
+                            acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
+                            acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
+                            acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * st.np + n] = acc[r];
+            }
+        } else if (pairs) {
             const int half = st.np / 2;
             for (int vt = threadIdx.x; vt < half * st.slices; vt += blockDim.x) {
                 const int n = 2 * (vt % half), slice = vt / half;
@@ -150,6 +214,9 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
             for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
             float v = to_f32(from_f32<T>(s));
             if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
+            if (st.gate != nullptr && r < rows &&
+                !(to_f32(reinterpret_cast<const T *>(st.gate)[(int64_t)(m0 + r) * st.N + c]) >= 0.f))
+                v = 0.f;
             if (st.pre != nullptr && r < rows)
                 reinterpret_cast<T *>(st.pre)[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
             if (st.relu) v = (v >= 0.f) ? v : 0.f;

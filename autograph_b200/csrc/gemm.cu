@@ -200,6 +200,85 @@ extern "C" int ag_dense_chain_forward_keep(ag_device *dev, ag_dtype dtype, const
     return AG_OK;
 }
 
+extern "C" int ag_dense_chain_backward(ag_device *dev, ag_dtype dtype, int64_t bs, int32_t n_layers,
+                                       const int64_t *dims, const void *const *layer_in,
+                                       const void *const *weights, const void *const *gate,
+                                       const void *dy, void *const *g, void *dx, void *const *dw,
+                                       void *const *db) {
+    AG_ENTER(dev);
+    AG_REQUIRE(dtype == AG_F32 || dtype == AG_BF16, AG_ERR_DTYPE, "Dense %d not implemented",
+               (int)dtype);
+    AG_REQUIRE(n_layers >= 1 && n_layers <= 64 && dims && layer_in && weights && gate && g && dw,
+               AG_ERR_INVALID, "null or empty chain");
+    AG_REQUIRE(bs >= 0, AG_ERR_SHAPE, "negative batch");
+    for (int i = 0; i <= n_layers; ++i)
+        AG_REQUIRE(dims[i] > 0 && dims[i] < (1ll << 31), AG_ERR_SHAPE, "bad layer width");
+    if (bs == 0) return AG_OK;
+    AG_REQUIRE(dy, AG_ERR_INVALID, "null tensor pointer");
+    const int L = n_layers;
+    for (int i = 0; i < L; ++i) {
+        AG_REQUIRE(layer_in[i] && weights[i] && dw[i], AG_ERR_INVALID, "null layer pointer");
+        // g[i] is written for every layer but the last, and for the last when it is gated
+        AG_REQUIRE(g[i] || (i == L - 1 && !gate[i]), AG_ERR_INVALID, "null gradient buffer");
+    }
+    // gradient at the last Dense's output
+    const void *g_last = gate[L - 1] ? g[L - 1] : dy;
+
+    // One kernel for the input gradients, one for all weight and bias gradients.
+    const int n_steps = dx ? L : L - 1;
+    bool fused = L <= dense_small::kMaxChain && bs <= 512 && n_steps >= 1;
+    dense_small::ChainLayer steps[dense_small::kMaxChain];
+    if (fused) {
+        for (int i = 0; i < n_steps; ++i) {
+            const int l = L - 1 - i;  // forward layer this step goes back through
+            steps[i] = {weights[l], nullptr, (int)dims[l + 1], (int)dims[l], 0};
+            steps[i].transposed = 1;
+            steps[i].gate = l >= 1 ? gate[l - 1] : nullptr;
+            steps[i].pre_out = (i + 1 < n_steps) ? g[l - 1] : nullptr;
+        }
+        fused = dense_small::chain_backward_eligible(bs, n_steps, steps);
+    }
+    if (fused) {
+        void *y = dx ? dx : g[0];
+        dense_small::WgradProblem pr[dense_small::kMaxChain];
+        for (int l = 0; l < L; ++l)
+            pr[l] = {layer_in[l], l == L - 1 ? g_last : g[l], dw[l], db ? db[l] : nullptr,
+                     (int)dims[l], (int)dims[l + 1], 0, 0};
+        if (dtype == AG_F32) {
+            AG_TRY(dense_small::chain_backward_input<float>(
+                dev, (const float *)dy, (int)bs, n_steps, steps, (const float *)gate[L - 1],
+                (float *)(gate[L - 1] ? g[L - 1] : nullptr), (float *)y));
+            return dense_small::chain_weight_grads<float>(dev, (int)bs, L, pr);
+        }
+        AG_TRY(dense_small::chain_backward_input<__nv_bfloat16>(
+            dev, (const __nv_bfloat16 *)dy, (int)bs, n_steps, steps,
+            (const __nv_bfloat16 *)gate[L - 1],
+            (__nv_bfloat16 *)(gate[L - 1] ? g[L - 1] : nullptr), (__nv_bfloat16 *)y));
+        return dense_small::chain_weight_grads<__nv_bfloat16>(dev, (int)bs, L, pr);
+    }
+
+    // Layer by layer: relu_backward, the two products and the column sum of every layer.
+    const void *incoming = dy;
+    for (int l = L - 1; l >= 0; --l) {
+        const int64_t ins = dims[l], outs = dims[l + 1];
+        const void *gl = incoming;
+        if (gate[l]) {
+            AG_TRY(ag_relu_backward(dev, dtype, gate[l], incoming, g[l], bs * outs));
+            gl = g[l];
+        }
+        // dw = in^T . g
+        AG_TRY(ag_gemm(dev, dtype, ins, bs, outs, 1.f, layer_in[l], 0, 1, ins, gl, 0, outs, 1, 0.f,
+                       dw[l], 0, outs, 1));
+        if (db && db[l]) AG_TRY(ag_bias_grad(dev, dtype, gl, bs, outs, 1, 0.f, db[l]));
+        void *out = l >= 1 ? g[l - 1] : dx;
+        if (out)  // g . w^T
+            AG_TRY(ag_gemm(dev, dtype, bs, outs, ins, 1.f, gl, 0, outs, 1, weights[l], 0, 1, outs,
+                           0.f, out, 0, ins, 1));
+        incoming = out;
+    }
+    return AG_OK;
+}
+
 extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int64_t n,
                        float alpha, const void *a, int64_t off_a, int64_t rsa, int64_t csa,
                        const void *b, int64_t off_b, int64_t rsb, int64_t csb, float beta,

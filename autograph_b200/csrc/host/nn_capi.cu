@@ -330,6 +330,83 @@ bool forward_whole_network(ag_model *m, const Variable &v, Variable *out, void *
     return true;
 }
 
+// One autograd node for a run of Dense (+ Relu) layers whose values were kept: the first
+// edge asked for its gradient computes all of them with one ag_dense_chain_backward call
+// (parameter gradients straight into the parameters' gradient storage where that is still
+// unset), the others hand out what it left.
+struct DenseChainGrads {
+    bool done = false;
+    Tensor dx;
+    std::vector<Tensor> dw, db;
+};
+
+Variable attach_dense_chain(Pool &pool, const Variable &input, const std::vector<Dense *> &run,
+                            const std::vector<int32_t> &relus, const std::vector<Tensor> &pre,
+                            const std::vector<Tensor> &act) {
+    const size_t L = run.size();
+    const Tensor x = input.value;
+    const std::shared_ptr<Node> in_node = input.node;
+    std::vector<Tensor> wv;
+    std::vector<std::shared_ptr<Node>> wn, bn;
+    for (Dense *d : run) {
+        wv.push_back(d->weight.value);
+        wn.push_back(d->weight.node);
+        bn.push_back(d->has_bias ? d->bias.node : nullptr);
+    }
+    auto st = std::make_shared<DenseChainGrads>();
+    Pool *pp = &pool;
+    auto ensure = [=](const Tensor &dy) {
+        if (st->done) return;
+        const int64_t bs = x.dim(0);
+        auto target = [&](const std::shared_ptr<Node> &n, const Shape &shape) {
+            if (n && !n->has_grad && n->grad_storage.defined()) return n->grad_storage;
+            return Tensor::uninit(*pp, shape, x.dtype());
+        };
+        std::vector<int64_t> dims = {x.dim(1)};
+        std::vector<const void *> lin, ws, gate;
+        std::vector<Tensor> g;
+        std::vector<void *> gp, dwp, dbp;
+        for (size_t l = 0; l < L; ++l) {
+            const int64_t ins = wv[l].dim(0), outs = wv[l].dim(1);
+            dims.push_back(outs);
+            lin.push_back(l == 0 ? x.data() : (relus[l - 1] ? act[l - 1].data() : pre[l - 1].data()));
+            ws.push_back(wv[l].data());
+            gate.push_back(relus[l] ? pre[l].data() : nullptr);
+            const bool need_g = l + 1 < L || relus[l];
+            g.push_back(need_g ? Tensor::uninit(*pp, {bs, outs}, x.dtype()) : Tensor{});
+            gp.push_back(need_g ? g.back().data() : nullptr);
+            st->dw.push_back(target(wn[l], Shape{ins, outs}));
+            dwp.push_back(st->dw.back().data());
+            st->db.push_back(bn[l] ? target(bn[l], Shape{outs}) : Tensor{});
+            dbp.push_back(bn[l] ? st->db.back().data() : nullptr);
+        }
+        if (in_node) st->dx = Tensor::uninit(*pp, x.shape(), x.dtype());
+        check(ag_dense_chain_backward(x.device(), x.dtype(), bs, (int32_t)L, dims.data(), lin.data(),
+                                      ws.data(), gate.data(), dy.data(), gp.data(),
+                                      in_node ? st->dx.data() : nullptr, dwp.data(), dbp.data()));
+        st->done = true;
+    };
+    VariableBuilder builder;
+    if (in_node)
+        builder.edge(in_node, [=](const Tensor &dy, Tensor *) {
+            ensure(dy);
+            return st->dx;
+        });
+    for (size_t l = 0; l < L; ++l) {
+        if (wn[l])
+            builder.edge(wn[l], [=](const Tensor &dy, Tensor *) {
+                ensure(dy);
+                return st->dw[l];
+            });
+        if (bn[l])
+            builder.edge(bn[l], [=](const Tensor &dy, Tensor *) {
+                ensure(dy);
+                return st->db[l];
+            });
+    }
+    return builder.build(relus[L - 1] ? act[L - 1] : pre[L - 1]);
+}
+
 // out_ptr (optional): where the result should land when the network runs as one kernel;
 // the caller compares the returned tensor's address to see whether it did.
 Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
@@ -425,10 +502,7 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                                                       bs, (int32_t)run.size(), dims.data(), ws.data(),
                                                       bs_ptr.data(), relus.data(), pre_ptr.data(),
                                                       act_ptr.data()));
-                    for (size_t k = 0; k < run.size(); ++k) {
-                        v = run[k]->attach(m->pool, v, pre[k]);
-                        if (relus[k]) v = Relu::attach(m->pool, v, act[k]);
-                    }
+                    v = attach_dense_chain(m->pool, v, run, relus, pre, act);
                     i = j - 1;
                     continue;
                 }

@@ -167,6 +167,21 @@ AG_API int ag_dense_chain_forward_keep(ag_device *dev, ag_dtype dtype, const voi
                                        const int32_t *relu, void *const *pre_out,
                                        void *const *act_out);
 
+/* Every backward edge of such a chain in one call (Variable2::dot's edges dX = dY.W^T and
+ * dW = X^T.dY, autograd.rs:607-627; the bias edge's column sum, autograd.rs:490-542; Relu's
+ * gate on its input, layer.rs:1283-1296).  layer_in[i] [bs, dims[i]] is Dense i's input,
+ * gate[i] the Dense's own output when a Relu follows it (NULL otherwise), dy [bs, dims[n]] the
+ * gradient at the chain's output.  g[i] [bs, dims[i+1]] receives the gradient at Dense i's
+ * output (g[n-1] may be NULL when gate[n-1] is NULL: dy is that gradient); dx (may be NULL) the
+ * gradient at the chain's input; dw[i] [dims[i], dims[i+1]] and db[i] (db or entries may be
+ * NULL) the parameter gradients, overwritten.  Small chains at small batch run as two kernels;
+ * anything else goes layer by layer through ag_relu_backward / ag_gemm / ag_bias_grad. */
+AG_API int ag_dense_chain_backward(ag_device *dev, ag_dtype dtype, int64_t bs, int32_t n_layers,
+                                   const int64_t *dims, const void *const *layer_in,
+                                   const void *const *weights, const void *const *gate,
+                                   const void *dy, void *const *g, void *dx, void *const *dw,
+                                   void *const *db);
+
 /* ------------------------------------------------------------ convolution */
 
 /* y = conv2(x, w) (+ bias) (then relu when fuse_relu != 0), NCHW.

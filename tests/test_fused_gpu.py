@@ -106,6 +106,47 @@ def test_dense_chain_equals_separate_calls(dev, dtype, case):
     assert torch.equal(fused, h)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(100, [256, 128, 84, 10], True), (37, [256, 128, 84, 10], False),
+                                  (5, [7, 3, 9], True), (300, [64, 32, 16], True),
+                                  (600, [64, 32, 16], True), (100, [40, 12], True)])
+def test_dense_chain_backward_equals_separate_calls(dev, dtype, case):
+    """One call gives the gradients of the layer-by-layer edges (products within the GEMM
+    tolerance, gates and zeros exactly)."""
+    bs, widths, want_dx = case
+    rng = np.random.default_rng(77 + bs)
+    n = len(widths) - 1
+    x = dev.tensor(_prep(rng.standard_normal((bs, widths[0])), dtype), dtype)
+    ws = [dev.tensor(_prep(rng.uniform(-0.3, 0.3, (widths[i], widths[i + 1])), dtype), dtype)
+          for i in range(n)]
+    relus = [i < n - 1 for i in range(n)] if len(widths) != 3 else [True, True]
+    has_bias = [i == n - 1 for i in range(n)]
+    pre, act = dev.dense_chain_forward_keep(x, ws, None, relus)
+    dy = dev.tensor(_prep(rng.standard_normal((bs, widths[-1])), dtype), dtype)
+    dx, dw, db, g = dev.dense_chain_backward(x, ws, relus, pre, act, dy, has_bias, want_dx)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+
+    def close(a, b):
+        a, b = a.float().cpu().numpy(), b.float().cpu().numpy()
+        return np.abs(a - b).max() <= tol * max(np.abs(b).max(), 1e-6)
+
+    incoming = dy
+    for l in range(n - 1, -1, -1):
+        gl = dev.relu_backward(pre[l], incoming) if relus[l] else incoming
+        if relus[l] or l < n - 1:
+            assert close(g[l], gl), l
+            assert torch.equal(g[l] == 0, gl == 0) or dtype == torch.bfloat16
+        lin = x if l == 0 else (act[l - 1] if relus[l - 1] else pre[l - 1])
+        assert close(dw[l], dev.dot(lin.T, gl)), l
+        if has_bias[l]:
+            assert close(db[l], dev.bias_grad(gl)), l
+        incoming = dev.dot(gl, ws[l].T)
+    if want_dx:
+        assert close(dx, incoming)
+    else:
+        assert dx is None
+
+
 NETS = [
     # bs, (ic, ih, iw), conv stages [(oc, f, relu, pool)], dense widths after the flatten
     (1000, (1, 28, 28), [(6, 5, True, (2, 2)), (16, 5, True, (2, 2))], [120, 84, 10]),   # LeNet5
