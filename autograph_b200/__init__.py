@@ -62,7 +62,9 @@ class Device:
     """≙ ``Device::builder().index(i).build()``.  Work is submitted to a CUDA
     stream: by default a torch stream created here, which also becomes torch's
     current stream for the GPU, so that torch allocations, copies and events are
-    ordered with the library's kernels."""
+    ordered with the library's kernels.  A second Device on the same GPU makes ITS stream
+    current: torch operations on tensors of the first must then be ordered by the caller
+    (``torch.cuda.set_stream(first.stream)`` or an event)."""
 
     def __init__(self, index: int = 0, stream=None):
         torch = _torch()

@@ -40,5 +40,15 @@ def dev():
     d.wait()
 
 
+@pytest.fixture(autouse=True)
+def _library_stream_is_current(request):
+    """torch ops of a GPU test (comparisons, copies) must run on the stream the library's kernels
+    run on; a Device created elsewhere in the session would have made its own stream current."""
+    if "dev" in request.fixturenames:
+        import torch
+        torch.cuda.set_stream(request.getfixturevalue("dev").stream)
+    yield
+
+
 def cycle(lo, hi, n):
     return (np.arange(n) % (hi - lo) + lo).astype(np.float32)

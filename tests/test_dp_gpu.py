@@ -57,14 +57,13 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_step_matches_global_batch(tmp_path):
+def test_two_gpu_step_matches_global_batch(tmp_path, dev):
     import torch.multiprocessing as mp
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     p0, p1 = np.load(tmp_path / "p0.npy"), np.load(tmp_path / "p1.npy")
     assert np.array_equal(p0, p1)                      # replicas stay identical
     import autograph_b200 as ag
-    dev = ag.Device(0)
     model = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)
     model.set_sgd(None)
     x, t = _data(200)
