@@ -191,6 +191,24 @@ class Device:
             _ptr(y)))
         return y
 
+    def conv2_relu_max_pool2_keep(self, x, w, bias=None, padding=(0, 0), stride=(1, 1),
+                                  dilation=(1, 1)):
+        """Conv2 -> Relu -> 2x2 MaxPool2 for a gradient-recording pass: returns (the
+        convolution's output, the pooled activations)."""
+        bs, ic, ih, iw = x.shape
+        oc, ic2, fh, fw = w.shape
+        if ic != ic2:
+            raise AgError(_capi.AG_ERR_SHAPE, "input channels do not match the weight")
+        o = _conv_options((fh, fw), padding, stride, dilation)
+        oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
+        pre = self.empty((bs, oc, oh, ow), x.dtype)
+        y = self.empty((bs, oc, oh // 2, ow // 2), x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_conv2_relu_max_pool2_forward_keep(
+            self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw,
+            _ptr(w.contiguous()), oc, _ptr(bias), ctypes.byref(o), _ptr(pre), _ptr(y)))
+        return pre, y
+
     def dense_forward(self, x, w, bias=None, relu=False):
         """≙ Dense::forward (x.dot(w) + bias) with an optional following Relu folded in."""
         if x.dtype != w.dtype:
@@ -505,6 +523,18 @@ class Device:
                                                 _ptr(x.contiguous()), _ptr(t), bs, classes,
                                                 ctypes.byref(loss)))
         return loss.value
+
+    def cross_entropy_loss_with_grad(self, x, t, dy=1.0):
+        """(loss as a one-element device tensor, dx) from one call; nothing synchronises."""
+        torch = _torch()
+        x, t = x.contiguous(), t.contiguous()
+        loss = torch.empty((1,), dtype=torch.float32, device=self.torch_device)
+        dx = self.empty(x.shape, x.dtype)
+        self._sync_in()
+        _capi.check(lib().ag_cross_entropy_loss_device_grad(
+            self._h, _dtype_code(x.dtype), _dtype_code(t.dtype), _ptr(x), _ptr(t), x.shape[0],
+            x.shape[1], _ptr(loss), ctypes.c_float(dy), _ptr(dx)))
+        return loss, dx
 
     def cross_entropy_loss_backward(self, x, t, dy=1.0):
         bs, classes = x.shape

@@ -93,6 +93,9 @@ _SIGNATURES = {
     "ag_conv2_relu_max_pool2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
                                                 _P, c_int64, _P, POINTER(ConvOptions), c_int,
                                                 c_int32, c_int32, _P]),
+    "ag_conv2_relu_max_pool2_forward_keep": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64,
+                                                     c_int64, _P, c_int64, _P, POINTER(ConvOptions),
+                                                     _P, _P]),
     "ag_conv2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int64,
                                  _P, POINTER(ConvOptions), c_int, _P]),
     "ag_conv2_backward_input": (c_int, [_P, c_int, _P, c_int64, c_int64, _P, c_int64, c_int64,
@@ -122,6 +125,8 @@ _SIGNATURES = {
     "ag_cross_entropy_loss": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64,
                                       POINTER(c_float)]),
     "ag_cross_entropy_loss_device": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, _P]),
+    "ag_cross_entropy_loss_device_grad": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, _P,
+                                                  c_float, _P]),
     "ag_cross_entropy_loss_backward": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, c_float,
                                                _P]),
     "ag_accuracy": (c_int, [_P, c_int, c_int, _P, _P, c_int64, c_int64, POINTER(c_uint64)]),

@@ -345,6 +345,39 @@ int ag_conv2_relu_max_pool2_forward(ag_device *dev, ag_dtype dtype, const void *
     return ag_max_pool2(dev, dtype, tmp, bs, oc, g.oh, g.ow, pool_h, pool_w, pool_h, pool_w, y);
 }
 
+int ag_conv2_relu_max_pool2_forward_keep(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
+                                         int64_t ic, int64_t ih, int64_t iw, const void *w,
+                                         int64_t oc, const void *bias, const ag_conv2_options *opt,
+                                         void *pre, void *y) {
+    AG_ENTER(dev);
+    AG_REQUIRE(is_float_dtype(dtype), AG_ERR_DTYPE, "Conv %d not implemented", (int)dtype);
+    ConvGeom g;
+    AG_TRY(make_geom(bs, ic, ih, iw, opt, &g));
+    AG_REQUIRE(g.oh >= 2 && g.ow >= 2, AG_ERR_SHAPE,
+               "pool window [2,2] does not fit the convolution output [%d,%d]", g.oh, g.ow);
+    if (bs == 0 || oc == 0) return AG_OK;
+    AG_REQUIRE(x && w && pre && y, AG_ERR_INVALID, "null tensor pointer");
+    const bool tensor_core = dtype == AG_BF16 && convtc::eligible_forward(bs, ic, ih, iw, oc, opt);
+    if (!tensor_core && oc < 32 && direct::eligible(bs, ic, ih, iw, oc, opt)) {
+        if (dtype == AG_F32)
+            return direct::forward<float>(dev, (const float *)x, bs, ic, ih, iw, (const float *)w,
+                                          oc, (const float *)bias, opt, true, true, (float *)y,
+                                          (float *)pre);
+        return direct::forward<__nv_bfloat16>(dev, (const __nv_bfloat16 *)x, bs, ic, ih, iw,
+                                              (const __nv_bfloat16 *)w, oc,
+                                              (const __nv_bfloat16 *)bias, opt, true, true,
+                                              (__nv_bfloat16 *)y, (__nv_bfloat16 *)pre);
+    }
+    AG_TRY(ag_conv2_forward(dev, dtype, x, bs, ic, ih, iw, w, oc, bias, opt, 0, pre));
+    if ((g.oh & 1) == 0 && (g.ow & 1) == 0)
+        return ag_relu_max_pool2_forward(dev, dtype, pre, bs, oc, g.oh, g.ow, y);
+    // odd planes: relu into the workspace, then the general pool
+    void *tmp = nullptr;
+    AG_TRY(workspace(dev, (size_t)bs * oc * g.oh * g.ow * dtype_size(dtype), &tmp));
+    AG_TRY(ag_relu(dev, dtype, pre, tmp, bs * oc * g.oh * g.ow));
+    return ag_max_pool2(dev, dtype, tmp, bs, oc, g.oh, g.ow, 2, 2, 2, 2, y);
+}
+
 int ag_conv2_backward_input(ag_device *dev, ag_dtype dtype, const void *w, int64_t oc, int64_t ic,
                             const void *dy, int64_t bs, int64_t ih, int64_t iw,
                             const ag_conv2_options *opt, void *dx) {

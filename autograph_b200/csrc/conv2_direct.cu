@@ -22,6 +22,11 @@ template <class T>
 struct GlobalOut {
     T *y;
     int b0, oc, h, w;  // first image of the CTA; channel count; height and width of y
+    T *pre_y;          // optional [bs][oc][ph][pw]: the convolution's output before relu / pool
+    int ph, pw;
+    __device__ __forceinline__ void pre(int g, int c, int yy, int xx, float v) const {
+        pre_y[(((int64_t)(b0 + g) * oc + c) * ph + yy) * pw + xx] = from_f32<T>(v);
+    }
     __device__ __forceinline__ void pooled(int g, int c, int py, int px, float v) const {
         y[(((int64_t)(b0 + g) * oc + c) * h + py) * w + px] = from_f32<T>(v);
     }
@@ -35,7 +40,8 @@ struct GlobalOut {
 template <class T, int FH, int FW, bool BWD>
 __global__ void __launch_bounds__(256, 2)
     conv2_direct_kernel(const T *__restrict__ x, const T *__restrict__ w,
-                        const T *__restrict__ bias, T *__restrict__ y, const Params p) {
+                        const T *__restrict__ bias, T *__restrict__ y, const Params p,
+                        T *__restrict__ pre_y) {
     extern __shared__ __align__(16) float smem[];
     const int img_elems = p.ic * p.ih * p.iw;
     const int taps = p.ic * FH * FW;
@@ -92,12 +98,22 @@ __global__ void __launch_bounds__(256, 2)
     __syncthreads();
 
     const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
-    GlobalOut<T> out{y, b0, p.oc, p.pool ? oh / 2 : oh, p.pool ? ow / 2 : ow};
-    if (p.split > 1)
+    GlobalOut<T> out{y, b0, p.oc, p.pool ? oh / 2 : oh, p.pool ? ow / 2 : ow, pre_y, oh, ow};
+    if (!BWD && p.keep_pre && p.fine)
+        compute_items_fine<T, FH, FW, GlobalOut<T>, 2, true>(s_img, s_w, s_bias, bias != nullptr, p,
+                                                            nimg, out);
+    else if (!BWD && p.keep_pre)
+        compute_items<T, FH, FW, GlobalOut<T>, true>(s_img, s_w, s_bias, bias != nullptr, p, nimg,
+                                                     out);
+    else if (p.split > 1)
         compute_items_split<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg,
                                        s_bias + p.ocp + 4, p.split, out);
+    else if (p.fine && p.pool)
+        compute_items_fine<T, FH, FW, GlobalOut<T>, 2, false>(s_img, s_w, s_bias, bias != nullptr, p,
+                                                             nimg, out);
     else if (p.fine)
-        compute_items_fine<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
+        compute_items_fine<T, FH, FW, GlobalOut<T>, 1, false>(s_img, s_w, s_bias, bias != nullptr, p,
+                                                             nimg, out);
     else
         compute_items<T, FH, FW>(s_img, s_w, s_bias, bias != nullptr, p, nimg, out);
 }
@@ -251,25 +267,27 @@ static size_t split_bytes(int split, int items_per_img) {
 
 template <class T, int FH, int FW, bool BWD>
 static int launch(ag_device *dev, const T *x, const T *w, const T *bias, T *y, const Params &p,
-                  size_t smem, int items_per_img) {
+                  size_t smem, int items_per_img, T *pre_y = nullptr) {
     auto kernel = conv2_direct_kernel<T, FH, FW, BWD>;
     if (smem > 48 * 1024)
         AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
     int threads = ((p.group * items_per_img * p.split + 31) / 32) * 32;
-    if (p.fine) threads *= 8;
+    if (p.fine) threads *= (p.pool || p.keep_pre) ? 4 : 8;
     if (threads > 256) threads = 256;
     if (threads < 64) threads = 64;
     const unsigned grid = (unsigned)ceil_div(p.bs, p.group);
-    kernel<<<grid, threads, smem, dev->stream>>>(x, w, bias, y, p);
+    kernel<<<grid, threads, smem, dev->stream>>>(x, w, bias, y, p, pre_y);
     AG_CHECK_LAUNCH();
     return AG_OK;
 }
 
 template <class T>
 int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw, const T *w,
-            int64_t oc, const T *bias, const ag_conv2_options *o, bool relu, bool pool, T *y) {
+            int64_t oc, const T *bias, const ag_conv2_options *o, bool relu, bool pool, T *y,
+            T *pre) {
     Params p;
+    p.keep_pre = pre != nullptr;  // callers pass it only with fewer than 32 output channels
     p.bs = (int)bs; p.ic = (int)ic; p.ih = (int)ih; p.iw = (int)iw; p.oc = (int)oc;
     p.ocp = ((int)oc + 1) & ~1;
     p.relu = relu;
@@ -289,11 +307,11 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
     // no channel split in the forward direction: its sums must keep the order of the
     // whole-network kernel and of the fused conv + pool call (bit-for-bit equality)
     p.split = 1;
-    // One image per CTA with fewer than 128 work items and no pool: finer items instead
-    // (the same sums in the same order on more threads).
-    p.fine = !pool && group == 1 && items_per_img < 128 && (ow & 1) == 0;
+    // One image per CTA with fewer than 128 work items: finer items instead (the same sums
+    // in the same order on more threads).
+    p.fine = group == 1 && items_per_img < 128 && (ow & 1) == 0 && (oh & 1) == 0;
     // Many output channels, one image per CTA anyway: the banded kernel (coalesced stores).
-    if (oc >= 32 && group == 1 && bs <= 2147483647) {
+    if (oc >= 32 && group == 1 && bs <= 2147483647 && pre == nullptr) {
         const int out_w = pool ? ow / 2 : ow;
         const int band_rows = pool ? PBH / 2 : PBH;
         const size_t smem_b = (size_t)(((p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes +
@@ -304,8 +322,8 @@ int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int6
         }
     }
     const size_t smem = (size_t)(((group * p.ic * p.ih * p.iw + 3) & ~3) * 4) + (size_t)w_bytes;
-    if (fh == 5) return launch<T, 5, 5, false>(dev, x, w, bias, y, p, smem, items_per_img);
-    return launch<T, 3, 3, false>(dev, x, w, bias, y, p, smem, items_per_img);
+    if (fh == 5) return launch<T, 5, 5, false>(dev, x, w, bias, y, p, smem, items_per_img, pre);
+    return launch<T, 3, 3, false>(dev, x, w, bias, y, p, smem, items_per_img, pre);
 }
 
 bool eligible_backward_input(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int64_t oc,
@@ -358,10 +376,11 @@ template int backward_input<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, i
 
 template int forward<float>(ag_device *, const float *, int64_t, int64_t, int64_t, int64_t,
                             const float *, int64_t, const float *, const ag_conv2_options *, bool,
-                            bool, float *);
+                            bool, float *, float *);
 template int forward<__nv_bfloat16>(ag_device *, const __nv_bfloat16 *, int64_t, int64_t, int64_t,
                                     int64_t, const __nv_bfloat16 *, int64_t, const __nv_bfloat16 *,
-                                    const ag_conv2_options *, bool, bool, __nv_bfloat16 *);
+                                    const ag_conv2_options *, bool, bool, __nv_bfloat16 *,
+                                    __nv_bfloat16 *);
 
 }  // namespace direct
 }  // namespace ag

@@ -15,7 +15,9 @@ bool eligible(int64_t bs, int64_t ic, int64_t ih, int64_t iw, int64_t oc,
 // output is [bs, oc, oh/2, ow/2], else [bs, oc, oh, ow].
 template <class T>
 int forward(ag_device *dev, const T *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw, const T *w,
-            int64_t oc, const T *bias, const ag_conv2_options *o, bool relu, bool pool, T *y);
+            int64_t oc, const T *bias, const ag_conv2_options *o, bool relu, bool pool, T *y,
+            T *pre = nullptr);  // pre: optional copy of the convolution's output before relu / pool
+                                // (fewer than 32 output channels only)
 
 // dx = the gradient of conv2(x, w) with respect to x, given dy [bs, oc, oh, ow]
 // and w [oc, ic, fh, fw]: the same kernel run on the transposed problem.

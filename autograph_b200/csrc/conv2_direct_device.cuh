@@ -36,6 +36,7 @@ struct Params {
     bool relu, pool;
     int split;       // threads per work item (ranges of input channels), stand-alone kernel only
     bool fine = false;  // 1x2-pixel work items (compute_items_fine), stand-alone kernel only
+    bool keep_pre = false;  // also store the values before the relu, stand-alone kernel only
 };
 
 constexpr int OC_T = 2;  // output channels per thread
@@ -149,7 +150,9 @@ __device__ __forceinline__ void accumulate_item(float (&acc)[PBH][PBW][OC_T], co
 //   out.plain(g, oc, y, x, v)     one convolution output                  (!p.pool)
 // v has been rounded to T (after the sum and again after the bias) like a
 // store / reload of the layer's output would.
-template <class T, int FH, int FW, class Out>
+// KEEP: every value is also handed to out.pre(g, oc, y, x, v) before the relu (the
+// convolution's own output, which the backward edges of a following Relu gate on).
+template <class T, int FH, int FW, class Out, bool KEEP = false>
 __device__ __forceinline__ void finish_item(const float (&acc)[PBH][PBW][OC_T],
                                             const float *s_bias, bool has_bias, const Params &p,
                                             const Item &it, Out out) {
@@ -165,6 +168,9 @@ __device__ __forceinline__ void finish_item(const float (&acc)[PBH][PBW][OC_T],
             for (int b = 0; b < PBW; ++b) {
                 float t = to_f32(from_f32<T>(acc[a][b][o]));
                 if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
+                if constexpr (KEEP) {
+                    if (it.y0 + a < oh && it.x0 + b < ow) out.pre(it.g, oc, it.y0 + a, it.x0 + b, t);
+                }
                 if (p.relu) t = (t >= 0.f) ? t : 0.f;
                 v[a][b] = t;
             }
@@ -199,7 +205,7 @@ __device__ __forceinline__ void finish_item(const float (&acc)[PBH][PBW][OC_T],
 // Consecutive threads take consecutive channel pairs of one pixel block, so a filter
 // tap is one 8-byte shared-memory load per thread (contiguous across the channel
 // pairs) and the input patch loads broadcast.
-template <class T, int FH, int FW, class Out>
+template <class T, int FH, int FW, class Out, bool KEEP = false>
 __device__ __forceinline__ void compute_items(const float *s_img, const float *s_w,
                                               const float *s_bias, bool has_bias, const Params &p,
                                               int nimg, Out out) {
@@ -218,34 +224,43 @@ __device__ __forceinline__ void compute_items(const float *s_img, const float *s
 #pragma unroll
                 for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
         accumulate_item<FH, FW>(acc, s_img, s_w, p, it, 0, p.ic);
-        finish_item<T, FH, FW>(acc, s_bias, has_bias, p, it, out);
+        finish_item<T, FH, FW, Out, KEEP>(acc, s_bias, has_bias, p, it, out);
     }
 }
 
-// Plain convolution output (no pool) for a CTA with few work items (one image of a small
-// layer): an item is 1 x 2 pixels x OC_T channels, eight times as many threads as above.
-// Every output is the same chain of FFMAs in the same (channel, row, column) order as in
-// accumulate_item, so the values are identical.  Needs an even output width.
-template <class T, int FH, int FW, class Out>
+// A CTA with few work items (one image of a small layer): an item is BH x 2 pixels x OC_T
+// channels (BH = 1 without a pool, 2 with one: the item is then exactly one pool window per
+// channel), four to eight times as many threads as above.  Every output is the same chain of
+// FFMAs in the same (channel, row, column) order as in accumulate_item and goes through the
+// same epilogue, so the values are identical.  Needs an even output width (and height for
+// BH = 2).
+template <class T, int FH, int FW, class Out, int BH, bool KEEP>
 __device__ __forceinline__ void compute_items_fine(const float *s_img, const float *s_w,
                                                    const float *s_bias, bool has_bias,
                                                    const Params &p, int nimg, Out out) {
     const int oh = p.ih - FH + 1, ow = p.iw - FW + 1;
-    const int nbx = ow / 2, n_ocg = p.ocp / OC_T;
-    const int items_per_img = n_ocg * oh * nbx;
+    const int nbx = ow / 2, nby = oh / BH, n_ocg = p.ocp / OC_T;
+    const int items_per_img = n_ocg * nby * nbx;
     const int img_elems = p.ic * p.ih * p.iw;
     for (int item = threadIdx.x; item < nimg * items_per_img; item += blockDim.x) {
         const int g = item / items_per_img;
         const int r = item - g * items_per_img;
         const int blk = r / n_ocg, oc0 = (r - blk * n_ocg) * OC_T;
-        const int y0 = blk / nbx, x0 = (blk - y0 * nbx) * 2;
-        float acc[2][OC_T] = {{0.f, 0.f}, {0.f, 0.f}};
+        const int by = blk / nbx;
+        const int y0 = by * BH, x0 = (blk - by * nbx) * 2;
+        float acc[BH][2][OC_T];
+#pragma unroll
+        for (int a = 0; a < BH; ++a)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int o = 0; o < OC_T; ++o) acc[a][b][o] = 0.f;
         const float *img = s_img + g * img_elems + y0 * p.iw + x0;
         for (int ci = 0; ci < p.ic; ++ci) {
-            float patch[FH][FW + 1];
+            float patch[FH + BH - 1][FW + 1];
             const float *pi = img + ci * p.ih * p.iw;
 #pragma unroll
-            for (int a = 0; a < FH; ++a)
+            for (int a = 0; a < FH + BH - 1; ++a)
 #pragma unroll
                 for (int b = 0; b < FW + 1; ++b) patch[a][b] = pi[a * p.iw + b];
             const float *wc = s_w + ci * FH * FW * p.ocp + oc0;
@@ -255,23 +270,44 @@ __device__ __forceinline__ void compute_items_fine(const float *s_img, const flo
                 for (int fj = 0; fj < FW; ++fj) {
                     const float2 wv = *reinterpret_cast<const float2 *>(wc + (fi * FW + fj) * p.ocp);
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        acc[b][0] = fmaf(patch[fi][fj + b], wv.x, acc[b][0]);
-                        acc[b][1] = fmaf(patch[fi][fj + b], wv.y, acc[b][1]);
-                    }
+                    for (int a = 0; a < BH; ++a)
+#pragma unroll
+                        for (int b = 0; b < 2; ++b) {
+                            acc[a][b][0] = fmaf(patch[fi + a][fj + b], wv.x, acc[a][b][0]);
+                            acc[a][b][1] = fmaf(patch[fi + a][fj + b], wv.y, acc[a][b][1]);
+                        }
                 }
         }
 #pragma unroll
         for (int o = 0; o < OC_T; ++o) {
             const int oc = oc0 + o;
             if (oc >= p.oc) break;
+            float v[BH][2];
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                float t = to_f32(from_f32<T>(acc[b][o]));
-                if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
-                if (p.relu) t = (t >= 0.f) ? t : 0.f;
-                out.plain(g, oc, y0, x0 + b, t);
+            for (int a = 0; a < BH; ++a)
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    float t = to_f32(from_f32<T>(acc[a][b][o]));
+                    if (has_bias) t = to_f32(from_f32<T>(t + s_bias[oc]));
+                    if constexpr (KEEP) out.pre(g, oc, y0 + a, x0 + b, t);
+                    if (p.relu) t = (t >= 0.f) ? t : 0.f;
+                    v[a][b] = t;
+                }
+            if constexpr (BH == 2) {
+                if (p.pool) {
+                    // window order (0,0),(0,1),(1,0),(1,1); the first maximum wins
+                    float m = v[0][0];
+                    if (v[0][1] > m) m = v[0][1];
+                    if (v[1][0] > m) m = v[1][0];
+                    if (v[1][1] > m) m = v[1][1];
+                    out.pooled(g, oc, y0 / 2, x0 / 2, m);
+                    continue;
+                }
             }
+#pragma unroll
+            for (int a = 0; a < BH; ++a)
+#pragma unroll
+                for (int b = 0; b < 2; ++b) out.plain(g, oc, y0 + a, x0 + b, v[a][b]);
         }
     }
 }

@@ -63,7 +63,7 @@ __global__ void sum_rows_kernel(const float *__restrict__ v, int64_t n, float *_
 template <class T, class L>
 __global__ void __launch_bounds__(1024)
     ce_loss_small_kernel(const T *__restrict__ x, const L *__restrict__ t, int bs, int classes,
-                         float *__restrict__ out) {
+                         float *__restrict__ out, float dy, T *__restrict__ dx) {
     __shared__ float part[1024];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     part[threadIdx.x] = 0.f;
@@ -83,6 +83,13 @@ __global__ void __launch_bounds__(1024)
                 if ((uint32_t)i == tt) xt = v;
             }
             part[r] = logf(s) - (xt - m);
+            if (dx != nullptr)  // the gradient the backward edge would compute: dy (softmax - onehot)
+                for (int i = 0; i < classes; ++i) {
+                    const float onehot = ((uint32_t)i == tt) ? 1.f : 0.f;
+                    const float g = __fmul_rn(
+                        dy, __fsub_rn(__fdiv_rn(expf(to_f32(row[i]) - m), s), onehot));
+                    dx[(int64_t)r * classes + i] = from_f32<T>(g);
+                }
         }
     } else {
         for (int r = warp; r < bs; r += 32) {
@@ -93,11 +100,18 @@ __global__ void __launch_bounds__(1024)
             float s = 0.f;
             for (int i = lane; i < classes; i += 32) s += expf(to_f32(row[i]) - m);
             s = warp_sum(s);
+            const uint32_t tt = label_at(t, r);
             if (lane == 0) {
-                uint32_t tt = label_at(t, r);
                 float xt = tt < (uint32_t)classes ? to_f32(row[tt]) : 0.f;
                 part[r] = logf(s) - (xt - m);
             }
+            if (dx != nullptr)
+                for (int i = lane; i < classes; i += 32) {
+                    const float onehot = ((uint32_t)i == tt) ? 1.f : 0.f;
+                    const float g = __fmul_rn(
+                        dy, __fsub_rn(__fdiv_rn(expf(to_f32(row[i]) - m), s), onehot));
+                    dx[(int64_t)r * classes + i] = from_f32<T>(g);
+                }
         }
     }
     __syncthreads();
@@ -158,11 +172,18 @@ static unsigned warp_grid(int64_t rows, int threads, int sms) {
 // Sum of the row losses into *loss_dev (device memory); no synchronisation.
 template <class T, class L>
 static int ce_loss_device(ag_device *dev, const T *x, const L *t, int64_t bs, int classes,
-                          float *loss_dev) {
+                          float *loss_dev, float dy = 0.f, T *dx = nullptr) {
     if (bs <= 1024) {
-        ce_loss_small_kernel<T, L><<<1, 1024, 0, dev->stream>>>(x, t, (int)bs, classes, loss_dev);
+        ce_loss_small_kernel<T, L><<<1, 1024, 0, dev->stream>>>(x, t, (int)bs, classes, loss_dev,
+                                                                dy / (float)bs, dx);
         AG_CHECK_LAUNCH();
         return AG_OK;
+    }
+    if (dx != nullptr) {
+        const int threads = 256;
+        ce_backward_kernel<T, L><<<warp_grid(bs, threads, dev->sm_count), threads, 0, dev->stream>>>(
+            x, t, bs, classes, dy / (float)bs, dx);
+        AG_CHECK_LAUNCH();
     }
     void *ws;
     AG_TRY(workspace(dev, sizeof(float) * (size_t)bs, &ws));
@@ -237,6 +258,19 @@ int ag_cross_entropy_loss_device(ag_device *dev, ag_dtype dtype, ag_dtype label_
     AG_REQUIRE(x && t, AG_ERR_INVALID, "null tensor pointer");
     AG_DISPATCH_XT(dtype, label_dtype, T, L,
                    return ce_loss_device<T, L>(dev, (const T *)x, (const L *)t, bs, (int)classes, loss_dev););
+}
+
+int ag_cross_entropy_loss_device_grad(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
+                                      const void *x, const void *t, int64_t bs, int64_t classes,
+                                      float *loss_dev, float dy, void *dx) {
+    AG_ENTER(dev);
+    AG_TRY(check_ce_args(dtype, label_dtype, bs, classes));
+    AG_REQUIRE(loss_dev != nullptr, AG_ERR_INVALID, "loss_dev is null");
+    if (bs == 0) return ag_fill_zero(dev, loss_dev, sizeof(float));
+    AG_REQUIRE(x && t && dx, AG_ERR_INVALID, "null tensor pointer");
+    AG_DISPATCH_XT(dtype, label_dtype, T, L,
+                   return ce_loss_device<T, L>(dev, (const T *)x, (const L *)t, bs, (int)classes,
+                                               loss_dev, dy, (T *)dx););
 }
 
 int ag_cross_entropy_loss_backward(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,

@@ -205,6 +205,18 @@ class Conv2 : public Layer {
         check(ag_conv2_forward(x.device(), x.dtype(), x.data(), bs, ic, ih, iw, w.value.data(), oc,
                                has_bias ? b.value.data() : nullptr, &copt, relu ? 1 : 0,
                                y.data()));
+        return attach(pool, input, y);
+    }
+    // The layer's output variable around y = conv2(input) (+ bias) that the caller has
+    // computed: the backward edges of Conv2::forward.
+    Variable attach(Pool &pool, const Variable &input, const Tensor &y) {
+        const Tensor &x = input.value;
+        const int64_t bs = x.dim(0), ic = x.dim(1), ih = x.dim(2), iw = x.dim(3);
+        const int64_t oc = weight.value.dim(0), oh = y.dim(2), ow = y.dim(3);
+        const Shape filter = {weight.value.dim(2), weight.value.dim(3)};
+        const ag_conv2_options copt = to_c_options(filter, options);
+        Variable w = weight.to_variable();
+        Variable b = has_bias ? bias.to_variable() : Variable{};
         VariableBuilder builder;
         Pool *pp = &pool;
         if (input.node) {
@@ -388,11 +400,18 @@ inline bool relu_pool_fusable(const Variable &input, const MaxPool2 &mp) {
            x.ndim() == 4 && x.is_standard_layout() && x.dim(2) >= 2 && x.dim(3) >= 2 &&
            x.dim(2) % 2 == 0 && x.dim(3) % 2 == 0;
 }
+inline Variable relu_pool_attach(Pool &pool, const Variable &input, const Tensor &y);
 inline Variable relu_pool_forward(Pool &pool, const Variable &input) {
     const Tensor &x = input.value;
     const int64_t bs = x.dim(0), c = x.dim(1), ih = x.dim(2), iw = x.dim(3);
     Tensor y = Tensor::uninit(pool, {bs, c, ih / 2, iw / 2}, x.dtype());
     check(ag_relu_max_pool2_forward(x.device(), x.dtype(), x.data(), bs, c, ih, iw, y.data()));
+    return relu_pool_attach(pool, input, y);
+}
+// The pooled variable around y = max_pool2(relu(input)) that the caller has computed.
+inline Variable relu_pool_attach(Pool &pool, const Variable &input, const Tensor &y) {
+    const Tensor &x = input.value;
+    const int64_t bs = x.dim(0), c = x.dim(1), ih = x.dim(2), iw = x.dim(3);
     VariableBuilder builder;
     Pool *pp = &pool;
     if (input.node) {
@@ -405,6 +424,28 @@ inline Variable relu_pool_forward(Pool &pool, const Variable &input) {
         });
     }
     return builder.build(y);
+}
+
+// Conv2 -> Relu -> 2x2 MaxPool2 of a gradient-recording pass in one forward call that keeps
+// the convolution's output; the two nodes (convolution, Relu + pool) are those of the
+// separate layers.
+inline Variable conv_relu_pool_forward(Pool &pool, Conv2 &conv, const Variable &input) {
+    const Tensor &x = input.value;
+    if (x.ndim() != 4 || x.dim(1) != conv.weight.value.dim(1))
+        throw Error(AG_ERR_SHAPE, "Conv2: input channels do not match the weight");
+    if (!x.is_standard_layout()) throw Error(AG_ERR_SHAPE, "Conv2 needs standard layout");
+    const int64_t bs = x.dim(0), ic = x.dim(1), ih = x.dim(2), iw = x.dim(3);
+    const int64_t oc = conv.weight.value.dim(0);
+    const Shape filter = {conv.weight.value.dim(2), conv.weight.value.dim(3)};
+    const ag_conv2_options copt = to_c_options(filter, conv.options);
+    int64_t oh = 0, ow = 0;
+    check(ag_conv2_output_shape(ih, iw, &copt, &oh, &ow));
+    Tensor pre = Tensor::uninit(pool, {bs, oc, oh, ow}, x.dtype());
+    Tensor y = Tensor::uninit(pool, {bs, oc, oh / 2, ow / 2}, x.dtype());
+    check(ag_conv2_relu_max_pool2_forward_keep(
+        x.device(), x.dtype(), x.data(), bs, ic, ih, iw, conv.weight.value.data(), oc,
+        conv.has_bias ? conv.bias.value.data() : nullptr, &copt, pre.data(), y.data()));
+    return relu_pool_attach(pool, conv.attach(pool, input, pre), y);
 }
 
 // Flatten (layer.rs:1224-1231): reshape to [batch, rest]; the edge reshapes back.
@@ -446,6 +487,18 @@ inline Loss cross_entropy_loss(Pool &pool, const Variable &input, const Tensor &
     if (x.ndim() != 2 || target.ndim() != 1 || target.dim(0) != x.dim(0))
         throw Error(AG_ERR_SHAPE, "Expected target with shape [" + std::to_string(x.dim(0)) + "]");
     Loss loss;
+    if (loss_dev && input.node) {
+        // The only consumer of this loss's node is Loss::backward with the seed gradient 1:
+        // compute the edge's result now, in the kernel that already has every row's sums.
+        Tensor dx = Tensor::uninit(pool, x.shape(), x.dtype());
+        check(ag_cross_entropy_loss_device_grad(x.device(), x.dtype(), target.dtype(), x.data(),
+                                                target.data(), x.dim(0), x.dim(1), loss_dev, 1.f,
+                                                dx.data()));
+        loss.node = std::make_shared<Node>();
+        ++input.node->pending;
+        loss.node->edges.push_back(Edge{input.node, [=](const Tensor &, Tensor *) { return dx; }});
+        return loss;
+    }
     if (loss_dev)
         check(ag_cross_entropy_loss_device(x.device(), x.dtype(), target.dtype(), x.data(),
                                            target.data(), x.dim(0), x.dim(1), loss_dev));

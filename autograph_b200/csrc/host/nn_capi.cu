@@ -427,6 +427,23 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                 i += pool_ok ? 2 : 1;
                 continue;
             }
+            // Recording gradients, Relu and an even 2x2 pool next: one forward call that keeps
+            // the convolution's output for the backward edges.
+            if (conv->records_gradient(v) && relu1 && i + 2 < n && v.value.ndim() == 4 &&
+                v.value.is_standard_layout() && v.value.dim(1) == conv->weight.value.dim(1)) {
+                auto *mp = dynamic_cast<MaxPool2 *>(m->layers[i + 2].get());
+                const Shape f = {conv->weight.value.dim(2), conv->weight.value.dim(3)};
+                const ag_conv2_options copt = to_c_options(f, conv->options);
+                int64_t oh = 0, ow = 0;
+                if (mp && mp->filter[0] == 2 && mp->filter[1] == 2 && mp->stride[0] == 2 &&
+                    mp->stride[1] == 2 &&
+                    ag_conv2_output_shape(v.value.dim(2), v.value.dim(3), &copt, &oh, &ow) == AG_OK &&
+                    oh >= 2 && ow >= 2 && oh % 2 == 0 && ow % 2 == 0) {
+                    v = conv_relu_pool_forward(m->pool, *conv, v);
+                    i += 2;
+                    continue;
+                }
+            }
         } else if (auto *dense = dynamic_cast<Dense *>(l)) {
             // A run of Dense (+ Relu) layers goes to one fused call.
             if (!dense->records_gradient(v) && v.value.ndim() == 2 && v.value.is_standard_layout()) {

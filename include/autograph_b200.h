@@ -217,6 +217,17 @@ typedef struct ag_conv_stage {
     int32_t pool[2];
 } ag_conv_stage;
 
+/* Conv2::forward -> Relu::forward -> MaxPool2::forward (2x2 window and stride) for a pass that
+ * records gradients: pre [bs, oc, oh, ow] receives the convolution's output (+ bias), which the
+ * Relu's and the pool's backward edges read (layer.rs:1283-1296, 1203-1212), y [bs, oc, oh/2, ow/2]
+ * the pooled activations.  One kernel for the shapes the direct kernel takes (fewer than 32 output
+ * channels), otherwise ag_conv2_forward followed by ag_relu_max_pool2_forward; the values are those
+ * of the separate calls. */
+AG_API int ag_conv2_relu_max_pool2_forward_keep(ag_device *dev, ag_dtype dtype, const void *x,
+                                                int64_t bs, int64_t ic, int64_t ih, int64_t iw,
+                                                const void *w, int64_t oc, const void *bias,
+                                                const ag_conv2_options *opt, void *pre, void *y);
+
 /* Inference fusion of a whole small network: n_conv stages of Conv2::forward -> Relu::forward ->
  * MaxPool2::forward (layer.rs:1035-1047, 1254-1267, 1193-1216), Flatten::forward
  * (layer.rs:1297-1309) and n_dense Dense::forward / Relu::forward pairs (layer.rs:1134-1143) --
@@ -368,6 +379,14 @@ AG_API int ag_cross_entropy_loss(ag_device *dev, ag_dtype dtype, ag_dtype label_
 AG_API int ag_cross_entropy_loss_device(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
                                         const void *x, const void *t, int64_t bs, int64_t classes,
                                         float *loss_dev);
+
+/* ag_cross_entropy_loss_device together with the gradient its backward edge would produce for an
+ * output gradient dy (ag_cross_entropy_loss_backward(.., dy, dx)): one kernel for up to 1024 rows,
+ * where loss and gradient share the row maxima and sums; two launches beyond.  For steps whose
+ * loss is always differentiated with the seed gradient 1 (Node::backward, autograd.rs:224-235). */
+AG_API int ag_cross_entropy_loss_device_grad(ag_device *dev, ag_dtype dtype, ag_dtype label_dtype,
+                                             const void *x, const void *t, int64_t bs,
+                                             int64_t classes, float *loss_dev, float dy, void *dx);
 
 /* ≙ kernels::cross_entropy_loss_backward_<X>_<T>
  * (src/learn/neural_network/criterion.rs:79-137, 154-184):

@@ -48,6 +48,11 @@ def test_criterion_random_vs_oracle(dev, dtype):
         assert abs(loss - ref) <= 2e-6 * bs * max(abs(ref) / bs, 1.0) + 1e-4
         dx = dev.cross_entropy_loss_backward(xd, td, 0.5).float().cpu().numpy()
         want = oracle.cross_entropy_loss_backward(x, t, 0.5, bf16=dtype == torch.bfloat16)
+        # loss and gradient from one call
+        loss1, dx1 = dev.cross_entropy_loss_with_grad(xd, td, 0.5)
+        assert abs(float(loss1.cpu()[0]) - loss) <= 1e-6 * max(abs(loss), 1.0)
+        dx1 = dx1.float().cpu().numpy()
+        assert np.abs(dx1 - want).max() <= (1e-2 if dtype == torch.bfloat16 else 2e-5) * max(np.abs(want).max(), 1e-30)
         np.testing.assert_allclose(dx, want, rtol=1e-2 if dtype == torch.bfloat16 else 2e-5,
                                    atol=1e-8)
         assert dev.accuracy(xd, td) == oracle.accuracy(x, t)

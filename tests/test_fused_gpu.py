@@ -44,6 +44,10 @@ def test_conv_relu_pool_equals_separate_calls(dev, dtype, shape):
                 y = dev.relu(y)
             sep = dev.max_pool2(y, pool)
             assert torch.equal(fused, sep), (shape, bias is not None, relu)
+        if pool == (2, 2):  # the gradient-recording form keeps the convolution's output
+            pre, kept = dev.conv2_relu_max_pool2_keep(xd, wd, bias=bias)
+            assert torch.equal(pre, dev.conv2_forward(xd, wd, bias=bias)), (shape, bias is not None)
+            assert torch.equal(kept, dev.max_pool2(dev.relu(pre), pool)), (shape, bias is not None)
     # against the oracle (f64 accumulation): tolerance of the convolution
     ref = oracle.max_pool2(oracle.relu(oracle.conv2_naive(x, w, acc64=True)), pool)
     got = dev.conv2_relu_max_pool2(xd, wd, pool=pool).float().cpu().numpy()
