@@ -57,6 +57,7 @@ struct TrainEntry {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     cudaGraphNode_t x_node = nullptr, t_node = nullptr;
+    const void *x_src = nullptr, *t_src = nullptr;  // what the two copy nodes read at present
     Pool::Parked parked;
     uint64_t kernels = 0;
     int seen = 0;
@@ -870,12 +871,19 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
         *loss_host = *m->loss_pinned;
     };
     if (e->exec) {
-        cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->x_node, e->x_stage.data(), x_host,
-                                                    e->x_stage.nbytes(), kin),
-                "graph input update");
-        cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->t_node, e->t_stage.data(), t_host,
-                                                    e->t_stage.nbytes(), kin),
-                "graph label update");
+        // a loader that refills the same buffers needs no node update
+        if (e->x_src != x_host) {
+            cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->x_node, e->x_stage.data(), x_host,
+                                                        e->x_stage.nbytes(), kin),
+                    "graph input update");
+            e->x_src = x_host;
+        }
+        if (e->t_src != t_host) {
+            cuda_ok(cudaGraphExecMemcpyNodeSetParams1D(e->exec, e->t_node, e->t_stage.data(), t_host,
+                                                        e->t_stage.nbytes(), kin),
+                    "graph label update");
+            e->t_src = t_host;
+        }
         cuda_ok(cudaGraphLaunch(e->exec, stream), "cudaGraphLaunch");
         ::ag::count_launches(e->kernels);
         finish();
@@ -933,6 +941,8 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
         m->graphs_enabled = false;
         return false;
     }
+    e->x_src = x_host;  // the copy nodes were captured with this call's buffers
+    e->t_src = t_host;
     cuda_ok(cudaGraphLaunch(e->exec, stream), "cudaGraphLaunch");
     ::ag::count_launches(e->kernels);
     finish();
