@@ -723,16 +723,23 @@ class Model:
                                               ctypes.c_float(lr), ctypes.byref(loss)))
         return loss.value
 
-    def train_forward_backward(self, x_dev, t_dev):
-        """Returns (loss, grad bucket pointer, bucket length); the bucket can be all-reduced."""
+    def train_forward_backward(self, x_dev, t_dev, sync=True):
+        """Returns (loss, grad bucket pointer, bucket length); the bucket can be all-reduced.
+        sync=False only enqueues the step (loss is None; read it with last_loss())."""
         bs, c, h, w = x_dev.shape
         loss = ctypes.c_float()
         bucket = ctypes.c_void_p()
         length = ctypes.c_int64()
         _capi.check(lib().ag_model_train_forward_backward(
-            self._h, _ptr(x_dev), _ptr(t_dev), bs, c, h, w, ctypes.byref(loss),
+            self._h, _ptr(x_dev), _ptr(t_dev), bs, c, h, w, ctypes.byref(loss) if sync else None,
             ctypes.byref(bucket), ctypes.byref(length)))
-        return loss.value, bucket.value, length.value
+        return (loss.value if sync else None), bucket.value, length.value
+
+    def last_loss(self) -> float:
+        """Waits for the stream and returns the loss of the last enqueued step."""
+        loss = ctypes.c_float()
+        _capi.check(lib().ag_model_last_loss(self._h, ctypes.byref(loss)))
+        return loss.value
 
     def apply_update(self, lr):
         _capi.check(lib().ag_model_apply_update(self._h, ctypes.c_float(lr)))

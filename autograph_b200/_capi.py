@@ -149,6 +149,7 @@ _SIGNATURES = {
     "ag_model_train_forward_backward": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64,
                                                 POINTER(c_float), POINTER(_P), POINTER(c_int64)]),
     "ag_model_apply_update": (c_int, [_P, c_float]),
+    "ag_model_last_loss": (c_int, [_P, POINTER(c_float)]),
 }
 
 _lib = None

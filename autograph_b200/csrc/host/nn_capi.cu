@@ -70,6 +70,8 @@ struct ag_model {
     std::vector<TrainEntry> train_graphs;
     Tensor loss_dev;             // one f32: the loss of the step in flight
     float *loss_pinned = nullptr;
+    float loss_eager = 0.f;      // loss of the last step that did not go through a graph
+    bool loss_in_flight = false; // the last step left its loss in loss_pinned, not yet read
     std::vector<GraphEntry> graphs;
     uint64_t tick = 0;
     bool graphs_enabled = true;
@@ -867,6 +869,8 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
             throw Error(AG_ERR_CUDA, std::string(what) + " failed: " + cudaGetErrorString(err));
     };
     auto finish = [&]() {
+        m->loss_in_flight = loss_host == nullptr;
+        if (!loss_host) return;  // the caller reads the loss later (ag_model_last_loss)
         cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
         *loss_host = *m->loss_pinned;
     };
@@ -1146,7 +1150,7 @@ int ag_model_train_step(ag_model *model, const void *x_host, const uint8_t *t_ho
 int ag_model_train_forward_backward(ag_model *model, const void *x_dev, const uint8_t *t_dev,
                                     int64_t bs, int64_t c, int64_t h, int64_t w, float *loss_host,
                                     void **grad_bucket, int64_t *grad_len) {
-    AG_REQUIRE(model && t_dev && loss_host, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(model && t_dev, AG_ERR_INVALID, "null argument");
     AG_ENTER(model->dev);
     AG_HOST_GUARD({
         if (bs < 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
@@ -1154,11 +1158,25 @@ int ag_model_train_forward_backward(ag_model *model, const void *x_dev, const ui
         if (!train_step_graph(model, x_dev, t_dev, bs, c, h, w, 0.f, loss_host, false, true)) {
             Tensor x = input_tensor(model, x_dev, false, bs, c, h, w);
             Tensor t = Tensor::external(model->dev, const_cast<uint8_t *>(t_dev), {bs}, AG_U8);
-            *loss_host = forward_backward(model, x, t);
+            model->loss_eager = forward_backward(model, x, t);
+            model->loss_in_flight = false;
+            if (loss_host) *loss_host = model->loss_eager;
         }
         if (grad_bucket) *grad_bucket = model->grads.data();
         if (grad_len) *grad_len = model->bucket_len;
     })
+}
+
+int ag_model_last_loss(ag_model *model, float *loss_host) {
+    AG_REQUIRE(model && loss_host, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    if (model->loss_in_flight) {
+        AG_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)ag_device_stream(model->dev)));
+        model->loss_eager = *model->loss_pinned;
+        model->loss_in_flight = false;
+    }
+    *loss_host = model->loss_eager;
+    return AG_OK;
 }
 
 int ag_model_apply_update(ag_model *model, float lr) {

@@ -312,11 +312,14 @@ def train_data_parallel(torch, ag, dp, dev, rank, world, barrier, max_over_ranks
 
     def step(i):
         nonlocal bucket
-        loss, ptr, length = m.train_forward_backward(x, t)
+        # forward/backward, all-reduce and update are enqueued back to back on one stream;
+        # the host reads the loss once, at the end of the step
+        _, ptr, length = m.train_forward_backward(x, t, sync=False)
         if bucket is None:
             bucket = dp.bucket_view(ptr, length, torch.float32, dev.torch_device)
         dp.allreduce_gradients(bucket, world)
         m.apply_update(0.01)
+        m.last_loss()
 
     for i in range(5):
         step(i)

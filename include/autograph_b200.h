@@ -482,6 +482,11 @@ AG_API int ag_model_train_forward_backward(ag_model *model, const void *x_dev,
                                            int64_t w, float *loss_host, void **grad_bucket,
                                            int64_t *grad_len);
 AG_API int ag_model_apply_update(ag_model *model, float lr);
+/* ag_model_train_forward_backward accepts loss_host == NULL: the step is then only enqueued (no
+ * synchronisation), so the caller's all-reduce and ag_model_apply_update can be enqueued behind it
+ * while it runs; this call waits for the stream and returns that step's loss (the one host read
+ * per step that the reference's training loop makes, autograph_backend.rs:70-85). */
+AG_API int ag_model_last_loss(ag_model *model, float *loss_host);
 
 #ifdef __cplusplus
 }

@@ -93,6 +93,29 @@ def test_lenet5_train_step_bs100(dev, dtype, momentum):
     model.close()
 
 
+def test_enqueued_forward_backward_equals_the_blocking_call(dev):
+    """The data-parallel half step without its host synchronisation: same loss, same update."""
+    import autograph_b200 as ag
+    rng = np.random.default_rng(5)
+    x = dev.tensor(rng.uniform(0, 1, (100, 1, 28, 28)).astype(np.float32))
+    t = torch.from_numpy(rng.integers(0, 10, 100).astype(np.uint8)).to(dev.torch_device)
+    a = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=3)
+    b = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=3)
+    for m in (a, b):
+        m.set_sgd(None)
+    for step in range(4):  # eager passes first, then the captured graph
+        la, _, _ = a.train_forward_backward(x, t)
+        a.apply_update(0.05)
+        lb, ptr, n = b.train_forward_backward(x, t, sync=False)
+        assert lb is None and ptr and n > 0
+        b.apply_update(0.05)
+        assert b.last_loss() == la, step
+    for i in range(len(a.parameter_lens)):
+        assert np.array_equal(a.get_parameter(i), b.get_parameter(i))
+    a.close()
+    b.close()
+
+
 def test_wide_stack_bf16_forward_backward(dev):
     """Benchmark configuration 3 at batch 8 (the oracle's naive loops finish in seconds), bf16."""
     import autograph_b200 as ag
