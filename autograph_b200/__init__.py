@@ -598,6 +598,8 @@ def _c_specs(spec):
                                                   layer[3][0], layer[3][1], int(layer[4]))
         elif kind == "dense":
             s.kind, s.a, s.b, s.bias = _capi.AG_LAYER_DENSE, layer[1], layer[2], int(layer[3])
+            if len(layer) > 4:   # shares the parameters of the dense layer at spec index layer[4]
+                s.c = layer[4] + 1
         elif kind == "relu":
             s.kind = _capi.AG_LAYER_RELU
         elif kind == "pool":
@@ -673,12 +675,29 @@ class Model:
     def set_grad_scale(self, scale: float):
         _capi.check(lib().ag_model_set_grad_scale(self._h, ctypes.c_float(scale)))
 
+    def _check(self, t, what, dtype, cuda, shape=None):
+        """The library reads raw pointers: refuse tensors it would read past or misread."""
+        if t.dtype != dtype:
+            raise AgError(_capi.AG_ERR_DTYPE, f"{what}: expected {dtype}, found {t.dtype}")
+        if not t.is_contiguous():
+            raise AgError(_capi.AG_ERR_INVALID, f"{what} must be contiguous")
+        if t.is_cuda != cuda:
+            raise AgError(_capi.AG_ERR_INVALID,
+                          f"{what} must be in {'device' if cuda else 'host'} memory")
+        if cuda and t.device.index != self.device.index:
+            raise AgError(_capi.AG_ERR_INVALID, f"{what} is on another GPU")
+        if shape is not None and tuple(t.shape) != tuple(shape):
+            raise AgError(_capi.AG_ERR_SHAPE, f"{what}: expected shape {tuple(shape)}, found "
+                                              f"{tuple(t.shape)}")
+
     def infer(self, x_host, out_host=None):
         """Host tensor [bs,c,h,w] (model dtype, ideally pinned) -> host logits (blocking)."""
         torch = _torch()
         bs, c, h, w = x_host.shape
+        self._check(x_host, "x_host", self.dtype, False)
         if out_host is None:
             out_host = torch.empty((bs, self.out_features), dtype=self.dtype)
+        self._check(out_host, "out_host", self.dtype, False, (bs, self.out_features))
         _capi.check(lib().ag_model_infer(self._h, _ptr(x_host), bs, c, h, w, _ptr(out_host)))
         return out_host
 
@@ -687,8 +706,10 @@ class Model:
         ≙ images_to_device_and_scale + forward of the reference's MNIST example."""
         torch = _torch()
         bs, c, h, w = x_host_u8.shape
+        self._check(x_host_u8, "x_host_u8", torch.uint8, False)
         if out_host is None:
             out_host = torch.empty((bs, self.out_features), dtype=self.dtype)
+        self._check(out_host, "out_host", self.dtype, False, (bs, self.out_features))
         _capi.check(lib().ag_model_infer_u8(self._h, _ptr(x_host_u8), bs, c, h, w,
                                             ctypes.c_float(alpha), _ptr(out_host)))
         return out_host
@@ -711,13 +732,17 @@ class Model:
 
     def forward_device(self, x_dev, out_dev=None):
         bs, c, h, w = x_dev.shape
+        self._check(x_dev, "x_dev", self.dtype, True)
         if out_dev is None:
             out_dev = self.device.empty((bs, self.out_features), self.dtype)
+        self._check(out_dev, "out_dev", self.dtype, True, (bs, self.out_features))
         _capi.check(lib().ag_model_forward_device(self._h, _ptr(x_dev), bs, c, h, w, _ptr(out_dev)))
         return out_dev
 
     def train_step(self, x_host, t_host, lr) -> float:
         bs, c, h, w = x_host.shape
+        self._check(x_host, "x_host", self.dtype, False)
+        self._check(t_host, "t_host", _torch().uint8, False, (bs,))
         loss = ctypes.c_float()
         _capi.check(lib().ag_model_train_step(self._h, _ptr(x_host), _ptr(t_host), bs, c, h, w,
                                               ctypes.c_float(lr), ctypes.byref(loss)))
@@ -727,6 +752,8 @@ class Model:
         """Returns (loss, grad bucket pointer, bucket length); the bucket can be all-reduced.
         sync=False only enqueues the step (loss is None; read it with last_loss())."""
         bs, c, h, w = x_dev.shape
+        self._check(x_dev, "x_dev", self.dtype, True)
+        self._check(t_dev, "t_dev", _torch().uint8, True, (bs,))
         loss = ctypes.c_float()
         bucket = ctypes.c_void_p()
         length = ctypes.c_int64()

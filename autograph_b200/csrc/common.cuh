@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
+#include <vector>
 
 #include "../../include/autograph_b200.h"
 
@@ -66,6 +67,7 @@ struct ag_device {
     size_t workspace_bytes = 0;
     void *staging = nullptr;        // second scratch block: operand re-layouts of the
     size_t staging_bytes = 0;       // tensor-core convolution (may be live next to workspace)
+    std::vector<void *> retired;    // outgrown scratch blocks that captured graphs may still use
     int *status_dev = nullptr;      // device word: 0 = ok, else a timeout code
     int *status_host = nullptr;     // pinned mirror
     float *scalar_dev = nullptr;    // small device buffer for loss / accuracy sums (64 B)
@@ -92,7 +94,8 @@ class DeviceGuard {
     return ::ag::fail(AG_ERR_CUDA, "cudaSetDevice(%d) failed: %s", (dev)->ordinal,        \
                       cudaGetErrorString(_guard.error()))
 
-// Returns a workspace of at least `bytes` (grown on demand; growth synchronises).
+// Returns a workspace of at least `bytes` (grown on demand; outgrown blocks stay allocated
+// until the device is destroyed because captured graphs may still point into them).
 int workspace(ag_device *dev, size_t bytes, void **out);
 // The same for the second scratch block.
 int staging(ag_device *dev, size_t bytes, void **out);

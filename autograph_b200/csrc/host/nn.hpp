@@ -258,9 +258,19 @@ class Dense : public Layer {
     Parameter weight;  // [inputs, outputs]
     bool has_bias = false;
     Parameter bias;    // [outputs]
+    // A layer that shares the parameters of an earlier Dense (one Parameter used by two
+    // layers: its node then receives two gradients, summed in arrival order,
+    // autograd.rs:126-131).  The owner's Parameter objects are used; this layer's stay empty.
+    Dense *tied = nullptr;
+    Shape weight_shape;  // [inputs, outputs], known before the value exists
+    Parameter &W() { return tied ? tied->weight : weight; }
+    Parameter &B() { return tied ? tied->bias : bias; }
+    const Parameter &W() const { return tied ? tied->weight : weight; }
+    const Parameter &B() const { return tied ? tied->bias : bias; }
 
     const char *name() const override { return "Dense"; }
     void parameters(std::vector<Parameter *> &out) override {
+        if (tied) return;  // visited through the owner
         out.push_back(&weight);
         if (has_bias) out.push_back(&bias);
     }
@@ -268,7 +278,7 @@ class Dense : public Layer {
         return forward_fused(pool, input, false);
     }
     bool records_gradient(const Variable &input) const {
-        return input.node || weight.node || (has_bias && bias.node);
+        return input.node || W().node || (has_bias && B().node);
     }
     // Forward with the bias add (and, when no gradient is recorded, the following
     // Relu) folded into the product's epilogue.
@@ -276,14 +286,14 @@ class Dense : public Layer {
         const Tensor &x = input.value;
         if (x.ndim() != 2) throw Error(AG_ERR_SHAPE, "Dense needs a 2-D input");
         if (!x.is_standard_layout()) throw Error(AG_ERR_SHAPE, "Dense needs standard layout");
-        Variable w = weight.to_variable();
+        Variable w = W().to_variable();
         if (x.dim(1) != w.value.dim(0))
             throw Error(AG_ERR_SHAPE, "a_cols != b_rows, " + std::to_string(x.dim(1)) +
                                           " != " + std::to_string(w.value.dim(0)));
         if (relu && records_gradient(input))
             throw Error(AG_ERR_INVALID, "Dense: fused relu while a gradient is recorded");
         const int64_t bs = x.dim(0), ins = x.dim(1), outs = w.value.dim(1);
-        Variable b = has_bias ? bias.to_variable() : Variable{};
+        Variable b = has_bias ? B().to_variable() : Variable{};
         Tensor y = Tensor::uninit(pool, {bs, outs}, x.dtype());
         check(ag_dense_forward(x.device(), x.dtype(), x.data(), bs, ins, w.value.data(), outs,
                                has_bias ? b.value.data() : nullptr, relu ? 1 : 0, y.data()));
@@ -293,8 +303,8 @@ class Dense : public Layer {
     // the three backward edges of Dense::forward.
     Variable attach(Pool &pool, const Variable &input, const Tensor &y) {
         const Tensor &x = input.value;
-        Variable w = weight.to_variable();
-        Variable b = has_bias ? bias.to_variable() : Variable{};
+        Variable w = W().to_variable();
+        Variable b = has_bias ? B().to_variable() : Variable{};
         const int64_t bs = x.dim(0), outs = w.value.dim(1);
         VariableBuilder builder;
         Pool *pp = &pool;

@@ -1,6 +1,7 @@
 // C ABI of the host-side neural-network layer: model construction, parameter
 // access, inference and training steps (the counterpart of LeNet5Classifier in
 // benches/neural-network-benches/src/autograph_backend.rs:16-85).
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cuda_bf16.h>
@@ -205,6 +206,17 @@ void build_model(ag_model *m, const ag_layer_spec *specs, int n, uint64_t seed) 
                 auto l = std::make_unique<Dense>();
                 float a = std::sqrt(2.f / (float)s.a);  // layer.rs:463-467
                 l->has_bias = s.bias != 0;
+                if (s.c > 0) {
+                    // c = 1 + index of an earlier Dense layer whose parameters this one shares
+                    auto *owner = s.c - 1 < i ? dynamic_cast<Dense *>(m->layers[s.c - 1].get()) : nullptr;
+                    if (!owner || owner->tied || owner->weight_shape != Shape{s.a, s.b} ||
+                        owner->has_bias != l->has_bias)
+                        throw Error(AG_ERR_INVALID, "Dense: c must name an earlier Dense layer of the same shape");
+                    l->tied = owner;
+                    m->layers.push_back(std::move(l));
+                    break;
+                }
+                l->weight_shape = {s.a, s.b};
                 pending.push_back({&l->weight, {s.a, s.b}, a});
                 if (l->has_bias) pending.push_back({&l->bias, {s.b}, a});
                 m->layers.push_back(std::move(l));
@@ -299,12 +311,12 @@ bool forward_whole_network(ag_model *m, const Variable &v, Variable *out, void *
     std::vector<int32_t> relus;
     while (i < n) {
         auto *d = dynamic_cast<Dense *>(m->layers[i].get());
-        if (!d || d->weight.node || (d->has_bias && d->bias.node)) return false;
-        if (dims.empty()) dims.push_back(d->weight.value.dim(0));
-        if (d->weight.value.dim(0) != dims.back()) return false;
-        dims.push_back(d->weight.value.dim(1));
-        ws.push_back(d->weight.value.data());
-        bs.push_back(d->has_bias ? d->bias.value.data() : nullptr);
+        if (!d || d->W().node || (d->has_bias && d->B().node)) return false;
+        if (dims.empty()) dims.push_back(d->W().value.dim(0));
+        if (d->W().value.dim(0) != dims.back()) return false;
+        dims.push_back(d->W().value.dim(1));
+        ws.push_back(d->W().value.data());
+        bs.push_back(d->has_bias ? d->B().value.data() : nullptr);
         const bool r = i + 1 < n && dynamic_cast<Relu *>(m->layers[i + 1].get());
         relus.push_back(r ? 1 : 0);
         i += r ? 2 : 1;
@@ -352,17 +364,25 @@ Variable attach_dense_chain(Pool &pool, const Variable &input, const std::vector
     std::vector<Tensor> wv;
     std::vector<std::shared_ptr<Node>> wn, bn;
     for (Dense *d : run) {
-        wv.push_back(d->weight.value);
-        wn.push_back(d->weight.node);
-        bn.push_back(d->has_bias ? d->bias.node : nullptr);
+        wv.push_back(d->W().value);
+        wn.push_back(d->W().node);
+        bn.push_back(d->has_bias ? d->B().node : nullptr);
     }
     auto st = std::make_shared<DenseChainGrads>();
     Pool *pp = &pool;
     auto ensure = [=](const Tensor &dy) {
         if (st->done) return;
         const int64_t bs = x.dim(0);
+        // A parameter's own gradient storage is handed out once: a parameter shared by two
+        // layers of the run gets its second gradient in a fresh tensor, which the backward
+        // walk then adds to the first.
+        std::vector<const Node *> handed;
         auto target = [&](const std::shared_ptr<Node> &n, const Shape &shape) {
-            if (n && !n->has_grad && n->grad_storage.defined()) return n->grad_storage;
+            if (n && !n->has_grad && n->grad_storage.defined() &&
+                std::find(handed.begin(), handed.end(), n.get()) == handed.end()) {
+                handed.push_back(n.get());
+                return n->grad_storage;
+            }
             return Tensor::uninit(*pp, shape, x.dtype());
         };
         std::vector<int64_t> dims = {x.dim(1)};
@@ -455,20 +475,20 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                 size_t j = i;
                 while (j < n && run.size() < 4) {
                     auto *d = dynamic_cast<Dense *>(m->layers[j].get());
-                    if (!d || d->weight.node || (d->has_bias && d->bias.node)) break;
-                    if (!run.empty() && d->weight.value.dim(0) != run.back()->weight.value.dim(1)) break;
+                    if (!d || d->W().node || (d->has_bias && d->B().node)) break;
+                    if (!run.empty() && d->W().value.dim(0) != run.back()->W().value.dim(1)) break;
                     const bool r = j + 1 < n && dynamic_cast<Relu *>(m->layers[j + 1].get());
                     run.push_back(d);
                     relus.push_back(r ? 1 : 0);
                     j += r ? 2 : 1;
                 }
-                if (run.size() >= 2 && v.value.dim(1) == run[0]->weight.value.dim(0)) {
+                if (run.size() >= 2 && v.value.dim(1) == run[0]->W().value.dim(0)) {
                     std::vector<int64_t> dims = {v.value.dim(1)};
                     std::vector<const void *> ws, bs;
                     for (Dense *d : run) {
-                        dims.push_back(d->weight.value.dim(1));
-                        ws.push_back(d->weight.value.data());
-                        bs.push_back(d->has_bias ? d->bias.value.data() : nullptr);
+                        dims.push_back(d->W().value.dim(1));
+                        ws.push_back(d->W().value.data());
+                        bs.push_back(d->has_bias ? d->B().value.data() : nullptr);
                     }
                     Tensor y = Tensor::uninit(m->pool, {v.value.dim(0), dims.back()}, v.value.dtype());
                     check(ag_dense_chain_forward(v.value.device(), v.value.dtype(), v.value.data(),
@@ -487,14 +507,14 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
             // Recording gradients: the same run as one call that keeps every layer's values,
             // then the layers' own backward edges around those values.
             if (dense->records_gradient(v) && v.value.ndim() == 2 && v.value.is_standard_layout() &&
-                v.value.dim(1) == dense->weight.value.dim(0)) {
+                v.value.dim(1) == dense->W().value.dim(0)) {
                 std::vector<Dense *> run;
                 std::vector<int32_t> relus;
                 size_t j = i;
                 while (j < n && run.size() < 4) {
                     auto *d = dynamic_cast<Dense *>(m->layers[j].get());
                     if (!d) break;
-                    if (!run.empty() && d->weight.value.dim(0) != run.back()->weight.value.dim(1)) break;
+                    if (!run.empty() && d->W().value.dim(0) != run.back()->W().value.dim(1)) break;
                     const bool r = j + 1 < n && dynamic_cast<Relu *>(m->layers[j + 1].get());
                     run.push_back(d);
                     relus.push_back(r ? 1 : 0);
@@ -508,10 +528,10 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                     std::vector<void *> pre_ptr, act_ptr;
                     for (size_t k = 0; k < run.size(); ++k) {
                         Dense *d = run[k];
-                        const int64_t outs = d->weight.value.dim(1);
+                        const int64_t outs = d->W().value.dim(1);
                         dims.push_back(outs);
-                        ws.push_back(d->weight.value.data());
-                        bs_ptr.push_back(d->has_bias ? d->bias.value.data() : nullptr);
+                        ws.push_back(d->W().value.data());
+                        bs_ptr.push_back(d->has_bias ? d->B().value.data() : nullptr);
                         pre.push_back(Tensor::uninit(m->pool, {bs, outs}, v.value.dtype()));
                         act.push_back(relus[k] ? Tensor::uninit(m->pool, {bs, outs}, v.value.dtype())
                                                : Tensor{});

@@ -25,31 +25,32 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 void count_launches(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 uint64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+// Growing a scratch block never frees the old one: captured CUDA graphs (the model's
+// inference and training passes) carry the old address in their kernel parameters and
+// tensor maps, and may be replayed after the growth.  The old block is retired instead and
+// lives until the device object is destroyed; sizes at least double, so all retired blocks
+// together are smaller than the live one.
+static int grow_block(ag_device *dev, void **block, size_t *have, size_t bytes, size_t floor) {
+    size_t want = *have ? *have * 2 : floor;
+    if (want < bytes) want = bytes + bytes / 4;
+    void *fresh = nullptr;
+    AG_CUDA_TRY(cudaMalloc(&fresh, want));
+    if (*block) dev->retired.push_back(*block);
+    *block = fresh;
+    *have = want;
+    return AG_OK;
+}
+
 int workspace(ag_device *dev, size_t bytes, void **out) {
-    if (bytes > dev->workspace_bytes) {
-        // Growth waits for work that may still use the old block.
-        AG_CUDA_TRY(cudaStreamSynchronize(dev->stream));
-        if (dev->workspace) AG_CUDA_TRY(cudaFree(dev->workspace));
-        dev->workspace = nullptr;
-        dev->workspace_bytes = 0;
-        size_t want = bytes < (size_t(8) << 20) ? (size_t(8) << 20) : bytes + bytes / 4;
-        AG_CUDA_TRY(cudaMalloc(&dev->workspace, want));
-        dev->workspace_bytes = want;
-    }
+    if (bytes > dev->workspace_bytes)
+        AG_TRY(grow_block(dev, &dev->workspace, &dev->workspace_bytes, bytes, size_t(8) << 20));
     *out = dev->workspace;
     return AG_OK;
 }
 
 int staging(ag_device *dev, size_t bytes, void **out) {
-    if (bytes > dev->staging_bytes) {
-        AG_CUDA_TRY(cudaStreamSynchronize(dev->stream));
-        if (dev->staging) AG_CUDA_TRY(cudaFree(dev->staging));
-        dev->staging = nullptr;
-        dev->staging_bytes = 0;
-        size_t want = bytes + bytes / 4;
-        AG_CUDA_TRY(cudaMalloc(&dev->staging, want));
-        dev->staging_bytes = want;
-    }
+    if (bytes > dev->staging_bytes)
+        AG_TRY(grow_block(dev, &dev->staging, &dev->staging_bytes, bytes, size_t(1) << 20));
     *out = dev->staging;
     return AG_OK;
 }
@@ -127,6 +128,7 @@ int ag_device_destroy(ag_device *dev) {
     if (dev->stream) cudaStreamSynchronize(dev->stream);
     if (dev->workspace) cudaFree(dev->workspace);
     if (dev->staging) cudaFree(dev->staging);
+    for (void *p : dev->retired) cudaFree(p);
     if (dev->status_dev) cudaFree(dev->status_dev);
     if (dev->scalar_dev) cudaFree(dev->scalar_dev);
     if (dev->status_host) cudaFreeHost(dev->status_host);

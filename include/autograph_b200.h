@@ -422,7 +422,10 @@ typedef enum ag_layer_kind {
     AG_LAYER_RELU = 1,
     AG_LAYER_MAXPOOL2 = 2, /* c = h, d = w (stride = filter, layer.rs:535-539) */
     AG_LAYER_FLATTEN = 3,
-    AG_LAYER_DENSE = 4    /* a = inputs, b = outputs, bias */
+    AG_LAYER_DENSE = 4    /* a = inputs, b = outputs, bias; c = 0, or 1 + the index of an earlier
+                           * Dense layer of the same shape whose parameters this layer shares
+                           * (one Parameter feeding two layers: its gradients are summed,
+                           * autograd.rs:126-131) */
 } ag_layer_kind;
 
 typedef struct ag_layer_spec {

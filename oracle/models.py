@@ -8,7 +8,8 @@ for LeNet5) and runs the reverse pass edge by edge the way
 A network is a list of layer specs shared with the product's host code:
     ("conv", inputs, outputs, (fh, fw), bias)   Conv2, default padding/stride/dilation
     ("relu",) ("pool", (h, w)) ("flatten",)
-    ("dense", inputs, outputs, bias)
+    ("dense", inputs, outputs, bias[, tie])  tie = index of an earlier dense layer of the
+                                             same shape whose parameters this layer shares
 """
 from __future__ import annotations
 
@@ -51,6 +52,8 @@ def init_params(spec, seed: int, bf16: bool = False):
             a = np.float32(np.sqrt(np.float32(2.0) / np.float32(ic * fh * fw)))
             shapes = [(oc, ic, fh, fw)] + ([(oc,)] if bias else [])
         elif layer[0] == "dense":
+            if len(layer) > 4:
+                continue  # shares an earlier layer's parameters
             _, ins, outs, bias = layer
             a = np.float32(np.sqrt(np.float32(2.0) / np.float32(ins)))
             shapes = [(ins, outs)] + ([(outs,)] if bias else [])
@@ -62,6 +65,21 @@ def init_params(spec, seed: int, bf16: bool = False):
             params.append(round_bf16(w) if bf16 else w)
             idx += 1
     return params
+
+
+def _param_index(spec):
+    """Index of the first parameter of every layer (a tied dense layer points at its owner's)."""
+    pidx, i = [], 0
+    for layer in spec:
+        if layer[0] == "dense" and len(layer) > 4:
+            pidx.append(pidx[layer[4]])
+            continue
+        pidx.append(i)
+        if layer[0] == "conv":
+            i += 1 + int(layer[4])
+        elif layer[0] == "dense":
+            i += 1 + int(layer[3])
+    return pidx
 
 
 def _dot(a, b, acc, bf16, fast):
@@ -76,25 +94,25 @@ def forward(spec, params, x, *, bf16=False, acc="f32", keep=False, fast=False):
     acc="f32" follows the reference's host arithmetic (direct conv for f32);
     acc="f64" is the high-precision checker used for tolerance tests.
     fast=True uses the threaded GEMM (CPU-baseline timing)."""
-    p = iter(params)
+    pidx = _param_index(spec)
     saved = []
     h = np.ascontiguousarray(x, np.float32)
-    for layer in spec:
+    for li, layer in enumerate(spec):
         kind = layer[0]
         saved.append(h if keep else None)
         if kind == "conv":
-            w = next(p)
+            w = params[pidx[li]]
             if acc == "f32" and not bf16:
                 h = conv2_direct_f32(h, w)
             else:
                 h = conv2_naive(h, w, acc64=(acc == "f64"), bf16=bf16)
             if layer[4]:
-                h = bias_add(h, next(p), bf16=bf16)
+                h = bias_add(h, params[pidx[li] + 1], bf16=bf16)
         elif kind == "dense":
-            w = next(p)
+            w = params[pidx[li]]
             h = _dot(h, w, acc, bf16, fast)
             if layer[3]:
-                h = bias_add(h, next(p), bf16=bf16)
+                h = bias_add(h, params[pidx[li] + 1], bf16=bf16)
         elif kind == "relu":
             h = relu(h)
         elif kind == "pool":
@@ -107,16 +125,18 @@ def forward(spec, params, x, *, bf16=False, acc="f32", keep=False, fast=False):
 def backward(spec, params, saved, dlogits, *, bf16=False, acc="f32"):
     """Gradients of every parameter, in parameter order."""
     grads = [None] * len(params)
-    # parameter index at the start of each layer
-    pidx = []
-    i = 0
-    for layer in spec:
-        pidx.append(i)
-        if layer[0] == "conv":
-            i += 1 + int(layer[4])
-        elif layer[0] == "dense":
-            i += 1 + int(layer[3])
+    pidx = _param_index(spec)
     a64 = acc == "f64"
+
+    def deliver(i, g):
+        # a second gradient arriving at a parameter is added to the first, in the element
+        # type (Node::backward_grad, autograd.rs:126-131)
+        if grads[i] is None:
+            grads[i] = g
+        else:
+            s = grads[i].astype(np.float32) + g.astype(np.float32)
+            grads[i] = round_bf16(s) if bf16 else s
+
     g = dlogits
     for li in range(len(spec) - 1, -1, -1):
         layer = spec[li]
@@ -125,8 +145,8 @@ def backward(spec, params, saved, dlogits, *, bf16=False, acc="f32"):
         if kind == "dense":
             w = params[pidx[li]]
             if layer[3]:
-                grads[pidx[li] + 1] = bias_grad(g, acc64=a64, bf16=bf16)
-            grads[pidx[li]] = gemm(xin.T, g, acc=acc, bf16=bf16)          # dW = X^T . dY
+                deliver(pidx[li] + 1, bias_grad(g, acc64=a64, bf16=bf16))
+            deliver(pidx[li], gemm(xin.T, g, acc=acc, bf16=bf16))         # dW = X^T . dY
             g = gemm(g, w.T, acc=acc, bf16=bf16)                          # dX = dY . W^T
         elif kind == "conv":
             w = params[pidx[li]]

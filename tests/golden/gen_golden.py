@@ -53,10 +53,18 @@ def conv_option_grid():
     opts += [dict(stride=s) for s in [(1, 2), (2, 2)]]
     opts += [dict(dilation=d) for d in [(1, 2), (2, 2)]]
     bio = [(1, 1, 1)] + [t for x in (2, 3, 13) for t in ((x, 1, 1), (1, x, 1), (1, 1, x))]
-    outs = [(1, 1), (2, 3), (3, 2), (5, 5), (1, 5)]
+    outs = [(oh, ow) for oh in (1, 2, 3, 5) for ow in (1, 2, 3, 5)]   # all 16 output shapes
     for f in filters:
         for o in opts:
             yield f, o, bio, outs
+
+
+def fingerprint(a):
+    """(sum, position-weighted sum) of an integer-valued array as exact int64: two numbers
+    that stand for the whole tensor where the full grid would make the fixture too large."""
+    v = np.rint(np.asarray(a, np.float64)).astype(np.int64).ravel()
+    wts = (np.arange(v.size, dtype=np.int64) * 2654435761 % 1000003) + 1
+    return [int(v.sum()), int((v * wts).sum())]
 
 
 def input_shape(oh, ow, f, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
@@ -69,17 +77,15 @@ def conv_cases(store):
     """conv2 forward / backward-input / backward-weight on cycle 1..=10 inputs
     (integration_tests.rs:1182-1497), expected from torch float64."""
     cases = []
+    grid, prints = [], []
     idx = 0
     for f, o, bio, outs in conv_option_grid():
         for (bs, ic, oc), (oh, ow) in itertools.product(bio, outs):
-            # keep the fixture small: a deterministic third of the grid
-            idx += 1
-            if idx % 3 != 0:
-                continue
             hw = input_shape(oh, ow, f, **o)
             if hw is None:
                 continue
             ih, iw = hw
+            idx += 1
             kw = dict(padding=o.get("padding", (0, 0)), stride=o.get("stride", (1, 1)),
                       dilation=o.get("dilation", (1, 1)))
             x = cycle(1, 11, bs * ic * ih * iw).reshape(bs, ic, ih, iw)
@@ -90,6 +96,13 @@ def conv_cases(store):
             assert tuple(y.shape[2:]) == (oh, ow), (y.shape, oh, ow, f, o)
             dy = cycle(1, 11, y.numel()).reshape(tuple(y.shape))
             y.backward(torch.tensor(dy, dtype=torch.float64))
+            # every case of the grid: its shape and the fingerprints of the three results
+            grid.append([bs, ic, ih, iw, oc, f[0], f[1], *kw["padding"], *kw["stride"],
+                         *kw["dilation"]])
+            prints.append([fingerprint(y.detach().numpy()), fingerprint(xt.grad.numpy()),
+                           fingerprint(wt.grad.numpy())])
+            if idx % 9 != 0:   # full expected tensors for a deterministic ninth of the grid
+                continue
             name = f"conv_{len(cases)}"
             store[name + "_y"] = y.detach().numpy().astype(np.float32)
             store[name + "_dx"] = xt.grad.numpy().astype(np.float32)
@@ -97,6 +110,8 @@ def conv_cases(store):
             cases.append(dict(name=name, x_shape=[bs, ic, ih, iw], oc=oc, filter=list(f),
                               padding=list(kw["padding"]), stride=list(kw["stride"]),
                               dilation=list(kw["dilation"])))
+    store["conv_grid"] = np.asarray(grid, np.int32)
+    store["conv_grid_fp"] = np.asarray(prints, np.int64)
     return cases
 
 
@@ -104,18 +119,17 @@ def im2col_cases(store):
     """im2col x = 1..len; col2im dy = 1..len (integration_tests.rs:1499-1552).
     Expected im2col from torch unfold; expected col2im from torch fold (float64)."""
     cases = []
+    grid, prints = [], []
     idx = 0
     for f, o, bio, outs in conv_option_grid():
         for (bs, c, oc), (oh, ow) in itertools.product(bio, outs):
             if oc != 1:
                 continue
-            idx += 1
-            if idx % 3 != 0:
-                continue
             hw = input_shape(oh, ow, f, **o)
             if hw is None:
                 continue
             ih, iw = hw
+            idx += 1
             kw = dict(padding=o.get("padding", (0, 0)), stride=o.get("stride", (1, 1)),
                       dilation=o.get("dilation", (1, 1)))
             n = bs * c * ih * iw
@@ -128,12 +142,19 @@ def im2col_cases(store):
             oh_img = (oh - 1) * kw["stride"][0] + kw["dilation"][0] * (f[0] - 1) + 1 - 2 * kw["padding"][0]
             ow_img = (ow - 1) * kw["stride"][1] + kw["dilation"][1] * (f[1] - 1) + 1 - 2 * kw["padding"][1]
             img = F.fold(dcols, output_size=(oh_img, ow_img), kernel_size=f, **kw)
+            grid.append([bs, c, ih, iw, oh, ow, f[0], f[1], *kw["padding"], *kw["stride"],
+                         *kw["dilation"]])
+            prints.append([fingerprint(im.numpy()), fingerprint(img.numpy())])
+            if idx % 9 != 0:
+                continue
             name = f"im2col_{len(cases)}"
             store[name + "_y"] = im.numpy().astype(np.float32)
             store[name + "_dx"] = img.numpy().astype(np.float32)
             cases.append(dict(name=name, x_shape=[bs, c, ih, iw], grid=[oh, ow], filter=list(f),
                               padding=list(kw["padding"]), stride=list(kw["stride"]),
                               dilation=list(kw["dilation"])))
+    store["im2col_grid"] = np.asarray(grid, np.int32)
+    store["im2col_grid_fp"] = np.asarray(prints, np.int64)
     return cases
 
 

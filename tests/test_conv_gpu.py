@@ -42,6 +42,33 @@ def test_conv2_golden(dev, golden, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_conv2_full_reference_grid(dev, golden, dtype):
+    """Every case of the reference's grid (7 filters x 7 option sets x 10 (bs, ic, oc) x 16 output
+    shapes, tests/integration_tests.rs:884-923).  The expected tensors come from the oracle, which
+    the CPU suite pins on this grid's fingerprints; f32 must equal them, bf16 after one rounding."""
+    grid = golden["conv_grid"]
+    step = 1 if dtype == torch.float32 else 5
+    for row in grid[::step]:
+        bs, ic, ih, iw, oc, fh, fw = (int(v) for v in row[:7])
+        kw = dict(padding=(int(row[7]), int(row[8])), stride=(int(row[9]), int(row[10])),
+                  dilation=(int(row[11]), int(row[12])))
+        x = cycle(1, 11, bs * ic * ih * iw).reshape(bs, ic, ih, iw)
+        w = cycle(1, 11, oc * ic * fh * fw).reshape(oc, ic, fh, fw)
+        y_true = oracle.conv2_naive(x, w, **kw)
+        dy = cycle(1, 11, y_true.size).reshape(y_true.shape)
+        want = [y_true, oracle.conv2_backward_input_naive(w, dy, (ih, iw), **kw),
+                oracle.conv2_backward_weight_naive(x, dy, (fh, fw), **kw)]
+        xd, wd, dyd = (torch.from_numpy(a).to(dtype).to(dev.torch_device, non_blocking=True)
+                       for a in (x, w, dy))
+        got = [dev.conv2_forward(xd, wd, **kw), dev.conv2_backward_input(wd, dyd, (ih, iw), **kw),
+               dev.conv2_backward_weight(xd, dyd, (fh, fw), **kw)]
+        for g, t in zip(got, want):
+            if dtype == torch.bfloat16:
+                t = oracle.round_bf16(t)
+            assert np.array_equal(g.float().cpu().numpy(), t), row.tolist()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_im2col_col2im_golden(dev, golden, dtype):
     """im2col_conv2_<T>_* / col2im_conv2_<T>_* (tests/integration_tests.rs:1499-1552)."""
     cases = golden.meta["im2col"]

@@ -191,3 +191,28 @@ def test_checkpoint_round_trip_in_the_reference_layout(dev, dtype):
     assert torch.equal(a.forward_device(x), b.forward_device(x))
     a.close()
     b.close()
+
+
+def test_model_wrappers_refuse_tensors_the_library_would_misread(dev):
+    """The C entry points take raw pointers; the Python front end checks dtype, contiguity and
+    which side (host / device) a tensor lives on before handing its address over."""
+    import autograph_b200 as ag
+    m = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=1)
+    x = torch.rand((8, 1, 28, 28))
+    t = torch.zeros(8, dtype=torch.uint8)
+    with pytest.raises(ag.AgError):
+        m.infer(x.to(torch.bfloat16))                       # wrong dtype
+    with pytest.raises(ag.AgError):
+        m.infer(torch.rand((8, 1, 28, 56))[..., ::2])       # not contiguous
+    with pytest.raises(ag.AgError):
+        m.infer(x.to(dev.torch_device))                     # device tensor where host is expected
+    with pytest.raises(ag.AgError):
+        m.forward_device(x)                                 # host tensor where device is expected
+    with pytest.raises(ag.AgError):
+        m.train_step(x, t.to(torch.int64), 0.01)            # labels must be u8
+    with pytest.raises(ag.AgError):
+        m.train_step(x, t[:4], 0.01)                        # one label per image
+    with pytest.raises(ag.AgError):
+        m.infer(x, torch.empty((8, 12)))                    # wrong output shape
+    assert m.infer(x).shape == (8, 10)
+    m.close()

@@ -54,6 +54,50 @@ def test_conv_forward_backward(golden):
             assert np.array_equal(oracle.conv2_direct_f32(x, w), y_true), c
 
 
+def fingerprint(a):
+    """Same two numbers as tests/golden/gen_golden.py stores for every case of the full grid."""
+    v = np.rint(np.asarray(a, np.float64)).astype(np.int64).ravel()
+    wts = (np.arange(v.size, dtype=np.int64) * 2654435761 % 1000003) + 1
+    return [int(v.sum()), int((v * wts).sum())]
+
+
+def grid_kw(row, at):
+    return dict(padding=(int(row[at]), int(row[at + 1])), stride=(int(row[at + 2]), int(row[at + 3])),
+                dilation=(int(row[at + 4]), int(row[at + 5])))
+
+
+def test_conv_full_reference_grid(golden):
+    """Every case of the reference's conv grid (7 filters x 7 option sets x 10 (bs, ic, oc) x 16
+    output shapes, tests/integration_tests.rs:884-923): the oracle's three results match the
+    fingerprints computed from torch float64."""
+    grid, fp = golden["conv_grid"], golden["conv_grid_fp"]
+    assert len(grid) > 7000
+    for row, want in zip(grid, fp):
+        bs, ic, ih, iw, oc, fh, fw = (int(v) for v in row[:7])
+        kw = grid_kw(row, 7)
+        x = cycle(1, 11, bs * ic * ih * iw).reshape(bs, ic, ih, iw)
+        w = cycle(1, 11, oc * ic * fh * fw).reshape(oc, ic, fh, fw)
+        y = oracle.conv2_naive(x, w, **kw)
+        dy = cycle(1, 11, y.size).reshape(y.shape)
+        dx = oracle.conv2_backward_input_naive(w, dy, (ih, iw), **kw)
+        dw = oracle.conv2_backward_weight_naive(x, dy, (fh, fw), **kw)
+        got = [fingerprint(y), fingerprint(dx), fingerprint(dw)]
+        assert got == want.tolist(), row.tolist()
+
+
+def test_im2col_full_reference_grid(golden):
+    grid, fp = golden["im2col_grid"], golden["im2col_grid_fp"]
+    assert len(grid) > 5000
+    for row, want in zip(grid, fp):
+        bs, ch, ih, iw, gh, gw, fh, fw = (int(v) for v in row[:8])
+        kw = grid_kw(row, 8)
+        x = np.arange(1, bs * ch * ih * iw + 1, dtype=np.float32).reshape(bs, ch, ih, iw)
+        y = oracle.im2col_conv2(x, (fh, fw), **kw)
+        dy = np.arange(1, y.size + 1, dtype=np.float32).reshape(y.shape)
+        dx = oracle.col2im_conv2(dy, (gh, gw), (fh, fw), **kw)
+        assert [fingerprint(y), fingerprint(dx)] == want.tolist(), row.tolist()
+
+
 def test_im2col_col2im(golden):
     for c in golden.meta["im2col"]:
         bs, ch, ih, iw = c["x_shape"]
