@@ -150,6 +150,16 @@ _SIGNATURES = {
                                                 POINTER(c_float), POINTER(_P), POINTER(c_int64)]),
     "ag_model_apply_update": (c_int, [_P, c_float]),
     "ag_model_last_loss": (c_int, [_P, POINTER(c_float)]),
+    "ag_comm_create": (c_int, [POINTER(_P), c_int, POINTER(_P)]),
+    "ag_comm_unique_id": (c_int, [_P, c_size_t]),
+    "ag_comm_create_rank": (c_int, [_P, c_int, c_int, _P, c_size_t, POINTER(_P)]),
+    "ag_comm_destroy": (c_int, [_P]),
+    "ag_comm_world": (c_int, [_P, POINTER(c_int), POINTER(c_int)]),
+    "ag_comm_set_timeout": (c_int, [_P, ctypes.c_double]),
+    "ag_allreduce_sum": (c_int, [_P, c_int, c_int, _P, c_int64]),
+    "ag_allreduce_sum_all": (c_int, [_P, c_int, POINTER(_P), c_int64]),
+    "ag_comm_wait": (c_int, [_P, c_int]),
+    "ag_model_allreduce_update": (c_int, [_P, _P, c_int, c_float]),
 }
 
 _lib = None

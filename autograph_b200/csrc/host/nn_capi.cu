@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cuda_bf16.h>
 
+#include "../comm.cuh"
 #include "../common.cuh"
 #include "nn.hpp"
 
@@ -1196,6 +1197,16 @@ int ag_model_last_loss(ag_model *model, float *loss_host) {
         model->loss_in_flight = false;
     }
     *loss_host = model->loss_eager;
+    return AG_OK;
+}
+
+int ag_model_allreduce_update(ag_model *model, ag_comm *comm, int rank, float lr) {
+    AG_REQUIRE(model != nullptr && comm != nullptr, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_TRY(::ag::comm_fused_update(comm, rank, model->dtype, model->grads.data(),
+                                   model->values.data(), model->velocity.data(), model->bucket_len,
+                                   model->grad_scale, lr, model->momentum, model->use_momentum));
+    for (Parameter *p : model->params) p->node.reset();  // ≙ take_grad consumed the gradient
     return AG_OK;
 }
 

@@ -379,34 +379,55 @@ def run_gpu(args):
 
 
 def train_data_parallel(torch, ag, dp, dev, rank, world, barrier, max_over_ranks):
-    m = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)   # same seed: replicated parameters
-    m.set_sgd(None)
-    m.set_grad_scale(1.0 / world)
+    """configs[4b]: forward / backward on 100 images per GPU, then the data-parallel tail two
+    ways: the fused kernel (one-shot all-reduce over NVLink + 1/world + SGD update) and, for
+    comparison, an NCCL all-reduce of the bucket followed by the update kernel."""
+    comm = dp.Comm.from_torch_distributed(dev) if world > 1 else dp.Comm.single_process([dev])
     gen = torch.Generator(device=dev.torch_device).manual_seed(7000 + rank)
     x = torch.rand((100, 1, 28, 28), generator=gen, device=dev.torch_device)
     t = torch.randint(0, 10, (100,), generator=gen, device=dev.torch_device, dtype=torch.uint8)
-    bucket = None
+    out = {"global_batch": 100 * world}
 
-    def step(i):
-        nonlocal bucket
-        # forward/backward, all-reduce and update are enqueued back to back on one stream;
-        # the host reads the loss once, at the end of the step
-        _, ptr, length = m.train_forward_backward(x, t, sync=False)
-        if bucket is None:
-            bucket = dp.bucket_view(ptr, length, torch.float32, dev.torch_device)
-        dp.allreduce_gradients(bucket, world)
-        m.apply_update(0.01)
-        m.last_loss()
+    def measure(fused):
+        m = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=2000)   # same seed: replicated parameters
+        m.set_sgd(None)
+        m.set_grad_scale(1.0 / world)
+        n_elems = [0]
 
-    for i in range(5):
-        step(i)
-    barrier()
-    n = 50
-    ms = max_over_ranks(event_time_ms(torch, step, n, dev.stream)) / n
-    barrier()
-    out = {"ms_per_step": ms, "img_per_s": 100 * world / ms * 1e3, "global_batch": 100 * world,
-           "allreduce_elements": int(bucket.numel()), "collective": "nccl all_reduce(sum)" if world > 1 else "none"}
-    m.close()
+        def step(i):
+            # everything is enqueued back to back on one stream; the host reads the loss once,
+            # at the end of the step
+            _, ptr, length = m.train_forward_backward(x, t, sync=False)
+            n_elems[0] = length
+            if fused:
+                comm.allreduce_update(m, 0.01)
+            else:
+                if world > 1:
+                    comm.allreduce_bucket(ptr, length, torch.float32)
+                m.apply_update(0.01)
+            m.last_loss()
+
+        for i in range(5):
+            step(i)
+        windows = []
+        for _ in range(5):
+            barrier()
+            windows.append(max_over_ranks(event_time_ms(torch, step, 40, dev.stream)) / 40)
+        barrier()
+        m.close()
+        return float(np.median(windows)), n_elems[0]
+
+    try:
+        ms_plain, n = measure(False)
+        out["nccl_then_update"] = {"ms_per_step": ms_plain, "img_per_s": 100 * world / ms_plain * 1e3}
+    except Exception as exc:
+        out["nccl_then_update_error"] = repr(exc)
+    use_fused = comm.fused_available
+    ms, n = measure(use_fused)
+    out.update({"ms_per_step": ms, "img_per_s": 100 * world / ms * 1e3, "allreduce_elements": int(n),
+                "collective": ("fused one-shot all-reduce over NVLink + update (one kernel)"
+                               if use_fused else "nccl all_reduce(sum)") if world > 1 else "none"})
+    comm.close()
     return out
 
 

@@ -42,6 +42,7 @@ extern "C" {
 
 typedef struct ag_device ag_device;
 typedef struct ag_model ag_model;
+typedef struct ag_comm ag_comm;
 
 typedef enum ag_dtype { AG_F32 = 0, AG_BF16 = 1, AG_U8 = 2, AG_U16 = 3, AG_U32 = 4 } ag_dtype;
 
@@ -490,6 +491,53 @@ AG_API int ag_model_apply_update(ag_model *model, float lr);
  * while it runs; this call waits for the stream and returns that step's loss (the one host read
  * per step that the reference's training loop makes, autograph_backend.rs:70-85). */
 AG_API int ag_model_last_loss(ag_model *model, float *loss_host);
+
+/* ------------------------------------------------------------ data parallel
+ * The reference has no multi-device code.  Its networks shard by batch (every image is
+ * independent, parameters are replicated), and because the loss gradient is scaled by the
+ * local batch size (src/learn/neural_network/criterion.rs:84) a data-parallel step is: every
+ * rank's forward / backward, ONE sum all-reduce of the flat gradient bucket, a factor
+ * 1 / world, the optimizer (optimizer.rs:389-428).  A communicator spans up to 16 GPUs of
+ * one box.  NCCL is looked up at run time (AG_ERR_UNSUPPORTED when it cannot be loaded). */
+
+/* One process drives all GPUs: devs[r] is rank r's device object (its stream carries the
+ * rank's collectives, so they are ordered with its kernels).  ≙ ncclCommInitAll. */
+AG_API int ag_comm_create(ag_device *const *devs, int n, ag_comm **out);
+/* One process per GPU: rank 0 calls ag_comm_unique_id (128 bytes), hands the id to the other
+ * ranks by any means, and every rank calls ag_comm_create_rank.  ≙ ncclCommInitRank. */
+AG_API int ag_comm_unique_id(void *id_out, size_t bytes);
+AG_API int ag_comm_create_rank(ag_device *dev, int world, int rank, const void *unique_id,
+                               size_t id_bytes, ag_comm **out);
+AG_API int ag_comm_destroy(ag_comm *comm);
+/* Number of ranks, and whether the GPUs can address one another's memory (what
+ * ag_model_allreduce_update needs). */
+AG_API int ag_comm_world(ag_comm *comm, int *world, int *fused_available);
+/* Limit, in seconds, of ag_comm_wait and of the device-side wait of
+ * ag_model_allreduce_update (default 2). */
+AG_API int ag_comm_set_timeout(ag_comm *comm, double seconds);
+
+/* buf (n elements of dtype, on rank's GPU) = sum over all ranks, in place, enqueued on the
+ * rank's stream.  With one process per GPU each process calls it for its rank.  With one
+ * process for all GPUs either one host thread per rank calls it, or one thread calls
+ * ag_allreduce_sum_all with every rank's buffer. */
+AG_API int ag_allreduce_sum(ag_comm *comm, int rank, ag_dtype dtype, void *buf, int64_t n);
+AG_API int ag_allreduce_sum_all(ag_comm *comm, ag_dtype dtype, void *const *bufs, int64_t n);
+/* Waits for rank's stream without blocking inside the driver: polls the stream and NCCL's
+ * asynchronous error state, and gives up after the communicator's timeout
+ * (AG_ERR_DEVICE_TIMEOUT; the rank's NCCL communicator is then aborted, because a collective
+ * whose peer never joins cannot complete). */
+AG_API int ag_comm_wait(ag_comm *comm, int rank);
+
+/* The data-parallel tail of a training step as ONE kernel per GPU: sum all-reduce of the
+ * model's gradient bucket over NVLink (each GPU reads its peers' buckets with plain loads
+ * and adds them in rank order, so all replicas compute the same bits), the factor set by
+ * ag_model_set_grad_scale, and the SGD update (≙ criterion.rs:84 + SGD::update,
+ * optimizer.rs:389-428).  Same result as ag_allreduce_sum on the bucket followed by
+ * ag_model_apply_update.  Enqueued on the model's stream; returns without waiting.  Buckets of
+ * more than 512 KiB return AG_ERR_LIMIT (use the two calls above).  A rank whose peers do not
+ * arrive within the communicator's timeout leaves its parameters untouched and reports
+ * AG_ERR_DEVICE_TIMEOUT at the next ag_device_wait / ag_comm_wait. */
+AG_API int ag_model_allreduce_update(ag_model *model, ag_comm *comm, int rank, float lr);
 
 #ifdef __cplusplus
 }

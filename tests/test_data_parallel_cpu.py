@@ -72,3 +72,36 @@ def test_gloo_two_ranks_match_global_batch(tmp_path):
     grads = models.backward(models.LENET5, P, saved, dl)
     full = np.concatenate([g.ravel() for g in grads])
     assert np.abs(g0 - full).max() <= 1e-5 * np.abs(full).max()
+
+
+def _absent_peer_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    sys.path.insert(0, str(ROOT))
+    import time
+    from autograph_b200 import AgError, _capi
+    from autograph_b200 import data_parallel as dp
+    dist = dp.init_process_group("gloo", timeout_s=1.0)
+    bucket = torch.ones(1000)
+    dp.allreduce_gradients(bucket, world)          # a step both ranks take
+    assert bucket[0].item() == world
+    if rank == 1:
+        time.sleep(4.0)                            # rank 1 never enters the next collective
+        return
+    t0 = time.time()
+    try:
+        dp.allreduce_gradients(bucket, world)
+        outcome = "completed"
+    except AgError as exc:
+        outcome = f"{exc.status} {time.time() - t0:.2f}"
+        assert exc.status == _capi.AG_ERR_DEVICE_TIMEOUT
+    (Path(out_dir) / "outcome.txt").write_text(outcome)
+
+
+def test_gloo_rank_that_never_joins_is_detected(tmp_path):
+    """Failure detection on the host: one rank skips a collective; the other gets an error
+    after the group's short timeout instead of waiting forever."""
+    port = _free_port()
+    mp.spawn(_absent_peer_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    status, waited = (tmp_path / "outcome.txt").read_text().split()
+    assert int(status) == -6 and float(waited) < 3.5
