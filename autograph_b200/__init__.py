@@ -16,6 +16,8 @@ from __future__ import annotations
 import ctypes
 from pathlib import Path
 
+import numpy as np
+
 from . import _capi
 from ._capi import AgError, lib, lib_path  # noqa: F401
 
@@ -669,8 +671,19 @@ class Model:
         return self._fetch(lib().ag_model_get_gradient, index)
 
     def set_sgd(self, momentum=None):
+        """≙ SGD::builder().momentum(m).build(); clears the velocity state."""
         _capi.check(lib().ag_model_set_sgd(self._h,
                                            ctypes.c_float(-1.0 if momentum is None else momentum)))
+        self.momentum = momentum
+
+    def get_velocity(self, index):
+        return self._fetch(lib().ag_model_get_velocity, index)
+
+    def set_velocities(self, arrays):
+        for i, a in enumerate(arrays):
+            h = self._host(np.asarray(a, dtype="float32").ravel())
+            assert h.numel() == self.parameter_lens[i]
+            _capi.check(lib().ag_model_set_velocity(self._h, i, _ptr(h)))
 
     def set_grad_scale(self, scale: float):
         _capi.check(lib().ag_model_set_grad_scale(self._h, ctypes.c_float(scale)))
@@ -718,17 +731,22 @@ class Model:
         """The model as serde_json text in the reference's layout (one field name per layer,
         as in the user's model struct); see serde_format."""
         from . import serde_format as sf
-        params = [self.get_parameter(i) for i in range(len(self.parameter_lens))]
+        n = len(self.parameter_lens)
+        params = [self.get_parameter(i) for i in range(n)]
         bf16 = self.dtype == _torch().bfloat16
-        return sf.dumps(sf.model_to_value(self.spec, params, field_names, bf16=bf16))
+        # optimizer state travels with the parameters when there is one (SGD with momentum)
+        vel = [self.get_velocity(i) for i in range(n)] if getattr(self, "momentum", None) else None
+        return sf.dumps(sf.model_to_value(self.spec, params, field_names, bf16=bf16, velocities=vel))
 
     def load_serde_json(self, text: str):
         """Loads the parameters of a stack written by to_serde_json or by the reference."""
         from . import serde_format as sf
-        params = sf.model_from_value(sf.loads(text))
+        params, states = sf.model_from_value(sf.loads(text), with_state=True)
         if [p.size for p in params] != list(self.parameter_lens):
             raise AgError(_capi.AG_ERR_SHAPE, "checkpoint does not match the model's parameters")
         self.set_parameters(params)
+        if all(v is not None for v in states) and getattr(self, "momentum", None):
+            self.set_velocities(states)   # a momentum run continues where it stopped
 
     def forward_device(self, x_dev, out_dev=None):
         bs, c, h, w = x_dev.shape

@@ -43,6 +43,10 @@ class LayerSpec(ctypes.Structure):
 
 
 def lib_path() -> Path:
+    import os
+    # AG_LIB: a side build of the same library (e.g. one with phase timestamps compiled in)
+    if os.environ.get("AG_LIB"):
+        return Path(os.environ["AG_LIB"]).resolve()
     return Path(__file__).resolve().parent / "libautograph_b200.so"
 
 
@@ -141,6 +145,8 @@ _SIGNATURES = {
     "ag_model_get_parameter": (c_int, [_P, c_int32, _P]),
     "ag_model_get_gradient": (c_int, [_P, c_int32, _P]),
     "ag_model_set_sgd": (c_int, [_P, c_float]),
+    "ag_model_get_velocity": (c_int, [_P, c_int32, _P]),
+    "ag_model_set_velocity": (c_int, [_P, c_int32, _P]),
     "ag_model_set_grad_scale": (c_int, [_P, c_float]),
     "ag_model_infer": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int64, _P]),
     "ag_model_forward_device": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int64, _P]),

@@ -19,9 +19,16 @@ BUILD = HERE / "_build"
 LIB = HERE / "libautograph_b200.so"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+# Extra compiler flags (e.g. AG_NVCC_EXTRA=-DAG_PHASE_STAMPS for the phase timestamps that the
+# profile summaries quote) and where to put the result (AG_LIB_OUT=<path>: a side build that
+# leaves the product library alone).
+EXTRA = os.environ.get("AG_NVCC_EXTRA", "").split()
+if os.environ.get("AG_LIB_OUT"):
+    LIB = Path(os.environ["AG_LIB_OUT"]).resolve()
+    BUILD = LIB.parent / (LIB.stem + "_build")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
-          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+          "--expt-relaxed-constexpr", "-Xptxas", "-v", *EXTRA]
 
 
 def sources() -> list[Path]:

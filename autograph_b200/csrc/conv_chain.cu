@@ -18,10 +18,38 @@
 #include "conv_chain.cuh"
 #include "dense_small_device.cuh"
 
+#include <cstdlib>
+
 namespace ag {
 namespace conv_chain {
 
 using dense_small::ROWS;
+
+// Phase timestamps for the profile summaries: a library built with -DAG_PHASE_STAMPS records
+// %globaltimer at every phase boundary of the first 1024 CTAs (thread 0) and exports
+// ag_debug_chain_stamps to read them.  Not part of normal builds.
+#ifdef AG_PHASE_STAMPS
+constexpr int kStampSlots = 8;
+static __device__ unsigned long long g_stamps[1024 * kStampSlots];
+__device__ __forceinline__ void stamp(int i) {
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_stamps[blockIdx.x * kStampSlots + i] = t;
+    }
+}
+#define AG_STAMP(i) stamp(i)
+#else
+#define AG_STAMP(i)
+#endif
+
+}  // namespace conv_chain
+}  // namespace ag
+
+#include "conv_chain_lenet.cuh"
+
+namespace ag {
+namespace conv_chain {
 
 struct StagePlan {
     const void *w, *bias;
@@ -75,6 +103,7 @@ __global__ void __launch_bounds__(512, 1)
     const direct::Params &p0 = pl.st[0].p;
     const int img_elems = p0.ic * p0.ih * p0.iw;
     float *xa = smem + pl.xa_off;
+    AG_STAMP(0);
 
     if (pl.x8 != nullptr) {
         // scaled_cast on the way in: alpha * u8 in T (alpha rounded to T, one rounding of the product)
@@ -109,6 +138,7 @@ __global__ void __launch_bounds__(512, 1)
         for (int i = threadIdx.x; i < k0 * ROWS; i += blockDim.x) xa[i] = 0.f;
     }
     __syncthreads();
+    AG_STAMP(1);
 
     const float *img = smem + pl.in_off;
     for (int s = 0; s < pl.n_conv; ++s) {
@@ -124,8 +154,10 @@ __global__ void __launch_bounds__(512, 1)
                                            sp.bias != nullptr, sp.p, nimg, out);
         }
         __syncthreads();
+        AG_STAMP(2 + s);
     }
     dense_small::chain_layers<T>(xa, smem + pl.xb_off, smem + pl.red_off, pl.chain, b0, nimg, y);
+    AG_STAMP(7);
 }
 
 static bool default_options(const ag_conv2_options &o) {
@@ -213,6 +245,44 @@ template <class T>
 int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t bs, int64_t ic,
             int64_t ih, int64_t iw, int n_conv, const ag_conv_stage *stages, int n_dense,
             const dense_small::ChainLayer *layers, T *y) {
+    // A network with LeNet5's geometry runs the kernel specialised for it (AG_CHAIN_GENERIC=1
+    // keeps the generic kernel, for comparisons).
+    static const bool generic_only = [] {
+        const char *e = getenv("AG_CHAIN_GENERIC");
+        return e && e[0] == '1';
+    }();
+    if (!generic_only) {
+        lenet::Plan lp;
+        const ag_dtype dtype = sizeof(T) == 4 ? AG_F32 : AG_BF16;
+        const size_t lsmem = lenet::make_plan(&lp, dtype, bs, ic, ih, iw, n_conv, stages, n_dense, layers);
+        if (lsmem != 0) {
+            int64_t group = ceil_div(bs, (int64_t)dev->sm_count);
+            lp.group = (int)(group < 1 ? 1 : (group > lenet::kGroup ? lenet::kGroup : group));
+            lp.status = dev->status_dev;
+            auto kernel = lenet::lenet_chain_kernel<T>;
+            static bool attr_set[2] = {false, false};
+            if (!attr_set[sizeof(T) == 4]) {
+                AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)lsmem));
+                attr_set[sizeof(T) == 4] = true;
+            }
+            // launched so that it may overlap the tail of a preceding launch of the same kernel
+            // (the kernel itself waits for its predecessor before it reads or writes memory)
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)ceil_div(bs, (int64_t)lp.group));
+            cfg.blockDim = dim3(lenet::kThreads);
+            cfg.dynamicSmemBytes = lsmem;
+            cfg.stream = dev->stream;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr.val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            AG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, x, x8, alpha, y, lp));
+            AG_CHECK_LAUNCH();
+            return AG_OK;
+        }
+    }
     Plan pl;
     pl.x8 = x8;
     pl.alpha = alpha;
@@ -270,6 +340,15 @@ static int conv_dense_chain_entry(ag_device *dev, ag_dtype dtype, const void *x,
                                               iw, n_conv, stages, n_dense, layers,
                                               (__nv_bfloat16 *)y);
 }
+
+#ifdef AG_PHASE_STAMPS
+extern "C" __attribute__((visibility("default"))) int ag_debug_chain_stamps(unsigned long long *host,
+                                                                            size_t count) {
+    const size_t n = count < 1024 * conv_chain::kStampSlots ? count : 1024 * conv_chain::kStampSlots;
+    AG_CUDA_TRY(cudaMemcpyFromSymbol(host, conv_chain::g_stamps, n * sizeof(unsigned long long)));
+    return AG_OK;
+}
+#endif
 
 extern "C" int ag_conv_dense_chain_forward(ag_device *dev, ag_dtype dtype, const void *x, int64_t bs,
                                            int64_t ic, int64_t ih, int64_t iw, int32_t n_conv,

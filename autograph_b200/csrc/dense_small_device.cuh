@@ -88,25 +88,107 @@ __device__ __forceinline__ void load4_w(const __nv_bfloat16 *p, float (&v)[4]) {
     v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xffff0000u);
 }
 
-// Runs every layer of the chain for the ROWS rows whose first-layer input is in
-// xa as [k][ROWS] (f32).  xb is the second activation buffer, red the
-// [slices][ROWS][np] scratch.  The plan's (column, k slice) pairs are spread over
-// the CTA's threads (a CTA with fewer threads than pairs takes several each), so
-// the sums and their order do not depend on the CTA size.  Rows >= rows are
-// computed but not stored.  All threads of the CTA must call this.
-template <class T>
-__device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, const ChainParams &p,
-                                             int m0, int rows, T *__restrict__ y) {
-    for (int l = 0; l < p.n_layers; ++l) {
-        const ChainStep st = p.s[l];
-        const T *w = reinterpret_cast<const T *>(st.w);
+// Weight loads from a known address space.  A pointer that may be global or shared compiles
+// to a generic load, which takes the global-memory path even when it lands in shared memory;
+// SMEM = true reads through ld.shared.
+template <bool SMEM>
+__device__ __forceinline__ void load4_w_as(const float *p, float (&v)[4]) {
+    if constexpr (SMEM) {
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3])
+                     : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    } else {
+        load4_w(p, v);
+    }
+}
+template <bool SMEM>
+__device__ __forceinline__ void load4_w_as(const __nv_bfloat16 *p, float (&v)[4]) {
+    if constexpr (SMEM) {
+        uint32_t a, b;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
+                     : "=r"(a), "=r"(b)
+                     : "r"((uint32_t)__cvta_generic_to_shared(p)));
+        v[0] = __uint_as_float(a << 16); v[1] = __uint_as_float(a & 0xffff0000u);
+        v[2] = __uint_as_float(b << 16); v[3] = __uint_as_float(b & 0xffff0000u);
+    } else {
+        load4_w(p, v);
+    }
+}
+template <bool SMEM>
+__device__ __forceinline__ void load2_as(const float *p, float &a, float &b) {
+    if constexpr (SMEM) {
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
+                     : "=f"(a), "=f"(b)
+                     : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    } else {
+        load2_to_f32(p, a, b);
+    }
+}
+template <bool SMEM>
+__device__ __forceinline__ void load2_as(const __nv_bfloat16 *p, float &a, float &b) {
+    if constexpr (SMEM) {
+        uint32_t v;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+        a = __uint_as_float(v << 16);
+        b = __uint_as_float(v & 0xffff0000u);
+    } else {
+        load2_to_f32(p, a, b);
+    }
+}
+
+// One layer of the chain: xa [K][ROWS] -> xb [N][ROWS] (or y for the last layer).  `w` is the
+// layer's weight matrix as the kernel should read it: st.w, or a copy of it in shared memory.
+// QUADS: a work item is four adjacent columns x four rows (half of ROWS) where the layer allows
+// it.  Shared memory delivers 128 bytes per clock to the register file whether a load is a
+// broadcast or not, so the square tile (16 + 16 bytes per k step for 16 FFMAs) beats the
+// 8 rows x 2 columns of the default path (32 + 8 bytes).  The k slices, and with them every
+// sum, are unchanged.
+template <class T, bool QUADS = false, bool SMEM = false>
+__device__ __forceinline__ void chain_layer(const ChainStep &st, const T *w, const float *xa,
+                                            float *xb, float *red, int m0, int rows, bool last,
+                                            T *__restrict__ y) {
+    {
         const T *bias = reinterpret_cast<const T *>(st.bias);
+        const bool quads = QUADS && !st.transposed && (st.N % 4 == 0) &&
+                           (reinterpret_cast<uintptr_t>(w) % (4 * sizeof(T)) == 0);
         // Two adjacent output columns per (column, k slice) work item when the weight rows
         // allow an aligned two-element load: twice the FFMAs per load instruction.  The sum
         // for every output is the same either way (same k slices, same order).
         const bool pairs = (st.N % 2 == 0) &&
                            (reinterpret_cast<uintptr_t>(w) % (2 * sizeof(T)) == 0);
-        if (st.transposed) {
+        if (quads) {
+            // item = (four columns, half of the rows, k slice)
+            const int quarter = st.np / 4;
+            for (int vt = threadIdx.x; vt < quarter * 2 * st.slices; vt += blockDim.x) {
+                const int half = vt & 1, q = vt >> 1;
+                const int n = 4 * (q % quarter), slice = q / quarter;
+                float acc[4][4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) acc[c][r] = 0.f;
+                if (n < st.N) {
+                    const int k0 = slice * st.kchunk, k1 = min(st.K, k0 + st.kchunk);
+                    const T *wp = w + (int64_t)k0 * st.N + n;
+                    const float *xp = xa + 4 * half;
+#pragma unroll 8
+                    for (int k = k0; k < k1; ++k, wp += st.N) {
+                        float wv[4];
+                        load4_w_as<SMEM>(wp, wv);
+                        const float4 a = *reinterpret_cast<const float4 *>(xp + k * ROWS);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            acc[c][0] = fmaf(a.x, wv[c], acc[c][0]); acc[c][1] = fmaf(a.y, wv[c], acc[c][1]);
+                            acc[c][2] = fmaf(a.z, wv[c], acc[c][2]); acc[c][3] = fmaf(a.w, wv[c], acc[c][3]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    *reinterpret_cast<float4 *>(red + (slice * ROWS + 4 * half + r) * st.np + n) =
+                        make_float4(acc[0][r], acc[1][r], acc[2][r], acc[3][r]);
+            }
+        } else if (st.transposed) {
             // Thread (n, k slice) walks row n of w, contiguous in k: four weights per load
             // when the rows keep 4-element alignment.
             const bool vec4 = (st.K % 4 == 0) && (st.kchunk % 4 == 0) &&
@@ -163,7 +245,7 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
 #pragma unroll 8
                     for (int k = k0; k < k1; ++k, wp += st.N) {
                         float w0, w1;
-                        load2_to_f32(wp, w0, w1);
+                        load2_as<SMEM>(wp, w0, w1);
                         const float4 a = *reinterpret_cast<const float4 *>(xa + k * ROWS);
                         const float4 b = *reinterpret_cast<const float4 *>(xa + k * ROWS + 4);
                         acc0[0] = fmaf(a.x, w0, acc0[0]); acc1[0] = fmaf(a.x, w1, acc1[0]);
@@ -206,12 +288,22 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
             }
         }
         __syncthreads();
-        const bool last = l + 1 == p.n_layers;
         for (int i = threadIdx.x; i < ROWS * st.np; i += blockDim.x) {
             const int r = i / st.np, c = i - r * st.np;
             if (c >= st.N) continue;
             float s = 0.f;
-            for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
+            if constexpr (QUADS) {
+                // the partial sums are fetched together and added in slice order
+                float part[16];
+#pragma unroll
+                for (int sl = 0; sl < 16; ++sl)
+                    part[sl] = sl < st.slices ? red[(sl * ROWS + r) * st.np + c] : 0.f;
+#pragma unroll
+                for (int sl = 0; sl < 16; ++sl)
+                    if (sl < st.slices) s += part[sl];
+            } else {
+                for (int sl = 0; sl < st.slices; ++sl) s += red[(sl * ROWS + r) * st.np + c];
+            }
             float v = to_f32(from_f32<T>(s));
             if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
             if (st.gate != nullptr && r < rows &&
@@ -229,6 +321,21 @@ __device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, c
             }
         }
         __syncthreads();
+    }
+}
+
+// Runs every layer of the chain for the ROWS rows whose first-layer input is in
+// xa as [k][ROWS] (f32).  xb is the second activation buffer, red the
+// [slices][ROWS][np] scratch.  The plan's (column, k slice) pairs are spread over
+// the CTA's threads (a CTA with fewer threads than pairs takes several each), so
+// the sums and their order do not depend on the CTA size.  Rows >= rows are
+// computed but not stored.  All threads of the CTA must call this.
+template <class T>
+__device__ __forceinline__ void chain_layers(float *xa, float *xb, float *red, const ChainParams &p,
+                                             int m0, int rows, T *__restrict__ y) {
+    for (int l = 0; l < p.n_layers; ++l) {
+        chain_layer<T>(p.s[l], reinterpret_cast<const T *>(p.s[l].w), xa, xb, red, m0, rows,
+                       l + 1 == p.n_layers, y);
         float *t = xa;
         xa = xb;
         xb = t;

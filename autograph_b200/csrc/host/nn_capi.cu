@@ -1101,6 +1101,23 @@ int ag_model_get_gradient(ag_model *model, int32_t index, void *host) {
     return ag_download(model->dev, host, g.data(), g.nbytes());
 }
 
+int ag_model_get_velocity(ag_model *model, int32_t index, void *host) {
+    AG_REQUIRE(model && host, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(index >= 0 && index < (int32_t)model->params.size(), AG_ERR_INVALID,
+               "parameter index %d out of range", index);
+    Tensor &v = model->params[index]->velocity;
+    return ag_download(model->dev, host, v.data(), v.nbytes());
+}
+
+int ag_model_set_velocity(ag_model *model, int32_t index, const void *host) {
+    AG_REQUIRE(model && host, AG_ERR_INVALID, "null argument");
+    AG_REQUIRE(index >= 0 && index < (int32_t)model->params.size(), AG_ERR_INVALID,
+               "parameter index %d out of range", index);
+    Tensor &v = model->params[index]->velocity;
+    AG_TRY(ag_upload(model->dev, v.data(), host, v.nbytes()));
+    return ag_device_wait(model->dev);
+}
+
 int ag_model_set_sgd(ag_model *model, float momentum) {
     AG_REQUIRE(model != nullptr, AG_ERR_INVALID, "model is null");
     model->use_momentum = momentum >= 0.f;

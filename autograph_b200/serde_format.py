@@ -15,7 +15,11 @@ the tree the reference builds and offers its serde_json form.
   does with a tail of fewer than eight bytes is not pinned: zero padding is assumed here.
 * Parameter (src/learn/neural_network/autograd.rs:638-656): ``{ value: ScalarTensor }`` plus
   ``optim_state`` only when an optimizer state exists (skipped when none; gradients are never
-  stored).
+  stored).  The state (src/learn/neural_network/optimizer.rs:102-131, 166-172) is
+  ``State { name, key_values: [(key, Value)] }`` (the type id is skipped) with
+  ``Value::Tensor(TensorValue { tensor, parameter_device, parameter_type })``; SGD with momentum
+  keeps one entry, ``"velocity"`` (optimizer.rs:366-383).  serde_json prints the enum as
+  ``{"Tensor": {...}}`` and the pair as a two-element array.
 * Layers (src/learn/neural_network/layer.rs:834-848, 1069-1073, 1150-1155, 1222-1251):
   ``Conv { weight, padding, stride, dilation, bias }``, ``Dense { weight, bias }``,
   ``MaxPool { filter, stride }``; ``Relu``, ``Flatten`` and ``Identity`` are unit structs
@@ -95,35 +99,68 @@ def _bf16_bits_to_f32(a: np.ndarray) -> np.ndarray:
     return (a.astype(np.uint32) << 16).view(np.float32)
 
 
-def _param(a: np.ndarray, bf16: bool) -> dict:
+def _tensor(a: np.ndarray, bf16: bool) -> dict:
     data = _f32_to_bf16_bits(a) if bf16 else np.ascontiguousarray(a, np.float32)
-    return {"value": tensor_to_value(data, bf16)}
+    return tensor_to_value(data, bf16)
 
 
-def model_to_value(spec, params, field_names, bf16: bool = False) -> dict:
+def sgd_state_to_value(velocity: np.ndarray, bf16: bool) -> dict:
+    """SGD's per-parameter state as the reference serialises it (momentum in use)."""
+    return {"name": "SGD",
+            "key_values": [["velocity", {"Tensor": {"tensor": _tensor(velocity, bf16),
+                                                    "parameter_device": True,
+                                                    "parameter_type": True}}]]}
+
+
+def sgd_state_from_value(v):
+    """The velocity array of an optim_state value, or None when it holds none."""
+    if not v:
+        return None
+    for key, value in v.get("key_values", []):
+        if key == "velocity" and "Tensor" in value:
+            a, is_bf16 = tensor_from_value(value["Tensor"]["tensor"])
+            return (_bf16_bits_to_f32(a) if is_bf16 else a.astype(np.float32)).ravel()
+    return None
+
+
+def _param(a: np.ndarray, bf16: bool, velocity=None) -> dict:
+    out = {"value": _tensor(a, bf16)}
+    if velocity is not None:   # skipped when there is no state (skip_serializing_if)
+        out["optim_state"] = sgd_state_to_value(np.asarray(velocity, np.float32).reshape(a.shape), bf16)
+    return out
+
+
+def model_to_value(spec, params, field_names, bf16: bool = False, velocities=None) -> dict:
     """A layer stack as the reference would serialise the user's model struct.
 
     spec: the layer list used to build an ``autograph_b200.Model`` (tuples such as
     ("conv", ic, oc, (fh, fw), bias), ("relu",), ("pool", (h, w)), ("flatten",),
     ("dense", inputs, outputs, bias)); params: the parameter arrays in the model's order
-    (float32; for a bf16 model the bf16-representable values); field_names: one name per layer.
+    (float32; for a bf16 model the bf16-representable values); field_names: one name per layer;
+    velocities: SGD's velocity per parameter (same order) when momentum is in use, else None.
     """
     if len(field_names) != len(spec):
         raise ValueError("one field name per layer")
     out, it = {}, iter(params)
+    vit = iter(velocities) if velocities is not None else None
+    vel = lambda: next(vit) if vit is not None else None
     for name, layer in zip(field_names, spec):
         kind = layer[0]
         if kind == "conv":
             _, ic, oc, (fh, fw), bias = layer
             w = np.asarray(next(it), np.float32).reshape(oc, ic, fh, fw)
             b = np.asarray(next(it), np.float32).reshape(oc) if bias else None
-            out[name] = {"weight": _param(w, bf16), "padding": [0, 0], "stride": [1, 1],
-                         "dilation": [1, 1], "bias": _param(b, bf16) if bias else None}
+            out[name] = {"weight": _param(w, bf16, vel()), "padding": [0, 0], "stride": [1, 1],
+                         "dilation": [1, 1], "bias": _param(b, bf16, vel()) if bias else None}
         elif kind == "dense":
+            if len(layer) > 4:
+                raise ValueError("a layer that shares another layer's parameters has no "
+                                 "counterpart in the reference's format")
             _, ins, outs, bias = layer
             w = np.asarray(next(it), np.float32).reshape(ins, outs)
             b = np.asarray(next(it), np.float32).reshape(outs) if bias else None
-            out[name] = {"weight": _param(w, bf16), "bias": _param(b, bf16) if bias else None}
+            out[name] = {"weight": _param(w, bf16, vel()),
+                         "bias": _param(b, bf16, vel()) if bias else None}
         elif kind == "pool":
             out[name] = {"filter": [int(layer[1][0]), int(layer[1][1])],
                          "stride": [int(layer[1][0]), int(layer[1][1])]}
@@ -134,10 +171,11 @@ def model_to_value(spec, params, field_names, bf16: bool = False) -> dict:
     return out
 
 
-def model_from_value(value: dict) -> list[np.ndarray]:
+def model_from_value(value: dict, with_state: bool = False):
     """The parameter arrays (float32, flattened, in field order: weight then bias) of a stack
-    written by model_to_value or by the reference."""
-    params = []
+    written by model_to_value or by the reference.  with_state: also the list of SGD velocities
+    (None where a parameter carries no state)."""
+    params, states = [], []
     for layer in value.values():
         if not isinstance(layer, dict):
             continue
@@ -147,7 +185,8 @@ def model_from_value(value: dict) -> list[np.ndarray]:
                 continue
             a, is_bf16 = tensor_from_value(p["value"])
             params.append((_bf16_bits_to_f32(a) if is_bf16 else a.astype(np.float32)).ravel())
-    return params
+            states.append(sgd_state_from_value(p.get("optim_state")))
+    return (params, states) if with_state else params
 
 
 def dumps(value) -> str:

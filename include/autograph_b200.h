@@ -451,8 +451,15 @@ AG_API int ag_model_set_parameter(ag_model *model, int32_t index, const void *ho
 AG_API int ag_model_get_parameter(ag_model *model, int32_t index, void *host);
 /* Gradient of the last training step (before the update consumed it). */
 AG_API int ag_model_get_gradient(ag_model *model, int32_t index, void *host);
-/* ≙ SGD::builder().momentum(m).build() (optimizer.rs:353-357); momentum < 0 = plain SGD. */
+/* ≙ SGD::builder().momentum(m).build() (optimizer.rs:353-357); momentum < 0 = plain SGD.
+ * Clears the velocity state. */
 AG_API int ag_model_set_sgd(ag_model *model, float momentum);
+/* The optimizer state of one parameter: SGD's "velocity" tensor (optimizer.rs:366-383), which
+ * the reference stores in the parameter (ParameterBase::optim_state, autograd.rs:647-656) and
+ * writes into checkpoints.  Host memory holding the model's dtype; same length as the
+ * parameter. */
+AG_API int ag_model_get_velocity(ag_model *model, int32_t index, void *host);
+AG_API int ag_model_set_velocity(ag_model *model, int32_t index, const void *host);
 /* Scale applied to gradients before the update (1/world for data parallel). */
 AG_API int ag_model_set_grad_scale(ag_model *model, float scale);
 

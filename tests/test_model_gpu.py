@@ -216,3 +216,36 @@ def test_model_wrappers_refuse_tensors_the_library_would_misread(dev):
         m.infer(x, torch.empty((8, 12)))                    # wrong output shape
     assert m.infer(x).shape == (8, 10)
     m.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_momentum_run_survives_a_checkpoint(dev, dtype):
+    """The optimizer state (SGD's velocity) is part of the checkpoint: a model restored from the
+    text continues a momentum run bit for bit (ParameterBase::optim_state, autograd.rs:647-656)."""
+    import autograph_b200 as ag
+    names = ["conv1", "relu1", "pool1", "conv2", "relu2", "pool2", "flatten", "dense1", "relu3",
+             "dense2", "relu4", "dense3"]
+    rng = np.random.default_rng(31)
+    x = torch.from_numpy(rng.uniform(0, 1, (64, 1, 28, 28)).astype(np.float32)).to(dtype).pin_memory()
+    t = torch.from_numpy(rng.integers(0, 10, 64).astype(np.uint8)).pin_memory()
+    a = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=41)
+    a.set_sgd(0.9)
+    for _ in range(3):
+        a.train_step(x, t, 0.05)
+    text = a.to_serde_json(names)
+    assert '"velocity"' in text
+    b = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=42)
+    b.set_sgd(0.9)
+    b.load_serde_json(text)
+    c = ag.Model(dev, ag.LENET5_SPEC, dtype, seed=43)      # restored without its optimizer state
+    c.set_sgd(0.9)
+    c.set_parameters([a.get_parameter(i) for i in range(len(a.parameter_lens))])
+    la, lb, lc = (m.train_step(x, t, 0.05) for m in (a, b, c))
+    assert la == lb == lc                                   # same parameters, same loss
+    for i in range(len(a.parameter_lens)):
+        assert np.array_equal(a.get_parameter(i), b.get_parameter(i)), i
+        assert np.array_equal(a.get_velocity(i), b.get_velocity(i)), i
+    assert any(not np.array_equal(a.get_parameter(i), c.get_parameter(i))
+               for i in range(len(a.parameter_lens)))      # the velocity mattered
+    for m in (a, b, c):
+        m.close()

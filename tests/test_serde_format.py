@@ -54,3 +54,32 @@ def test_model_round_trip_f32_and_bf16():
     assert len(vb["dense1"]["weight"]["value"]["buffer"][2]) == 256 * 128 * 2 // 8
     back = sf.model_from_value(vb)
     assert all(np.array_equal(a.ravel(), b) for a, b in zip(pb, back))
+
+
+def test_optimizer_state_layout_and_round_trip():
+    """Parameter { value, optim_state } with SGD's velocity (autograd.rs:647-656,
+    optimizer.rs:102-131, 166-172, 366-383): State { name, key_values: [("velocity",
+    Value::Tensor(TensorValue { tensor, parameter_device, parameter_type }))] }."""
+    import autograph_b200 as ag
+    rng = np.random.default_rng(7)
+    shapes = [(6, 1, 5, 5), (16, 6, 5, 5), (256, 128), (128, 84), (84, 10), (10,)]
+    params = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+    vel = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+    names = ["conv1", "relu1", "pool1", "conv2", "relu2", "pool2", "flatten", "dense1", "relu3",
+             "dense2", "relu4", "dense3"]
+    v = sf.loads(sf.dumps(sf.model_to_value(ag.LENET5_SPEC, params, names, velocities=vel)))
+    st = v["dense3"]["bias"]["optim_state"]
+    assert st["name"] == "SGD" and len(st["key_values"]) == 1
+    key, value = st["key_values"][0]
+    assert key == "velocity" and list(value) == ["Tensor"]
+    tv = value["Tensor"]
+    assert list(tv) == ["tensor", "parameter_device", "parameter_type"]
+    assert tv["parameter_device"] is True and tv["parameter_type"] is True
+    assert tv["tensor"]["dim"] == [10] and tv["tensor"]["buffer"][0] == "F32"
+    back, states = sf.model_from_value(v, with_state=True)
+    assert all(np.array_equal(a.ravel(), b) for a, b in zip(params, back))
+    assert all(np.array_equal(a.ravel(), b) for a, b in zip(vel, states))
+    # no optimizer state: the field is absent, as skip_serializing_if leaves it
+    plain = sf.model_to_value(ag.LENET5_SPEC, params, names)
+    assert "optim_state" not in plain["dense1"]["weight"]
+    assert sf.model_from_value(plain, with_state=True)[1] == [None] * 6
