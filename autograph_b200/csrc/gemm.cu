@@ -92,11 +92,16 @@ extern "C" int ag_dense_forward(ag_device *dev, ag_dtype dtype, const void *x, i
     const __nv_bfloat16 *px = (const __nv_bfloat16 *)x, *pw = (const __nv_bfloat16 *)w;
     __nv_bfloat16 *py = (__nv_bfloat16 *)y;
     if (tc::gemm_bf16_eligible(bs, inputs, outputs, px, inputs, 1, pw, outputs, 1, py, outputs, 1)) {
-        // Large products go to the tensor cores; bias and relu follow as separate passes.
+        // Large products go to the tensor cores with bias and relu in the kernel's epilogue
+        // (a bias that is not 16-byte aligned is added by a separate pass).
+        const __nv_bfloat16 *pb = (const __nv_bfloat16 *)bias;
+        const bool bias_fused = pb && (reinterpret_cast<uintptr_t>(pb) & 15) == 0;
+        const bool relu_fused = fuse_relu && (!pb || bias_fused);
+        tc::Epilogue epi{bias_fused ? pb : nullptr, relu_fused};
         AG_TRY(tc::gemm_bf16(dev, (int)bs, (int)inputs, (int)outputs, 1.f, px, inputs, 1, pw,
-                             outputs, 1, 0.f, py, outputs, 1));
-        if (bias) AG_TRY(ag_bias_add(dev, dtype, y, bias, bs, outputs, 1));
-        if (fuse_relu) AG_TRY(ag_relu(dev, dtype, y, y, bs * outputs));
+                             outputs, 1, 0.f, py, outputs, 1, &epi));
+        if (pb && !bias_fused) AG_TRY(ag_bias_add(dev, dtype, y, bias, bs, outputs, 1));
+        if (fuse_relu && !relu_fused) AG_TRY(ag_relu(dev, dtype, y, y, bs * outputs));
         return AG_OK;
     }
     return dense_forward_simt<__nv_bfloat16>(dev, px, (int)bs, (int)inputs, pw, (int)outputs,

@@ -52,6 +52,8 @@ struct Params {
     float *partial;    // null: one slice, results go to C
     int splits;
     int kb_per_split;  // 64-wide k blocks per slice
+    const __nv_bfloat16 *bias;  // fused Dense epilogue (alpha = 1, beta = 0): bias [N] or null, relu
+    int relu;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int &m_blk, int &n_blk) {
@@ -271,17 +273,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 }
                             }
                             uint32_t o[4];
+                            if (p.bias != nullptr || p.relu) {
+                                float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                                if (p.bias != nullptr) {
+                                    const uint4 b4 = *reinterpret_cast<const uint4 *>(p.bias + col);
+                                    const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                o[j] = *reinterpret_cast<uint32_t *>(&h);
+                                    for (int j = 0; j < 4; ++j) {
+                                        bv[2 * j] = __uint_as_float(bw[j] << 16);
+                                        bv[2 * j + 1] = __uint_as_float(bw[j] & 0xffff0000u);
+                                    }
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    o[j] = bf16_pair_epilogue(__float_as_uint(v[2 * j]),
+                                                              __float_as_uint(v[2 * j + 1]), bv[2 * j],
+                                                              bv[2 * j + 1], p.bias != nullptr,
+                                                              p.relu != 0);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                    o[j] = *reinterpret_cast<uint32_t *>(&h);
+                                }
                             }
                             *dst = make_uint4(o[0], o[1], o[2], o[3]);
                         } else {
                             for (int j = 0; j < 8 && col + j < p.N; ++j) {
                                 float x = v[j];
                                 if (p.beta != 0.f) x += p.beta * __bfloat162float(crow[col + j]);
-                                crow[col + j] = __float2bfloat16_rn(x);
+                                __nv_bfloat16 h = __float2bfloat16_rn(x);
+                                if (p.bias != nullptr)
+                                    h = __float2bfloat16_rn(__bfloat162float(h) +
+                                                            __bfloat162float(p.bias[col + j]));
+                                if (p.relu && !(__bfloat162float(h) >= 0.f)) h = __float2bfloat16_rn(0.f);
+                                crow[col + j] = h;
                             }
                         }
                     }
@@ -402,8 +428,12 @@ static int launch(ag_device *dev, const CUtensorMap &ta, const CUtensorMap &tb, 
 
 int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloat16 *a,
               int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
-              float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc) {
+              float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc, const Epilogue *epi) {
     (void)csc;
+    if (epi && !epi->bias && !epi->relu) epi = nullptr;
+    if (epi) AG_REQUIRE(alpha == 1.f && beta == 0.f, AG_ERR_INVALID, "fused epilogue needs alpha 1, beta 0");
+    if (epi && epi->bias)
+        AG_REQUIRE((reinterpret_cast<uintptr_t>(epi->bias) & 15) == 0, AG_ERR_INVALID, "bias not 16-byte aligned");
     // Few output tiles and a long k (a Dense layer with tens of thousands of inputs at a
     // small batch): slices of k become work items so that the whole GPU is used.
     const int out_tiles = (int)(ceil_div(m, BLOCK_M) * ceil_div(n, BLOCK_N));
@@ -417,7 +447,7 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
         splits = (int)ceil_div(total_kb, kb_per_split);
     }
     if (splits == 1 && gemm_bf16_pair_enabled() && m >= 256 && n >= 256)
-        return gemm_bf16_pair(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta, c, rsc, csc);
+        return gemm_bf16_pair(dev, m, k, n, alpha, a, rsa, csa, b, rsb, csb, beta, c, rsc, csc, epi);
     const bool a_mn = !(csa == 1 && rsa % 8 == 0 && rsa >= k);  // else contiguous along m
     const bool b_mn = !(rsb == 1 && csb % 8 == 0 && csb >= k);  // else contiguous along n
     CUtensorMap ta, tb;
@@ -440,6 +470,8 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
     p.status = dev->status_dev;
     p.lbo_k = 0;
     p.partial = nullptr;
+    p.bias = (epi && splits == 1) ? epi->bias : nullptr;   // slices keep raw sums; the reduction applies it
+    p.relu = (epi && splits == 1 && epi->relu) ? 1 : 0;
     p.splits = splits;
     p.kb_per_split = kb_per_split;
     if (splits > 1) {
@@ -457,11 +489,18 @@ int gemm_bf16(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloa
         AG_TRY((launch<false, false>(dev, ta, tb, p)));
     if (splits > 1) {
         // fixed slice order: the result does not depend on scheduling
-        using Epi = simt::StridedEpilogue<__nv_bfloat16>;
-        Epi E{c, rsc, 1, alpha, beta, false, n};
         const int64_t plane = (int64_t)m * n;
-        simt::splitk_reduce_kernel<Epi><<<(unsigned)ceil_div(plane, 256), 256, 0, dev->stream>>>(
-            p.partial, plane, splits, m, n, E);
+        if (epi) {
+            using Epi = simt::BiasReluEpilogue<__nv_bfloat16>;
+            Epi E{c, rsc, epi->bias, epi->relu};
+            simt::splitk_reduce_kernel<Epi><<<(unsigned)ceil_div(plane, 256), 256, 0, dev->stream>>>(
+                p.partial, plane, splits, m, n, E);
+        } else {
+            using Epi = simt::StridedEpilogue<__nv_bfloat16>;
+            Epi E{c, rsc, 1, alpha, beta, false, n};
+            simt::splitk_reduce_kernel<Epi><<<(unsigned)ceil_div(plane, 256), 256, 0, dev->stream>>>(
+                p.partial, plane, splits, m, n, E);
+        }
         AG_CHECK_LAUNCH();
     }
     return AG_OK;

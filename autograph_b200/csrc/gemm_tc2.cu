@@ -16,6 +16,9 @@
 // with one tcgen05.commit that arrives in both CTAs.  Every TMA load is a plain
 // (single-destination) load into the issuing CTA's own shared memory.
 //
+// The PTX wrappers that do not depend on the CTA group (mbarriers with bounded waits,
+// descriptors, tensor-memory loads) are those of tc_ptx.cuh; only the cta_group::2 and
+// cluster forms live here.
 // Every mbarrier wait is bounded (about 2 s) and reports through a status word.
 // Tensor memory is allocated in two 256-column steps; after the first step the
 // two CTAs compare the addresses they were given, and stop with an error if
@@ -25,6 +28,7 @@
 #include <cstdlib>
 
 #include "gemm_tc.cuh"
+#include "tc_ptx.cuh"
 
 namespace ag {
 namespace tc {
@@ -35,18 +39,14 @@ constexpr int TILE_M = 256;   // per pair; 128 rows per CTA
 constexpr int TILE_N = 256;   // per pair; each CTA stages 128 columns of B
 constexpr int BLOCK_K = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
+constexpr int STAGES = 7;
 constexpr int A_BYTES = 128 * BLOCK_K * 2;  // 16 KiB
 constexpr int B_BYTES = 128 * BLOCK_K * 2;  // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int ATOM_BYTES = 64 * BLOCK_K * 2;
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int GROUP_M = 4;
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -67,50 +67,10 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
 // Arrive on a barrier that may live in the peer CTA (cluster address).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                  : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 1023u) {
-            if (*abort_flag) return false;
-            uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > 2000000000ull) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
 }
 // TMA load whose completion may be signalled to a barrier in the peer CTA.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map,
@@ -120,9 +80,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
         "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
         : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
@@ -135,12 +92,6 @@ __device__ __forceinline__ void tmem_relinquish2() {
 __device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
                  : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void umma2_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                            uint32_t idesc, uint32_t accumulate) {
@@ -162,36 +113,6 @@ __device__ __forceinline__ void umma2_commit_multicast(uint32_t bar, uint16_t ma
         "h"(mask)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;
-    d |= 2ull << 61;  // SWIZZLE_128B
-    return d;
-}
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn_major, bool b_mn_major, int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
-           ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
 struct Params {
     int M, N, K;
     int64_t ldc;
@@ -202,6 +123,9 @@ struct Params {
     // partial wave are cut along n into `tail_split` pieces so that they spread over
     // all CTA pairs instead of leaving most of them idle for a whole tile time.
     int t_full, tail_split, num_work;
+    int group_m;  // m blocks per group of the tile order (tiles of a group share B columns in L2)
+    const __nv_bfloat16 *bias;  // fused Dense epilogue (alpha = 1, beta = 0): bias [N] or null, relu
+    int relu;
 };
 
 struct Work {
@@ -210,11 +134,12 @@ struct Work {
     int n_width;  // 256, or 128 for a piece of a tail tile
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int &m_blk, int &n_blk) {
-    const int group_size = GROUP_M * num_n;
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int &m_blk,
+                                            int &n_blk) {
+    const int group_size = group_m * num_n;
     const int g = tile / group_size;
-    const int first_m = g * GROUP_M;
-    const int gm = min(num_m - first_m, GROUP_M);
+    const int first_m = g * group_m;
+    const int gm = min(num_m - first_m, group_m);
     const int r = tile - g * group_size;
     m_blk = first_m + r % gm;
     n_blk = r / gm;
@@ -233,7 +158,7 @@ __device__ __forceinline__ Work decode_work(int w, const Params &p, int num_m, i
         k.n_width = TILE_N / p.tail_split;
         k.n_off = (j % p.tail_split) * k.n_width;
     }
-    tile_coords(tile, num_m, num_n, k.m_blk, k.n_blk);
+    tile_coords(tile, num_m, num_n, p.group_m, k.m_blk, k.n_blk);
     return k;
 }
 
@@ -438,43 +363,76 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
             const int row = m_blk * TILE_M + (int)rank * 128 + quarter * 32 + lane;
             const uint32_t taddr = tmem_acc[acc] + ((uint32_t)(quarter * 32) << 16);
             __nv_bfloat16 *crow = p.C + (int64_t)row * p.ldc;
+            // Each thread holds one row of the accumulator and stores it in 16-byte pieces.
+            // (Passing the tile through shared memory to store whole 128-byte lines was measured
+            // and is slower: the main loop already saturates the shared-memory data path, 1306
+            // against 1342 TFLOP/s at 4096^3.)  Two tensor-memory loads are in flight per wait.
 #pragma unroll 1
-            for (int chunk = 0; chunk < wk.n_width / 32; ++chunk) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + chunk * 32, r);
+            for (int chunk = 0; chunk < wk.n_width / 64; ++chunk) {
+                uint32_t r2[2][32];
+                tmem_ld_32x32(taddr + chunk * 64, r2[0]);
+                tmem_ld_32x32(taddr + chunk * 64 + 32, r2[1]);
                 tmem_ld_wait();
-                const int col0 = wk.n_blk * TILE_N + wk.n_off + chunk * 32;
-                if (row < p.M && col0 < p.N) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const int col = col0 + g * 8;
-                        if (col >= p.N) break;
-                        float v[8];
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t(&r)[32] = r2[half];
+                    const int col0 = wk.n_blk * TILE_N + wk.n_off + chunk * 64 + half * 32;
+                    if (row < p.M && col0 < p.N) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = p.alpha * __uint_as_float(r[g * 8 + j]);
-                        if (col + 8 <= p.N) {
-                            uint4 *dst = reinterpret_cast<uint4 *>(crow + col);
-                            if (p.beta != 0.f) {
-                                uint4 old = *dst;
-                                const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+                        for (int g = 0; g < 4; ++g) {
+                            const int col = col0 + g * 8;
+                            if (col >= p.N) break;
+                            float v[8];
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[2 * j] += p.beta * __uint_as_float(o[j] << 16);
-                                    v[2 * j + 1] += p.beta * __uint_as_float(o[j] & 0xffff0000u);
+                            for (int j = 0; j < 8; ++j) v[j] = p.alpha * __uint_as_float(r[g * 8 + j]);
+                            if (col + 8 <= p.N) {
+                                uint4 *dst = reinterpret_cast<uint4 *>(crow + col);
+                                if (p.beta != 0.f) {
+                                    uint4 old = *dst;
+                                    const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        v[2 * j] += p.beta * __uint_as_float(o[j] << 16);
+                                        v[2 * j + 1] += p.beta * __uint_as_float(o[j] & 0xffff0000u);
+                                    }
                                 }
-                            }
-                            uint32_t o[4];
+                                uint32_t o[4];
+                                if (p.bias != nullptr || p.relu) {
+                                    float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                                    if (p.bias != nullptr) {
+                                        const uint4 b4 = *reinterpret_cast<const uint4 *>(p.bias + col);
+                                        const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                o[j] = *reinterpret_cast<uint32_t *>(&h);
-                            }
-                            *dst = make_uint4(o[0], o[1], o[2], o[3]);
-                        } else {
-                            for (int j = 0; j < 8 && col + j < p.N; ++j) {
-                                float x = v[j];
-                                if (p.beta != 0.f) x += p.beta * __bfloat162float(crow[col + j]);
-                                crow[col + j] = __float2bfloat16_rn(x);
+                                        for (int j = 0; j < 4; ++j) {
+                                            bv[2 * j] = __uint_as_float(bw[j] << 16);
+                                            bv[2 * j + 1] = __uint_as_float(bw[j] & 0xffff0000u);
+                                        }
+                                    }
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j)
+                                        o[j] = bf16_pair_epilogue(__float_as_uint(v[2 * j]),
+                                                                  __float_as_uint(v[2 * j + 1]), bv[2 * j],
+                                                                  bv[2 * j + 1], p.bias != nullptr,
+                                                                  p.relu != 0);
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) {
+                                        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                        o[j] = *reinterpret_cast<uint32_t *>(&h);
+                                    }
+                                }
+                                *dst = make_uint4(o[0], o[1], o[2], o[3]);
+                            } else {
+                                for (int j = 0; j < 8 && col + j < p.N; ++j) {
+                                    float x = v[j];
+                                    if (p.beta != 0.f) x += p.beta * __bfloat162float(crow[col + j]);
+                                    __nv_bfloat16 h = __float2bfloat16_rn(x);
+                                    if (p.bias != nullptr)
+                                        h = __float2bfloat16_rn(__bfloat162float(h) +
+                                                                __bfloat162float(p.bias[col + j]));
+                                    if (p.relu && !(__bfloat162float(h) >= 0.f)) h = __float2bfloat16_rn(0.f);
+                                    crow[col + j] = h;
+                                }
                             }
                         }
                     }
@@ -526,8 +484,34 @@ static EncodeTiledFn encode_fn2() {
     return fn;
 }
 
+// Encoding a tensor map costs a driver call of a microsecond or two, three per product; a
+// caller that multiplies the same buffers again (every layer of every step does) finds its
+// maps in a small per-thread cache keyed by everything the encoding depends on.
+struct TmapKey {
+    const void *base;
+    uint64_t inner, outer, outer_stride;
+    uint32_t box_inner, box_outer;
+    bool operator==(const TmapKey &o) const {
+        return base == o.base && inner == o.inner && outer == o.outer &&
+               outer_stride == o.outer_stride && box_inner == o.box_inner && box_outer == o.box_outer;
+    }
+};
+struct TmapCache {
+    static constexpr int N = 32;
+    TmapKey key[N];
+    CUtensorMap map[N];
+    int used = 0, next = 0;
+};
+
 static int make_tmap2(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
                       uint64_t outer_stride, uint32_t box_inner, uint32_t box_outer) {
+    static thread_local TmapCache cache;
+    const TmapKey k{base, inner, outer, outer_stride, box_inner, box_outer};
+    for (int i = 0; i < cache.used; ++i)
+        if (cache.key[i] == k) {
+            *map = cache.map[i];
+            return AG_OK;
+        }
     EncodeTiledFn fn = encode_fn2();
     AG_REQUIRE(fn != nullptr, AG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
     cuuint64_t dims[2] = {inner, outer};
@@ -539,6 +523,9 @@ static int make_tmap2(CUtensorMap *map, const void *base, uint64_t inner, uint64
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     AG_REQUIRE(r == CUDA_SUCCESS, AG_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)",
                (int)r);
+    const int slot = cache.used < TmapCache::N ? cache.used++ : (cache.next++ % TmapCache::N);
+    cache.key[slot] = k;
+    cache.map[slot] = *map;
     return AG_OK;
 }
 
@@ -546,8 +533,12 @@ template <bool A_MN, bool B_MN>
 static int launch_pair(ag_device *dev, const CUtensorMap &ta, const CUtensorMap &tb,
                        const CUtensorMap &tb_tail, const pair::Params &p) {
     auto kernel = pair::gemm_bf16_tc2_kernel<A_MN, B_MN>;
-    AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     pair::SMEM_BYTES));
+    static bool attr_done[64] = {};   // per GPU: the attribute belongs to the GPU's copy of the kernel
+    if (dev->ordinal >= 64 || !attr_done[dev->ordinal]) {
+        AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         pair::SMEM_BYTES));
+        if (dev->ordinal < 64) attr_done[dev->ordinal] = true;
+    }
     const int tiles = (int)(ceil_div(p.M, pair::TILE_M) * ceil_div(p.N, pair::TILE_N));
     int pairs = dev->sm_count / 2;
     if (tiles < pairs) pairs = tiles;
@@ -566,7 +557,7 @@ bool gemm_bf16_pair_enabled() {
 
 int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_bfloat16 *a,
                    int64_t rsa, int64_t csa, const __nv_bfloat16 *b, int64_t rsb, int64_t csb,
-                   float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc) {
+                   float beta, __nv_bfloat16 *c, int64_t rsc, int64_t csc, const Epilogue *epi) {
     (void)csc;
     const bool a_mn = !(csa == 1 && rsa % 8 == 0 && rsa >= k);
     const bool b_mn = !(rsb == 1 && csb % 8 == 0 && csb >= k);
@@ -592,6 +583,16 @@ int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_
     p.beta = beta;
     p.C = c;
     p.status = dev->status_dev;
+    p.bias = epi ? epi->bias : nullptr;
+    p.relu = epi && epi->relu ? 1 : 0;
+    {
+        static const int group_m = []() {
+            const char *e = getenv("AG_TC2_GROUP_M");
+            const int v = e ? atoi(e) : 8;
+            return v < 1 ? 1 : v;
+        }();
+        p.group_m = group_m;
+    }
     {
         const int tiles = (int)(ceil_div(m, pair::TILE_M) * ceil_div(n, pair::TILE_N));
         int pairs = dev->sm_count / 2;

@@ -112,3 +112,35 @@ def test_bf16_split_k(dev, layout, shape):
     dev.gemm(0.5, *_views(dev.tensor(ai, torch.bfloat16), dev.tensor(bi, torch.bfloat16), layout), 2.0, cd)
     want = oracle.round_bf16((0.5 * (aiv @ biv) + 2.0 * c0).astype(np.float32))
     assert np.array_equal(cd.float().cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("shape", [(512, 1024, 512), (192, 640, 384), (256, 25088, 512), (300, 520, 264)])
+@pytest.mark.parametrize("with_bias,relu", [(True, True), (True, False), (False, True)])
+def test_dense_epilogue_fused_on_the_tensor_cores(dev, shape, with_bias, relu):
+    """Dense::forward (+ Relu) on the tcgen05 kernels: bias add and ReLU happen in the kernel's
+    epilogue (paired-CTA kernel, one-CTA kernel, and the reduction of the k-split kernel).  The
+    result equals the product, the bias add and the ReLU as three separate calls bit for bit, and
+    an f64 reference within the bf16 tolerance."""
+    import autograph_b200 as ag
+    bs, ins, outs = shape
+    rng = np.random.default_rng(bs + ins)
+    x = oracle.round_bf16(rng.uniform(-1, 1, (bs, ins)).astype(np.float32))
+    w = oracle.round_bf16(rng.uniform(-1, 1, (ins, outs)).astype(np.float32) / np.sqrt(ins))
+    b = oracle.round_bf16(rng.uniform(-1, 1, outs).astype(np.float32))
+    xd, wd, bd = (dev.tensor(a, torch.bfloat16) for a in (x, w, b))
+    launches = ag.kernel_launch_count()
+    y = dev.dense_forward(xd, wd, bias=bd if with_bias else None, relu=relu)
+    fused_launches = ag.kernel_launch_count() - launches
+    sep = dev.dot(xd, wd)
+    if with_bias:
+        sep = dev.bias_add(sep, bd)
+    if relu:
+        sep = dev.relu(sep, inplace=True)
+    assert torch.equal(y, sep)
+    assert fused_launches <= 2          # the product (and, when k is split, its reduction)
+    ref = x.astype(np.float64) @ w.astype(np.float64)
+    if with_bias:
+        ref = ref + b
+    if relu:
+        ref = np.maximum(ref, 0)
+    assert np.abs(y.float().cpu().numpy() - ref).max() <= 1e-2 * max(np.abs(ref).max(), 1e-6)
