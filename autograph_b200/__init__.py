@@ -102,6 +102,52 @@ class Device:
         torch = _torch()
         return torch.empty(shape, dtype=dtype, device=self.torch_device)
 
+    # Memory-safety net for tests (compute-sanitizer's place where it cannot run): with guards
+    # on, every output an operator allocates sits between two red zones and is pre-filled
+    # with a poison pattern (all bits set: a NaN no kernel produces).  check_guards() then
+    # reports an operator that wrote outside its output (a damaged red zone) or left part of
+    # it unwritten (surviving poison).  Off by default; costs two fills per output.
+    GUARD_BYTES = 512
+
+    def set_guards(self, on: bool):
+        self._guarded = [] if on else None
+
+    def _out(self, shape, dtype):
+        """Output buffer of an operator (guarded and poisoned when guards are on)."""
+        torch = _torch()
+        if getattr(self, "_guarded", None) is None:
+            return torch.empty(shape, dtype=dtype, device=self.torch_device)
+        import weakref
+        n = 1
+        for d in shape:
+            n *= int(d)
+        es = torch.empty((), dtype=dtype).element_size()
+        pad = self.GUARD_BYTES // es
+        raw = torch.empty((n + 2 * pad,), dtype=dtype, device=self.torch_device)
+        raw.view(torch.uint8).fill_(0xFF)
+        out = raw[pad:pad + n].view(tuple(shape))
+        self._guarded.append((weakref.ref(out), raw, pad, n, tuple(shape)))
+        return out
+
+    def check_guards(self):
+        """Raises AssertionError for the first damaged red zone or unwritten output among the
+        outputs that are still alive; forgets all of them."""
+        torch = _torch()
+        entries, self._guarded = (self._guarded or []), ([] if self._guarded is not None else None)
+        torch.cuda.current_stream(self.index).synchronize()
+        self.stream.synchronize()
+        for ref, raw, pad, n, shape in entries:
+            bytes_ = raw.view(torch.uint8)
+            es = raw.element_size()
+            lo, hi = bytes_[:pad * es], bytes_[(pad + n) * es:]
+            assert bool((lo == 0xFF).all()) and bool((hi == 0xFF).all()), \
+                f"an operator wrote outside its output of shape {shape}"
+            if ref() is None or n == 0:
+                continue   # the caller dropped it (e.g. the call raised): nothing to say
+            body = bytes_[pad * es:(pad + n) * es].view(-1, es)
+            unwritten = int((body == 0xFF).all(dim=1).sum())
+            assert unwritten == 0, f"{unwritten} of {n} elements of an output of shape {shape} were never written"
+
     def tensor(self, array, dtype=None):
         """Host numpy array -> device tensor (≙ Tensor::from(array).into_device(device))."""
         torch = _torch()
@@ -147,7 +193,7 @@ class Device:
                           f"Can not dot tensors of different types {a.dtype} != {b.dtype}!")
         if a.shape[1] != b.shape[0]:
             raise AgError(_capi.AG_ERR_SHAPE, f"a_cols != b_rows, {a.shape[1]} != {b.shape[0]}")
-        c = self.empty((a.shape[0], b.shape[1]), a.dtype)
+        c = self._out((a.shape[0], b.shape[1]), a.dtype)
         return self.gemm(1.0, a, b, 0.0, c)
 
     # -- convolution -----------------------------------------------------------
@@ -166,7 +212,7 @@ class Device:
             raise AgError(_capi.AG_ERR_SHAPE, "input channels do not match the weight")
         o = _conv_options((fh, fw), padding, stride, dilation)
         oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
-        y = self.empty((bs, oc, oh, ow), x.dtype)
+        y = self._out((bs, oc, oh, ow), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_conv2_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
                                            ic, ih, iw, _ptr(w.contiguous()), oc, _ptr(bias),
@@ -184,7 +230,7 @@ class Device:
         oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
         if oh < pool[0] or ow < pool[1]:
             raise AgError(_capi.AG_ERR_SHAPE, "pool window does not fit the convolution output")
-        y = self.empty((bs, oc, (oh - pool[0]) // pool[0] + 1, (ow - pool[1]) // pool[1] + 1),
+        y = self._out((bs, oc, (oh - pool[0]) // pool[0] + 1, (ow - pool[1]) // pool[1] + 1),
                        x.dtype)
         self._sync_in()
         _capi.check(lib().ag_conv2_relu_max_pool2_forward(
@@ -203,8 +249,8 @@ class Device:
             raise AgError(_capi.AG_ERR_SHAPE, "input channels do not match the weight")
         o = _conv_options((fh, fw), padding, stride, dilation)
         oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
-        pre = self.empty((bs, oc, oh, ow), x.dtype)
-        y = self.empty((bs, oc, oh // 2, ow // 2), x.dtype)
+        pre = self._out((bs, oc, oh, ow), x.dtype)
+        y = self._out((bs, oc, oh // 2, ow // 2), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_conv2_relu_max_pool2_forward_keep(
             self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw,
@@ -217,7 +263,7 @@ class Device:
             raise AgError(_capi.AG_ERR_DTYPE, "Can not dot tensors of different types")
         if x.shape[1] != w.shape[0]:
             raise AgError(_capi.AG_ERR_SHAPE, f"a_cols != b_rows, {x.shape[1]} != {w.shape[0]}")
-        y = self.empty((x.shape[0], w.shape[1]), x.dtype)
+        y = self._out((x.shape[0], w.shape[1]), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_dense_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()),
                                            x.shape[0], x.shape[1], _ptr(w.contiguous()),
@@ -233,7 +279,7 @@ class Device:
         ws = (ctypes.c_void_p * n)(*[w.contiguous().data_ptr() for w in weights])
         bs = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
         rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
-        y = self.empty((x.shape[0], weights[-1].shape[1]), x.dtype)
+        y = self._out((x.shape[0], weights[-1].shape[1]), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_dense_chain_forward(self._h, _dtype_code(x.dtype),
                                                  _ptr(x.contiguous()), x.shape[0], n, dims, ws, bs,
@@ -250,8 +296,8 @@ class Device:
         ws = (ctypes.c_void_p * n)(*[w.contiguous().data_ptr() for w in weights])
         bs = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
         rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
-        pre = [self.empty((x.shape[0], w.shape[1]), x.dtype) for w in weights]
-        act = [self.empty((x.shape[0], w.shape[1]), x.dtype) if r else None
+        pre = [self._out((x.shape[0], w.shape[1]), x.dtype) for w in weights]
+        act = [self._out((x.shape[0], w.shape[1]), x.dtype) if r else None
                for w, r in zip(weights, relus)]
         pp = (ctypes.c_void_p * n)(*[_ptr(t) for t in pre])
         ap = (ctypes.c_void_p * n)(*[(_ptr(t) if t is not None else None) for t in act])
@@ -269,10 +315,10 @@ class Device:
         dt = x.dtype
         dims = (ctypes.c_int64 * (n + 1))(x.shape[1], *[w.shape[1] for w in weights])
         ins = [x.contiguous()] + [(act[i] if relus[i] else pre[i]) for i in range(n - 1)]
-        g = [self.empty(p.shape, dt) for p in pre]
-        dw = [self.empty(w.shape, dt) for w in weights]
-        db = [self.empty((w.shape[1],), dt) if b else None for w, b in zip(weights, has_bias)]
-        dx = self.empty(x.shape, dt) if want_dx else None
+        g = [self._out(p.shape, dt) for p in pre]
+        dw = [self._out(w.shape, dt) for w in weights]
+        db = [self._out((w.shape[1],), dt) if b else None for w, b in zip(weights, has_bias)]
+        dx = self._out(x.shape, dt) if want_dx else None
         dy = dy.contiguous()
         if not relus[-1]:
             g[-1] = dy
@@ -318,7 +364,7 @@ class Device:
 
     def scaled_cast_u8(self, x_u8, alpha, dtype):
         """≙ Tensor::scaled_cast for u8 input: alpha * x in `dtype` (f32 or bf16)."""
-        y = self.empty(tuple(x_u8.shape), dtype)
+        y = self._out(tuple(x_u8.shape), dtype)
         self._sync_in()
         _capi.check(lib().ag_scaled_cast_u8(self._h, _dtype_code(dtype), ctypes.c_float(alpha),
                                             _ptr(x_u8.contiguous()), _ptr(y), x_u8.numel()))
@@ -351,7 +397,7 @@ class Device:
         bp = (ctypes.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
         rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
         out_dtype = weights[0].dtype
-        y = self.empty((bs, weights[-1].shape[1]), out_dtype)
+        y = self._out((bs, weights[-1].shape[1]), out_dtype)
         self._sync_in()
         if u8_alpha is not None:
             _capi.check(lib().ag_conv_dense_chain_forward_u8(
@@ -369,7 +415,7 @@ class Device:
         bs = dy.shape[0]
         ih, iw = input_hw
         o = _conv_options((fh, fw), padding, stride, dilation)
-        dx = self.empty((bs, ic, ih, iw), dy.dtype)
+        dx = self._out((bs, ic, ih, iw), dy.dtype)
         self._sync_in()
         _capi.check(lib().ag_conv2_backward_input(self._h, _dtype_code(dy.dtype),
                                                   _ptr(w.contiguous()), oc, ic,
@@ -383,7 +429,7 @@ class Device:
         oc = dy.shape[1]
         o = _conv_options(filter, padding, stride, dilation)
         if dw is None:
-            dw = self.empty((oc, ic, filter[0], filter[1]), x.dtype)
+            dw = self._out((oc, ic, filter[0], filter[1]), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_conv2_backward_weight(self._h, _dtype_code(x.dtype),
                                                    _ptr(x.contiguous()), bs, ic, ih, iw,
@@ -395,7 +441,7 @@ class Device:
         bs, c, ih, iw = x.shape
         o = _conv_options(filter, padding, stride, dilation)
         oh, ow = self.conv2_output_shape(ih, iw, filter, padding, stride, dilation)
-        y = self.empty((bs * oh * ow, c * filter[0] * filter[1]), x.dtype)
+        y = self._out((bs * oh * ow, c * filter[0] * filter[1]), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_im2col_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
                                           c, ih, iw, ctypes.byref(o), _ptr(y)))
@@ -409,7 +455,7 @@ class Device:
         oh = (gh - 1) * stride[0] + dilation[0] * (fh - 1) + 1 - 2 * padding[0]
         ow = (gw - 1) * stride[1] + dilation[1] * (fw - 1) + 1 - 2 * padding[1]
         o = _conv_options(filter, padding, stride, dilation)
-        y = self.empty((bs, c, oh, ow), x.dtype)
+        y = self._out((bs, c, oh, ow), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_col2im_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
                                           c, gh, gw, ctypes.byref(o), _ptr(y)))
@@ -422,7 +468,7 @@ class Device:
         if ih < size[0] or iw < size[1]:
             raise AgError(_capi.AG_ERR_SHAPE, "pool window does not fit input")
         oh, ow = (ih - size[0]) // strides[0] + 1, (iw - size[1]) // strides[1] + 1
-        y = self.empty((bs, c, oh, ow), x.dtype)
+        y = self._out((bs, c, oh, ow), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_max_pool2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, c,
                                        ih, iw, size[0], size[1], strides[0], strides[1], _ptr(y)))
@@ -443,7 +489,7 @@ class Device:
         """The same result in one pass: x is read, the gradient written (no clone)."""
         strides = strides or size
         x = x.contiguous()
-        dx = self.empty(x.shape, x.dtype)
+        dx = self._out(x.shape, x.dtype)
         bs, c, ih, iw = x.shape
         self._sync_in()
         _capi.check(lib().ag_max_pool2_backward_from_input(
@@ -455,7 +501,7 @@ class Device:
         """max_pool2(relu(x)) with a 2x2 window and stride in one pass (even planes)."""
         x = x.contiguous()
         bs, c, ih, iw = x.shape
-        y = self.empty((bs, c, ih // 2, iw // 2), x.dtype)
+        y = self._out((bs, c, ih // 2, iw // 2), x.dtype)
         self._sync_in()
         _capi.check(lib().ag_relu_max_pool2_forward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
                                                     ih, iw, _ptr(y)))
@@ -465,7 +511,7 @@ class Device:
         """Gradient of relu_max_pool2 at x: the pool's and the Relu's backward in one pass."""
         x = x.contiguous()
         bs, c, ih, iw = x.shape
-        dx = self.empty(x.shape, x.dtype)
+        dx = self._out(x.shape, x.dtype)
         self._sync_in()
         _capi.check(lib().ag_relu_max_pool2_backward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
                                                      ih, iw, _ptr(dy.contiguous()), _ptr(dx)))
@@ -473,14 +519,14 @@ class Device:
 
     def relu(self, x, inplace=False):
         x = x.contiguous()
-        y = x if inplace else self.empty(x.shape, x.dtype)
+        y = x if inplace else self._out(x.shape, x.dtype)
         self._sync_in()
         _capi.check(lib().ag_relu(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(y), x.numel()))
         return y
 
     def relu_backward(self, x, dy, inplace=False):
         x, dy = x.contiguous(), dy.contiguous()
-        dx = dy if inplace else self.empty(dy.shape, dy.dtype)
+        dx = dy if inplace else self._out(dy.shape, dy.dtype)
         self._sync_in()
         _capi.check(lib().ag_relu_backward(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(dy),
                                            _ptr(dx), x.numel()))
@@ -507,7 +553,7 @@ class Device:
         rows, cols = dy.shape[0], dy.shape[1]
         inner = dy[0, 0].numel() if dy.dim() > 2 else 1
         if out is None:
-            out = self.empty((cols,), dy.dtype)
+            out = self._out((cols,), dy.dtype)
         self._sync_in()
         _capi.check(lib().ag_bias_grad(self._h, _dtype_code(dy.dtype), _ptr(dy.contiguous()), rows,
                                        cols, inner, ctypes.c_float(beta), _ptr(out)))
@@ -531,7 +577,7 @@ class Device:
         torch = _torch()
         x, t = x.contiguous(), t.contiguous()
         loss = torch.empty((1,), dtype=torch.float32, device=self.torch_device)
-        dx = self.empty(x.shape, x.dtype)
+        dx = self._out(x.shape, x.dtype)
         self._sync_in()
         _capi.check(lib().ag_cross_entropy_loss_device_grad(
             self._h, _dtype_code(x.dtype), _dtype_code(t.dtype), _ptr(x), _ptr(t), x.shape[0],
@@ -540,7 +586,7 @@ class Device:
 
     def cross_entropy_loss_backward(self, x, t, dy=1.0):
         bs, classes = x.shape
-        dx = self.empty(x.shape, x.dtype)
+        dx = self._out(x.shape, x.dtype)
         self._sync_in()
         _capi.check(lib().ag_cross_entropy_loss_backward(
             self._h, _dtype_code(x.dtype), _dtype_code(t.dtype), _ptr(x.contiguous()), _ptr(t), bs,

@@ -60,6 +60,7 @@ _SIGNATURES = {
     "ag_device_create_on_stream": (c_int, [c_int, _P, POINTER(_P)]),
     "ag_device_destroy": (c_int, [_P]),
     "ag_device_wait": (c_int, [_P]),
+    "ag_debug_expiring_wait": (c_int, [_P, c_uint64]),
     "ag_device_stream": (_P, [_P]),
     "ag_device_ordinal": (c_int, [_P]),
     "ag_alloc": (c_int, [_P, c_size_t, POINTER(_P)]),

@@ -47,6 +47,7 @@ __device__ __forceinline__ void stamp(int i) {
 }  // namespace ag
 
 #include "conv_chain_lenet.cuh"
+#include "conv_chain_lenet_tc.cuh"
 
 namespace ag {
 namespace conv_chain {
@@ -251,6 +252,41 @@ int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t 
         const char *e = getenv("AG_CHAIN_GENERIC");
         return e && e[0] == '1';
     }();
+    if constexpr (sizeof(T) == 2) {
+        // bf16: the variant whose second convolution runs on the tensor cores (AG_LENET_TC=0
+        // keeps the FFMA kernel below)
+        static const bool tc_off = [] {
+            const char *e = getenv("AG_LENET_TC");
+            return e && e[0] == '0';
+        }();
+        lenet_tc::Plan tp;
+        size_t tsmem = 0;
+        if (!generic_only && !tc_off &&
+            (tsmem = lenet_tc::make_plan(&tp, bs, ic, ih, iw, n_conv, stages, n_dense, layers)) != 0) {
+            int64_t group = ceil_div(bs, (int64_t)dev->sm_count);
+            tp.group = (int)(group < 1 ? 1 : (group > lenet::kGroup ? lenet::kGroup : group));
+            tp.status = dev->status_dev;
+            static bool attr_set = false;
+            if (!attr_set) {
+                AG_CUDA_TRY(cudaFuncSetAttribute(lenet_tc::lenet_chain_tc_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem));
+                attr_set = true;
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)ceil_div(bs, (int64_t)tp.group));
+            cfg.blockDim = dim3(lenet::kThreads);
+            cfg.dynamicSmemBytes = tsmem;
+            cfg.stream = dev->stream;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr.val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            AG_CUDA_TRY(cudaLaunchKernelEx(&cfg, lenet_tc::lenet_chain_tc_kernel, x, x8, alpha, y, tp));
+            AG_CHECK_LAUNCH();
+            return AG_OK;
+        }
+    }
     if (!generic_only) {
         lenet::Plan lp;
         const ag_dtype dtype = sizeof(T) == 4 ? AG_F32 : AG_BF16;

@@ -3,6 +3,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace ag {
 
@@ -94,11 +95,35 @@ static int device_init(int ordinal, cudaStream_t stream, bool owns, ag_device **
     return AG_OK;
 }
 
+// One CTA waits on an mbarrier that nothing will ever complete, with the library's bounded wait
+// and the caller's limit: the wait runs out, the kernel records status 199 and returns.
+__global__ void expiring_wait_kernel(uint64_t limit_ns, int *status) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        tc::mbar_init(tc::smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!tc::mbar_wait_for(tc::smem_u32(&bar), 0, &abort_flag, limit_ns) && threadIdx.x == 0)
+        atomicCAS(status, 0, 199);
+}
+
 }  // namespace ag
 
 using namespace ag;
 
 extern "C" {
+
+int ag_debug_expiring_wait(ag_device *dev, uint64_t limit_ns) {
+    AG_ENTER(dev);
+    AG_REQUIRE(limit_ns > 0 && limit_ns <= 1000000000ull, AG_ERR_INVALID,
+               "limit must be between 1 ns and 1 s");
+    expiring_wait_kernel<<<1, 64, 0, dev->stream>>>(limit_ns, dev->status_dev);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
 
 const char *ag_last_error(void) { return error_buffer(); }
 

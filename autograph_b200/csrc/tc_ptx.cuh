@@ -48,9 +48,10 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// Bounded wait: gives up after about two seconds, or as soon as another thread
-// of the CTA has given up, and reports through *abort_flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+// Bounded wait: gives up after limit_ns, or as soon as another thread of the CTA has given
+// up, and reports through *abort_flag.
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                              uint64_t limit_ns) {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -58,12 +59,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > 2000000000ull) {
+            if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+
+// The limit every kernel of the library uses: about two seconds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return mbar_wait_for(bar, parity, abort_flag, 2000000000ull);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,

@@ -145,6 +145,25 @@ def cpu_forward_rate(seconds: float, min_steps: int = 2):
     return n * BATCH / dt, oracle.num_threads(), n, dt
 
 
+def cpu_train_rate(seconds: float):
+    """Steps/s of the oracle's LeNet5 training step at batch 100 (benchmark configuration 2:
+    forward, cross-entropy, backward through the reference's host direct-convolution kernels,
+    plain SGD) on all host cores."""
+    import oracle
+    from oracle import models
+    oracle.use_all_cores()
+    P = models.init_params(models.LENET5, 2000)
+    x = np.random.default_rng(4000).uniform(0, 1, (100, 1, 28, 28)).astype(np.float32)
+    t = np.random.default_rng(4001).integers(0, 10, 100).astype(np.uint32)
+    models.train_step(models.LENET5, P, x, t, 0.01)
+    n, t0 = 0, time.perf_counter()
+    while n < 3 or time.perf_counter() - t0 < seconds:
+        models.train_step(models.LENET5, P, x, t, 0.01)
+        n += 1
+    dt = time.perf_counter() - t0
+    return n / dt, oracle.num_threads(), n, dt
+
+
 def run_reference(args):
     """The reference arm: the reference's host path, restated in C (oracle/), timed on the
     host cores with all threads; K steps of one 1000-image forward each."""
@@ -375,6 +394,15 @@ def run_gpu(args):
         rate, cores, n, dt = cpu_forward_rate(secs)
         line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"{n} forward passes of 1000 images in {dt:.1f} s"}
+        if not args.quick:
+            try:
+                sps, cores, n, dt = cpu_train_rate(4.0)
+                line["cpu_baseline_train"] = {
+                    "value": sps * 100, "unit": "img/s", "ms_per_step": 1e3 / sps, "cores": cores,
+                    "kind": "port", "sample": f"{n} training steps of 100 images in {dt:.1f} s "
+                                              "(benchmark configuration 2)"}
+            except Exception as exc:
+                line["cpu_baseline_train_error"] = repr(exc)
         print(json.dumps(line), flush=True)
 
 

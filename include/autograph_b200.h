@@ -85,6 +85,13 @@ AG_API int ag_device_create_on_stream(int ordinal, void *cuda_stream, ag_device 
 AG_API int ag_device_destroy(ag_device *dev);
 /* ≙ device.wait() (src/tensor/linalg.rs:549). Also reports a device-side timeout flag. */
 AG_API int ag_device_wait(ag_device *dev);
+/* Diagnostic with no counterpart in the reference: exercises the bounded device-side wait
+ * that every tcgen05 kernel of the library uses.  Enqueues one small kernel that waits on a
+ * barrier nothing will ever complete; after limit_ns (at most one second) the wait gives up,
+ * the kernel records status 199 and returns, and the next ag_device_wait reports
+ * AG_ERR_DEVICE_TIMEOUT.  The GPU and the device object stay usable.  For tests of a host's
+ * error handling. */
+AG_API int ag_debug_expiring_wait(ag_device *dev, uint64_t limit_ns);
 AG_API void *ag_device_stream(ag_device *dev);
 AG_API int ag_device_ordinal(ag_device *dev);
 

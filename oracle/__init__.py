@@ -204,6 +204,34 @@ def conv2_direct_f32(x, w):
     return y
 
 
+def conv2_direct_backward_input_f32(w, dy, input_hw):
+    """Input gradient of the reference's host f32 direct convolution, in its accumulation
+    order (conv_direct.rs:948-1156); default options."""
+    w = np.ascontiguousarray(w, np.float32)
+    dy = np.ascontiguousarray(dy, np.float32)
+    oc, ic, fh, fw = w.shape
+    bs = dy.shape[0]
+    ih, iw = input_hw
+    dx = np.empty((bs, ic, ih, iw), np.float32)
+    lib().orc_conv2_direct_backward_input_f32(_f(w), _f(dy), _f(dx), bs, ic, ih, iw, oc, fh, fw)
+    return dx
+
+
+def conv2_direct_backward_weight_f32(x, dy, filter, threads=None):
+    """Weight gradient of the reference's host f32 direct convolution (conv_direct.rs:1158-1346).
+    The reference's summation order depends on its thread count: `threads` stands for
+    rayon::current_num_threads() (default: the oracle's own thread count)."""
+    x = np.ascontiguousarray(x, np.float32)
+    dy = np.ascontiguousarray(dy, np.float32)
+    bs, ic, ih, iw = x.shape
+    oc = dy.shape[1]
+    fh, fw = filter
+    dw = np.empty((oc, ic, fh, fw), np.float32)
+    lib().orc_conv2_direct_backward_weight_f32(_f(x), _f(dy), _f(dw), bs, ic, ih, iw, oc, fh, fw,
+                                               int(threads or num_threads()))
+    return dw
+
+
 def im2col_conv2(x, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
     x = np.ascontiguousarray(x, np.float32)
     bs, c, ih, iw = x.shape

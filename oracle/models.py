@@ -16,7 +16,8 @@ from __future__ import annotations
 import numpy as np
 
 from . import (accuracy, bias_add, bias_grad, conv2_backward_input_naive,
-               conv2_backward_weight_naive, conv2_direct_f32, conv2_naive, cross_entropy_loss,
+               conv2_backward_weight_naive, conv2_direct_backward_input_f32,
+               conv2_direct_backward_weight_f32, conv2_direct_f32, conv2_naive, cross_entropy_loss,
                cross_entropy_loss_backward, gemm, gemm_f32_fast, max_pool2, max_pool2_backward,
                relu, relu_backward, round_bf16, sgd_update, sgd_update_momentum)
 
@@ -151,10 +152,17 @@ def backward(spec, params, saved, dlogits, *, bf16=False, acc="f32"):
         elif kind == "conv":
             w = params[pidx[li]]
             if layer[4]:
-                grads[pidx[li] + 1] = bias_grad(g, acc64=a64, bf16=bf16)
-            grads[pidx[li]] = conv2_backward_weight_naive(xin, g, layer[3], acc64=a64, bf16=bf16)
+                deliver(pidx[li] + 1, bias_grad(g, acc64=a64, bf16=bf16))
+            host_f32 = acc == "f32" and not bf16   # the reference's host path: direct kernels
+            if host_f32:
+                deliver(pidx[li], conv2_direct_backward_weight_f32(xin, g, layer[3]))
+            else:
+                deliver(pidx[li], conv2_backward_weight_naive(xin, g, layer[3], acc64=a64, bf16=bf16))
             if li > 0:  # the network input has no node: no dX for the first layer
-                g = conv2_backward_input_naive(w, g, xin.shape[2:], acc64=a64, bf16=bf16)
+                if host_f32:
+                    g = conv2_direct_backward_input_f32(w, g, xin.shape[2:])
+                else:
+                    g = conv2_backward_input_naive(w, g, xin.shape[2:], acc64=a64, bf16=bf16)
         elif kind == "relu":
             g = relu_backward(xin, g)
         elif kind == "pool":

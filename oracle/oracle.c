@@ -312,6 +312,94 @@ ORC_API void orc_conv2_direct_f32(const float *x, const float *w, float *y, int 
     }
 }
 
+/* Gradient with respect to the input of the host direct convolution, restating the
+ * accumulation order of conv2_direct_backward_input_host_f32
+ * (src/learn/neural_network/layer/conv_direct.rs:948-1156): images are spread over threads
+ * (:1083-1089); the gradient starts at zero (:1140) and every element is updated in place, in
+ * this loop order: block of 8 output channels (:1098-1103), row of dy (:1106), tile of TWY
+ * positions along that row (:1108-1126; TWY = min(7, ow), or min(8, ow) when there is a single
+ * input channel, :1134-1139), filter row, filter column (:975-976), channel inside the block
+ * (:982), with fused multiply-add (:987).  Default options only. */
+ORC_API void orc_conv2_direct_backward_input_f32(const float *w, const float *dy, float *dx, int bs,
+                                                 int ic, int ih, int iw, int oc, int fh, int fw) {
+    int oh = ih - fh + 1, ow = iw - fw + 1;
+    int twy_max = (ic == 1) ? 8 : 7;
+    if (twy_max > ow) twy_max = ow;
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < bs; ++b) {
+        float *dxb = dx + (size_t)b * ic * ih * iw;
+        const float *dyb = dy + (size_t)b * oc * oh * ow;
+        for (size_t i = 0; i < (size_t)ic * ih * iw; ++i) dxb[i] = 0.f;
+        for (int ci = 0; ci < ic; ++ci) {   /* the lanes of an input-channel block are independent */
+            float *dxc = dxb + (size_t)ci * ih * iw;
+            for (int cyb = 0; cyb < oc; cyb += 8)
+                for (int hy = 0; hy < oh; ++hy)
+                    for (int wy0 = 0; wy0 < ow; wy0 += twy_max) {
+                        int twy = ow - wy0 < twy_max ? ow - wy0 : twy_max;
+                        for (int fi = 0; fi < fh; ++fi)
+                            for (int fj = 0; fj < fw; ++fj)
+                                for (int co = cyb; co < oc && co < cyb + 8; ++co) {
+                                    float wv = w[((size_t)(co * ic + ci) * fh + fi) * fw + fj];
+                                    const float *g = dyb + ((size_t)co * oh + hy) * ow + wy0;
+                                    float *d = dxc + (size_t)(hy + fi) * iw + wy0 + fj;
+                                    for (int t = 0; t < twy; ++t) d[t] = fmaf(g[t], wv, d[t]);
+                                }
+                    }
+        }
+    }
+}
+
+/* Gradient with respect to the weight, restating conv2_direct_backward_weight_host_f32
+ * (conv_direct.rs:1158-1346): the batch is dealt out to threads_bs partial sums, image bid
+ * going to partial bid % threads_bs (:1194-1201); a partial adds its images in ascending order
+ * and, per image, walks the rows and columns of dy with fused multiply-add (:1241-1264); the
+ * partials are then added in order, starting from zero (:1318-1343; a single partial is the
+ * result as it is, :1313-1317).  threads_bs = min(threads / threads_c, bs) with threads_c =
+ * min(threads, groups of output-channel blocks x input-channel blocks) (:1286-1291): the result
+ * depends on the number of threads the reference runs with, which is a parameter here. */
+ORC_API void orc_conv2_direct_backward_weight_f32(const float *x, const float *dy, float *dw, int bs,
+                                                  int ic, int ih, int iw, int oc, int fh, int fw,
+                                                  int threads) {
+    int oh = ih - fh + 1, ow = iw - fw + 1;
+    int oc_blocks = (oc + 7) / 8, ic_blocks = ic == 1 ? 1 : (ic + 7) / 8;
+    int tby = oc_blocks < 4 ? oc_blocks : 4;
+    int oc_groups = (oc_blocks + tby - 1) / tby;
+    if (threads < 1) threads = 1;
+    int threads_c = threads < oc_groups * ic_blocks ? threads : oc_groups * ic_blocks;
+    int threads_bs = threads / threads_c;
+    if (threads_bs > bs) threads_bs = bs;
+    if (threads_bs < 1) threads_bs = 1;
+    size_t plane = (size_t)oc * ic * fh * fw;
+    float *tmp = (float *)calloc((size_t)threads_bs * plane, sizeof(float));
+#pragma omp parallel for schedule(static)
+    for (int tb = 0; tb < threads_bs; ++tb) {
+        float *acc = tmp + (size_t)tb * plane;
+        for (int b = tb; b < bs; b += threads_bs)
+            for (int co = 0; co < oc; ++co)
+                for (int ci = 0; ci < ic; ++ci)
+                    for (int fi = 0; fi < fh; ++fi)
+                        for (int fj = 0; fj < fw; ++fj) {
+                            float a = acc[((size_t)(co * ic + ci) * fh + fi) * fw + fj];
+                            for (int hy = 0; hy < oh; ++hy) {
+                                const float *xr = x + (((size_t)b * ic + ci) * ih + hy + fi) * iw + fj;
+                                const float *g = dy + (((size_t)b * oc + co) * oh + hy) * ow;
+                                for (int wy = 0; wy < ow; ++wy) a = fmaf(xr[wy], g[wy], a);
+                            }
+                            acc[((size_t)(co * ic + ci) * fh + fi) * fw + fj] = a;
+                        }
+    }
+    if (threads_bs == 1) {
+        for (size_t i = 0; i < plane; ++i) dw[i] = tmp[i];
+    } else {
+        for (size_t i = 0; i < plane; ++i) {
+            float s = 0.f;
+            for (int tb = 0; tb < threads_bs; ++tb) s += tmp[(size_t)tb * plane + i];
+            dw[i] = s;
+        }
+    }
+    free(tmp);
+}
+
 /* im2col, host version (src/tensor/ops.rs:741-813): rows (b,oh,ow), columns
  * (c,fi,fj), zero outside the image. */
 ORC_API void orc_im2col_conv2(const float *x, float *y, int bs, int c, int ih, int iw,

@@ -43,11 +43,24 @@ def dev():
 @pytest.fixture(autouse=True)
 def _library_stream_is_current(request):
     """torch ops of a GPU test (comparisons, copies) must run on the stream the library's kernels
-    run on; a Device created elsewhere in the session would have made its own stream current."""
-    if "dev" in request.fixturenames:
-        import torch
-        torch.cuda.set_stream(request.getfixturevalue("dev").stream)
+    run on; a Device created elsewhere in the session would have made its own stream current.
+
+    Every GPU test also runs with the device's memory-safety net on (compute-sanitizer cannot be
+    used on these machines): each operator output is allocated between two red zones and
+    pre-filled with a poison pattern, and after the test every red zone must be intact and no
+    output that is still alive may hold surviving poison (Device.set_guards / check_guards)."""
+    if "dev" not in request.fixturenames:
+        yield
+        return
+    import torch
+    d = request.getfixturevalue("dev")
+    torch.cuda.set_stream(d.stream)
+    d.set_guards(True)
     yield
+    try:
+        d.check_guards()
+    finally:
+        d.set_guards(False)
 
 
 def cycle(lo, hi, n):

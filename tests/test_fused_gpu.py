@@ -197,6 +197,51 @@ def test_conv_dense_chain_equals_separate_calls(dev, dtype, net):
     assert torch.equal(fused, v)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bs", [1, 6, 7, 8, 50, 1000, 1037])
+def test_lenet5_geometry_kernel(dev, dtype, bs):
+    """LeNet5 itself (no convolution bias) takes the kernels specialised for its geometry.  f32:
+    the bits of the layer-by-layer calls.  bf16: the second convolution runs on the tensor
+    cores, whose f32 sums are added in another order, so values agree within bf16 rounding (one
+    rounding step at a layer boundary moves a logit by about 2^-8 of its size) and with an f64
+    reference within the bf16 tolerance."""
+    rng = np.random.default_rng(500 + bs)
+    bf = dtype == torch.bfloat16
+    xn = _prep(rng.uniform(0, 1, (bs, 1, 28, 28)), dtype)
+    shapes = [(6, 1, 5, 5), (16, 6, 5, 5), (256, 120), (120, 84), (84, 10)]
+    fan = [25, 150, 256, 120, 84]
+    P = [_prep(rng.uniform(-1, 1, s) * np.sqrt(2.0 / f), dtype) for s, f in zip(shapes, fan)]
+    bias = _prep(rng.uniform(-0.1, 0.1, 10), dtype)
+    x = dev.tensor(xn, dtype)
+    Pd = [dev.tensor(p, dtype) for p in P]
+    bd = dev.tensor(bias, dtype)
+    stages = [(Pd[0], None, True, (2, 2)), (Pd[1], None, True, (2, 2))]
+    fused = dev.conv_dense_chain_forward(x, stages, Pd[2:], [None, None, bd], [True, True, False])
+    v = x
+    for wt, b, relu, pool in stages:
+        v = dev.max_pool2(dev.conv2_forward(v, wt, bias=b, relu=relu), pool)
+    v = v.reshape(bs, -1)
+    for wd, b, r in zip(Pd[2:], [None, None, bd], [True, True, False]):
+        v = dev.dense_forward(v, wd, bias=b, relu=r)
+    if not bf:
+        assert torch.equal(fused, v)
+    else:
+        scale = v.float().abs().max().item()
+        assert (fused.float() - v.float()).abs().max().item() <= 2e-2 * scale
+    # f64 reference of the same network
+    h = torch.tensor(xn, dtype=torch.float64)
+    rd = (lambda t: t.to(torch.bfloat16).to(torch.float64)) if bf else (lambda t: t.to(torch.float32).to(torch.float64))
+    import torch.nn.functional as F
+    for w in P[:2]:
+        h = F.max_pool2d(torch.relu(rd(F.conv2d(h, torch.tensor(w, dtype=torch.float64)))), 2)
+    h = h.reshape(bs, -1)
+    h = torch.relu(rd(h @ torch.tensor(P[2], dtype=torch.float64)))
+    h = torch.relu(rd(h @ torch.tensor(P[3], dtype=torch.float64)))
+    h = rd(rd(h @ torch.tensor(P[4], dtype=torch.float64)) + torch.tensor(bias, dtype=torch.float64))
+    tol = 1e-2 if bf else 1e-5 * np.sqrt(256)
+    assert (fused.double().cpu() - h).abs().max().item() <= tol * h.abs().max().item()
+
+
 def test_conv_dense_chain_unsupported(dev):
     """Networks the one-kernel form does not take are refused, not approximated."""
     import autograph_b200 as ag

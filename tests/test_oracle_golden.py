@@ -51,7 +51,13 @@ def test_conv_forward_backward(golden):
         assert np.array_equal(dx, golden[c["name"] + "_dx"]), c
         assert np.array_equal(dw, golden[c["name"] + "_dw"]), c
         if c["padding"] == [0, 0] and c["stride"] == [1, 1] and c["dilation"] == [1, 1]:
+            # the reference's host production path (conv_direct.rs), all three directions
             assert np.array_equal(oracle.conv2_direct_f32(x, w), y_true), c
+            assert np.array_equal(oracle.conv2_direct_backward_input_f32(w, dy, (ih, iw)),
+                                  golden[c["name"] + "_dx"]), c
+            for threads in (1, 3, 16):
+                assert np.array_equal(oracle.conv2_direct_backward_weight_f32(x, dy, f, threads=threads),
+                                      golden[c["name"] + "_dw"]), (c, threads)
 
 
 def fingerprint(a):
@@ -228,3 +234,21 @@ def test_lenet5_against_torch_f64():
         assert np.abs(g - ref).max() <= 2e-5 * np.abs(ref).max() + 1e-8
     for w, g, nw in zip(P, grads, new_p):
         assert np.array_equal(nw, np.float32(-0.01) * g + w)
+
+
+def test_direct_conv_backward_matches_the_plain_loops():
+    """conv_direct.rs backward kernels restated (order of accumulation: blocks of 8 output
+    channels, tiles of 7 positions, per-thread partial sums) against the naive loops on random
+    data: same values up to f32 rounding, for LeNet5's two layers and a ragged shape."""
+    rng = np.random.default_rng(12)
+    for bs, ic, ih, iw, oc, f in [(9, 1, 28, 28, 6, 5), (5, 6, 12, 12, 16, 5), (4, 11, 9, 10, 19, 3)]:
+        x = rng.standard_normal((bs, ic, ih, iw)).astype(np.float32)
+        w = rng.standard_normal((oc, ic, f, f)).astype(np.float32)
+        dy = rng.standard_normal((bs, oc, ih - f + 1, iw - f + 1)).astype(np.float32)
+        dx64 = oracle.conv2_backward_input_naive(w, dy, (ih, iw), acc64=True)
+        dw64 = oracle.conv2_backward_weight_naive(x, dy, (f, f), acc64=True)
+        dx = oracle.conv2_direct_backward_input_f32(w, dy, (ih, iw))
+        assert np.abs(dx - dx64).max() <= 1e-5 * np.sqrt(oc * f * f) * np.abs(dx64).max()
+        for threads in (1, 4, 16):
+            dw = oracle.conv2_direct_backward_weight_f32(x, dy, (f, f), threads=threads)
+            assert np.abs(dw - dw64).max() <= 1e-5 * np.sqrt(bs * ih * iw) * np.abs(dw64).max()
