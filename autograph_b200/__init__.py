@@ -111,6 +111,7 @@ class Device:
 
     def set_guards(self, on: bool):
         self._guarded = [] if on else None
+        self._guard_mark = 0
 
     def _out(self, shape, dtype):
         """Output buffer of an operator (guarded and poisoned when guards are on)."""
@@ -129,11 +130,22 @@ class Device:
         self._guarded.append((weakref.ref(out), raw, pad, n, tuple(shape)))
         return out
 
+    def _check(self, status):
+        """_capi.check for operator calls: outputs allocated for a call that failed are not
+        expected to have been written."""
+        guarded = getattr(self, "_guarded", None)
+        if status != _capi.AG_OK and guarded is not None:
+            del guarded[getattr(self, "_guard_mark", 0):]
+        _capi.check(status)
+        if guarded is not None:
+            self._guard_mark = len(guarded)
+
     def check_guards(self):
         """Raises AssertionError for the first damaged red zone or unwritten output among the
         outputs that are still alive; forgets all of them."""
         torch = _torch()
         entries, self._guarded = (self._guarded or []), ([] if self._guarded is not None else None)
+        self._guard_mark = 0
         torch.cuda.current_stream(self.index).synchronize()
         self.stream.synchronize()
         for ref, raw, pad, n, shape in entries:
@@ -180,7 +192,7 @@ class Device:
         if n != n2:
             raise AgError(_capi.AG_ERR_SHAPE, f"b_cols != c_rows, {n} != {n2}")
         self._sync_in()
-        _capi.check(lib().ag_gemm(
+        self._check(lib().ag_gemm(
             self._h, _dtype_code(a.dtype), m, k, n, ctypes.c_float(alpha),
             _ptr(a), 0, a.stride(0), a.stride(1), _ptr(b), 0, b.stride(0), b.stride(1),
             ctypes.c_float(beta), _ptr(c), 0, c.stride(0), c.stride(1)))
@@ -200,7 +212,7 @@ class Device:
     def conv2_output_shape(self, ih, iw, filter, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
         oh, ow = ctypes.c_int64(), ctypes.c_int64()
         o = _conv_options(filter, padding, stride, dilation)
-        _capi.check(lib().ag_conv2_output_shape(ih, iw, ctypes.byref(o), ctypes.byref(oh),
+        self._check(lib().ag_conv2_output_shape(ih, iw, ctypes.byref(o), ctypes.byref(oh),
                                                 ctypes.byref(ow)))
         return oh.value, ow.value
 
@@ -214,7 +226,7 @@ class Device:
         oh, ow = self.conv2_output_shape(ih, iw, (fh, fw), padding, stride, dilation)
         y = self._out((bs, oc, oh, ow), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_conv2_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
+        self._check(lib().ag_conv2_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
                                            ic, ih, iw, _ptr(w.contiguous()), oc, _ptr(bias),
                                            ctypes.byref(o), int(relu), _ptr(y)))
         return y
@@ -233,7 +245,7 @@ class Device:
         y = self._out((bs, oc, (oh - pool[0]) // pool[0] + 1, (ow - pool[1]) // pool[1] + 1),
                        x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_conv2_relu_max_pool2_forward(
+        self._check(lib().ag_conv2_relu_max_pool2_forward(
             self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw,
             _ptr(w.contiguous()), oc, _ptr(bias), ctypes.byref(o), int(relu), pool[0], pool[1],
             _ptr(y)))
@@ -252,7 +264,7 @@ class Device:
         pre = self._out((bs, oc, oh, ow), x.dtype)
         y = self._out((bs, oc, oh // 2, ow // 2), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_conv2_relu_max_pool2_forward_keep(
+        self._check(lib().ag_conv2_relu_max_pool2_forward_keep(
             self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw,
             _ptr(w.contiguous()), oc, _ptr(bias), ctypes.byref(o), _ptr(pre), _ptr(y)))
         return pre, y
@@ -265,7 +277,7 @@ class Device:
             raise AgError(_capi.AG_ERR_SHAPE, f"a_cols != b_rows, {x.shape[1]} != {w.shape[0]}")
         y = self._out((x.shape[0], w.shape[1]), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_dense_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()),
+        self._check(lib().ag_dense_forward(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()),
                                            x.shape[0], x.shape[1], _ptr(w.contiguous()),
                                            w.shape[1], _ptr(bias), int(relu), _ptr(y)))
         return y
@@ -281,7 +293,7 @@ class Device:
         rl = (ctypes.c_int32 * n)(*[int(r) for r in relus])
         y = self._out((x.shape[0], weights[-1].shape[1]), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_dense_chain_forward(self._h, _dtype_code(x.dtype),
+        self._check(lib().ag_dense_chain_forward(self._h, _dtype_code(x.dtype),
                                                  _ptr(x.contiguous()), x.shape[0], n, dims, ws, bs,
                                                  rl, _ptr(y)))
         return y
@@ -302,7 +314,7 @@ class Device:
         pp = (ctypes.c_void_p * n)(*[_ptr(t) for t in pre])
         ap = (ctypes.c_void_p * n)(*[(_ptr(t) if t is not None else None) for t in act])
         self._sync_in()
-        _capi.check(lib().ag_dense_chain_forward_keep(self._h, _dtype_code(x.dtype),
+        self._check(lib().ag_dense_chain_forward_keep(self._h, _dtype_code(x.dtype),
                                                       _ptr(x.contiguous()), x.shape[0], n, dims, ws,
                                                       bs, rl, pp, ap))
         return pre, act
@@ -324,7 +336,7 @@ class Device:
             g[-1] = dy
         arr = lambda ts: (ctypes.c_void_p * n)(*[(_ptr(t) if t is not None else None) for t in ts])
         self._sync_in()
-        _capi.check(lib().ag_dense_chain_backward(
+        self._check(lib().ag_dense_chain_backward(
             self._h, _dtype_code(dt), x.shape[0], n, dims, arr(ins),
             arr([w.contiguous() for w in weights]), arr([pre[i] if relus[i] else None for i in range(n)]),
             _ptr(dy), arr([g[i] if (i < n - 1 or relus[i]) else None for i in range(n)]),
@@ -366,7 +378,7 @@ class Device:
         """≙ Tensor::scaled_cast for u8 input: alpha * x in `dtype` (f32 or bf16)."""
         y = self._out(tuple(x_u8.shape), dtype)
         self._sync_in()
-        _capi.check(lib().ag_scaled_cast_u8(self._h, _dtype_code(dtype), ctypes.c_float(alpha),
+        self._check(lib().ag_scaled_cast_u8(self._h, _dtype_code(dtype), ctypes.c_float(alpha),
                                             _ptr(x_u8.contiguous()), _ptr(y), x_u8.numel()))
         return y
 
@@ -400,11 +412,11 @@ class Device:
         y = self._out((bs, weights[-1].shape[1]), out_dtype)
         self._sync_in()
         if u8_alpha is not None:
-            _capi.check(lib().ag_conv_dense_chain_forward_u8(
+            self._check(lib().ag_conv_dense_chain_forward_u8(
                 self._h, _dtype_code(out_dtype), _ptr(x.contiguous()), ctypes.c_float(u8_alpha), bs,
                 ic, ih, iw, len(convs), stages, n, dims, ws, bp, rl, _ptr(y)))
         else:
-            _capi.check(lib().ag_conv_dense_chain_forward(
+            self._check(lib().ag_conv_dense_chain_forward(
                 self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, ic, ih, iw, len(convs),
                 stages, n, dims, ws, bp, rl, _ptr(y)))
         return y
@@ -417,7 +429,7 @@ class Device:
         o = _conv_options((fh, fw), padding, stride, dilation)
         dx = self._out((bs, ic, ih, iw), dy.dtype)
         self._sync_in()
-        _capi.check(lib().ag_conv2_backward_input(self._h, _dtype_code(dy.dtype),
+        self._check(lib().ag_conv2_backward_input(self._h, _dtype_code(dy.dtype),
                                                   _ptr(w.contiguous()), oc, ic,
                                                   _ptr(dy.contiguous()), bs, ih, iw,
                                                   ctypes.byref(o), _ptr(dx)))
@@ -431,7 +443,7 @@ class Device:
         if dw is None:
             dw = self._out((oc, ic, filter[0], filter[1]), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_conv2_backward_weight(self._h, _dtype_code(x.dtype),
+        self._check(lib().ag_conv2_backward_weight(self._h, _dtype_code(x.dtype),
                                                    _ptr(x.contiguous()), bs, ic, ih, iw,
                                                    _ptr(dy.contiguous()), oc, ctypes.byref(o),
                                                    ctypes.c_float(beta), _ptr(dw)))
@@ -443,7 +455,7 @@ class Device:
         oh, ow = self.conv2_output_shape(ih, iw, filter, padding, stride, dilation)
         y = self._out((bs * oh * ow, c * filter[0] * filter[1]), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_im2col_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
+        self._check(lib().ag_im2col_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
                                           c, ih, iw, ctypes.byref(o), _ptr(y)))
         return y
 
@@ -457,7 +469,7 @@ class Device:
         o = _conv_options(filter, padding, stride, dilation)
         y = self._out((bs, c, oh, ow), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_col2im_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
+        self._check(lib().ag_col2im_conv2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs,
                                           c, gh, gw, ctypes.byref(o), _ptr(y)))
         return y
 
@@ -470,7 +482,7 @@ class Device:
         oh, ow = (ih - size[0]) // strides[0] + 1, (iw - size[1]) // strides[1] + 1
         y = self._out((bs, c, oh, ow), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_max_pool2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, c,
+        self._check(lib().ag_max_pool2(self._h, _dtype_code(x.dtype), _ptr(x.contiguous()), bs, c,
                                        ih, iw, size[0], size[1], strides[0], strides[1], _ptr(y)))
         return y
 
@@ -480,7 +492,7 @@ class Device:
         dx = x.contiguous().clone()
         bs, c, ih, iw = dx.shape
         self._sync_in()
-        _capi.check(lib().ag_max_pool2_backward(self._h, _dtype_code(dx.dtype), _ptr(dx), bs, c, ih,
+        self._check(lib().ag_max_pool2_backward(self._h, _dtype_code(dx.dtype), _ptr(dx), bs, c, ih,
                                                 iw, size[0], size[1], strides[0], strides[1],
                                                 _ptr(dy.contiguous())))
         return dx
@@ -492,7 +504,7 @@ class Device:
         dx = self._out(x.shape, x.dtype)
         bs, c, ih, iw = x.shape
         self._sync_in()
-        _capi.check(lib().ag_max_pool2_backward_from_input(
+        self._check(lib().ag_max_pool2_backward_from_input(
             self._h, _dtype_code(x.dtype), _ptr(x), bs, c, ih, iw, size[0], size[1], strides[0],
             strides[1], _ptr(dy.contiguous()), _ptr(dx)))
         return dx
@@ -503,7 +515,7 @@ class Device:
         bs, c, ih, iw = x.shape
         y = self._out((bs, c, ih // 2, iw // 2), x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_relu_max_pool2_forward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
+        self._check(lib().ag_relu_max_pool2_forward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
                                                     ih, iw, _ptr(y)))
         return y
 
@@ -513,7 +525,7 @@ class Device:
         bs, c, ih, iw = x.shape
         dx = self._out(x.shape, x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_relu_max_pool2_backward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
+        self._check(lib().ag_relu_max_pool2_backward(self._h, _dtype_code(x.dtype), _ptr(x), bs, c,
                                                      ih, iw, _ptr(dy.contiguous()), _ptr(dx)))
         return dx
 
@@ -521,14 +533,14 @@ class Device:
         x = x.contiguous()
         y = x if inplace else self._out(x.shape, x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_relu(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(y), x.numel()))
+        self._check(lib().ag_relu(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(y), x.numel()))
         return y
 
     def relu_backward(self, x, dy, inplace=False):
         x, dy = x.contiguous(), dy.contiguous()
         dx = dy if inplace else self._out(dy.shape, dy.dtype)
         self._sync_in()
-        _capi.check(lib().ag_relu_backward(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(dy),
+        self._check(lib().ag_relu_backward(self._h, _dtype_code(x.dtype), _ptr(x), _ptr(dy),
                                            _ptr(dx), x.numel()))
         return dx
 
@@ -537,7 +549,7 @@ class Device:
         """≙ ``y.scaled_add(alpha, &x)`` (in place on y)."""
         assert y.is_contiguous() and x.is_contiguous() and x.shape == y.shape
         self._sync_in()
-        _capi.check(lib().ag_scaled_add(self._h, _dtype_code(y.dtype), ctypes.c_float(alpha),
+        self._check(lib().ag_scaled_add(self._h, _dtype_code(y.dtype), ctypes.c_float(alpha),
                                         _ptr(x), _ptr(y), y.numel()))
         return y
 
@@ -545,7 +557,7 @@ class Device:
         rows, cols = y.shape[0], y.shape[1]
         inner = y[0, 0].numel() if y.dim() > 2 else 1
         self._sync_in()
-        _capi.check(lib().ag_bias_add(self._h, _dtype_code(y.dtype), _ptr(y), _ptr(bias), rows,
+        self._check(lib().ag_bias_add(self._h, _dtype_code(y.dtype), _ptr(y), _ptr(bias), rows,
                                       cols, inner))
         return y
 
@@ -555,7 +567,7 @@ class Device:
         if out is None:
             out = self._out((cols,), dy.dtype)
         self._sync_in()
-        _capi.check(lib().ag_bias_grad(self._h, _dtype_code(dy.dtype), _ptr(dy.contiguous()), rows,
+        self._check(lib().ag_bias_grad(self._h, _dtype_code(dy.dtype), _ptr(dy.contiguous()), rows,
                                        cols, inner, ctypes.c_float(beta), _ptr(out)))
         return out
 
@@ -567,7 +579,7 @@ class Device:
                                               f"[{t.shape[0]}]")
         loss = ctypes.c_float()
         self._sync_in()
-        _capi.check(lib().ag_cross_entropy_loss(self._h, _dtype_code(x.dtype), _dtype_code(t.dtype),
+        self._check(lib().ag_cross_entropy_loss(self._h, _dtype_code(x.dtype), _dtype_code(t.dtype),
                                                 _ptr(x.contiguous()), _ptr(t), bs, classes,
                                                 ctypes.byref(loss)))
         return loss.value
@@ -579,7 +591,7 @@ class Device:
         loss = torch.empty((1,), dtype=torch.float32, device=self.torch_device)
         dx = self._out(x.shape, x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_cross_entropy_loss_device_grad(
+        self._check(lib().ag_cross_entropy_loss_device_grad(
             self._h, _dtype_code(x.dtype), _dtype_code(t.dtype), _ptr(x), _ptr(t), x.shape[0],
             x.shape[1], _ptr(loss), ctypes.c_float(dy), _ptr(dx)))
         return loss, dx
@@ -588,7 +600,7 @@ class Device:
         bs, classes = x.shape
         dx = self._out(x.shape, x.dtype)
         self._sync_in()
-        _capi.check(lib().ag_cross_entropy_loss_backward(
+        self._check(lib().ag_cross_entropy_loss_backward(
             self._h, _dtype_code(x.dtype), _dtype_code(t.dtype), _ptr(x.contiguous()), _ptr(t), bs,
             classes, ctypes.c_float(dy), _ptr(dx)))
         return dx
@@ -597,7 +609,7 @@ class Device:
         bs, classes = x.shape
         out = ctypes.c_uint64()
         self._sync_in()
-        _capi.check(lib().ag_accuracy(self._h, _dtype_code(x.dtype), _dtype_code(t.dtype),
+        self._check(lib().ag_accuracy(self._h, _dtype_code(x.dtype), _dtype_code(t.dtype),
                                       _ptr(x.contiguous()), _ptr(t), bs, classes,
                                       ctypes.byref(out)))
         return out.value
@@ -605,13 +617,13 @@ class Device:
     # -- optimizer ----------------------------------------------------------------------
     def sgd_update(self, w, g, lr):
         self._sync_in()
-        _capi.check(lib().ag_sgd_update(self._h, _dtype_code(w.dtype), _ptr(w), _ptr(g), w.numel(),
+        self._check(lib().ag_sgd_update(self._h, _dtype_code(w.dtype), _ptr(w), _ptr(g), w.numel(),
                                         ctypes.c_float(lr)))
         return w
 
     def sgd_update_momentum(self, w, g, v, lr, momentum):
         self._sync_in()
-        _capi.check(lib().ag_sgd_update_momentum(self._h, _dtype_code(w.dtype), _ptr(w), _ptr(g),
+        self._check(lib().ag_sgd_update_momentum(self._h, _dtype_code(w.dtype), _ptr(w), _ptr(g),
                                                  _ptr(v), w.numel(), ctypes.c_float(lr),
                                                  ctypes.c_float(momentum)))
         return w, v

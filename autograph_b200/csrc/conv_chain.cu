@@ -242,6 +242,43 @@ static int launch(ag_device *dev, const T *x, T *y, const Plan &pl, size_t smem)
     return AG_OK;
 }
 
+// Launches the kernel specialised for LeNet5's geometry, or returns AG_ERR_UNSUPPORTED when
+// the network is not of that geometry.  flat_out != null: stop after the flatten.
+template <class T>
+static int launch_lenet(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t bs,
+                        int64_t ic, int64_t ih, int64_t iw, int n_conv, const ag_conv_stage *stages,
+                        int n_dense, const dense_small::ChainLayer *layers, T *y, T *flat_out) {
+    lenet::Plan lp;
+    const ag_dtype dtype = sizeof(T) == 4 ? AG_F32 : AG_BF16;
+    const size_t lsmem =
+        lenet::make_plan(&lp, dtype, bs, ic, ih, iw, n_conv, stages, n_dense, layers, flat_out);
+    if (lsmem == 0) return AG_ERR_UNSUPPORTED;
+    int64_t group = ceil_div(bs, (int64_t)dev->sm_count);
+    lp.group = (int)(group < 1 ? 1 : (group > lenet::kGroup ? lenet::kGroup : group));
+    lp.status = dev->status_dev;
+    auto kernel = lenet::lenet_chain_kernel<T>;
+    static bool attr_set[64] = {};
+    if (dev->ordinal >= 64 || !attr_set[dev->ordinal]) {
+        AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lsmem));
+        if (dev->ordinal < 64) attr_set[dev->ordinal] = true;
+    }
+    // launched so that it may overlap the tail of a preceding launch of the same kernel
+    // (the kernel itself waits for its predecessor before it reads or writes memory)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(bs, (int64_t)lp.group));
+    cfg.blockDim = dim3(lenet::kThreads);
+    cfg.dynamicSmemBytes = lsmem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    AG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, x, x8, alpha, y, lp));
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
 template <class T>
 int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t bs, int64_t ic,
             int64_t ih, int64_t iw, int n_conv, const ag_conv_stage *stages, int n_dense,
@@ -252,13 +289,46 @@ int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t 
         const char *e = getenv("AG_CHAIN_GENERIC");
         return e && e[0] == '1';
     }();
+    // Large batches of a LeNet5-geometry network: the kernel stops after the flatten and the
+    // dense layers run as products over the whole batch (ag_dense_forward: tensor cores for
+    // bf16, the SIMT tile engine for f32).  Inside the one-kernel form every CTA streams all
+    // dense weights for its 7 images; over the whole batch they are read once per 128-row tile.
+    static const int64_t split_batch = [] {
+        const char *e = getenv("AG_CHAIN_SPLIT_BATCH");
+        return e ? (int64_t)atoll(e) : (int64_t)8192;
+    }();
+    if (!generic_only && split_batch > 0 && bs >= split_batch) {
+        const ag_dtype dtype = sizeof(T) == 4 ? AG_F32 : AG_BF16;
+        int64_t widest = layers[0].inputs;
+        for (int i = 0; i < n_dense; ++i) widest = layers[i].outputs > widest ? layers[i].outputs : widest;
+        void *scratch = nullptr;
+        // [bs, 256] after the flatten, then two buffers the layers alternate between
+        const size_t plane = (size_t)bs * (size_t)widest * sizeof(T);
+        AG_TRY(staging(dev, 3 * plane, &scratch));
+        T *flat = reinterpret_cast<T *>(scratch);
+        const int r = launch_lenet<T>(dev, x, x8, alpha, bs, ic, ih, iw, n_conv, stages, n_dense, layers, y, flat);
+        if (r == AG_OK) {
+            const T *in = flat;
+            for (int i = 0; i < n_dense; ++i) {
+                T *out = i + 1 == n_dense
+                             ? y
+                             : reinterpret_cast<T *>(reinterpret_cast<char *>(scratch) + (1 + (i & 1)) * plane);
+                AG_TRY(ag_dense_forward(dev, dtype, in, bs, layers[i].inputs, layers[i].w, layers[i].outputs,
+                                        layers[i].bias, layers[i].relu, out));
+                in = out;
+            }
+            return AG_OK;
+        }
+        if (r != AG_ERR_UNSUPPORTED) return r;
+    }
     if constexpr (sizeof(T) == 2) {
-        // bf16: the variant whose second convolution runs on the tensor cores (AG_LENET_TC=0
-        // keeps the FFMA kernel below)
-        static const bool tc_off = [] {
-            const char *e = getenv("AG_LENET_TC");
-            return e && e[0] == '0';
-        }();
+        // bf16: the variant whose second convolution runs on the tensor cores.  Off unless
+        // AG_LENET_TC=1 (read per call): correct, but slower than the FFMA kernel below, because
+        // a tcgen05.mma with N = 16, K = 16 occupies the tensor core about as long as one with
+        // N = 256, and this layer cannot fill more of it (measured: 10 us against 7 us for the
+        // phase, 29.7 against 22.7 us for the step).
+        const char *tc_env = getenv("AG_LENET_TC");
+        const bool tc_off = !(tc_env && tc_env[0] == '1');
         lenet_tc::Plan tp;
         size_t tsmem = 0;
         if (!generic_only && !tc_off &&
@@ -288,36 +358,9 @@ int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t 
         }
     }
     if (!generic_only) {
-        lenet::Plan lp;
-        const ag_dtype dtype = sizeof(T) == 4 ? AG_F32 : AG_BF16;
-        const size_t lsmem = lenet::make_plan(&lp, dtype, bs, ic, ih, iw, n_conv, stages, n_dense, layers);
-        if (lsmem != 0) {
-            int64_t group = ceil_div(bs, (int64_t)dev->sm_count);
-            lp.group = (int)(group < 1 ? 1 : (group > lenet::kGroup ? lenet::kGroup : group));
-            lp.status = dev->status_dev;
-            auto kernel = lenet::lenet_chain_kernel<T>;
-            static bool attr_set[2] = {false, false};
-            if (!attr_set[sizeof(T) == 4]) {
-                AG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)lsmem));
-                attr_set[sizeof(T) == 4] = true;
-            }
-            // launched so that it may overlap the tail of a preceding launch of the same kernel
-            // (the kernel itself waits for its predecessor before it reads or writes memory)
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned)ceil_div(bs, (int64_t)lp.group));
-            cfg.blockDim = dim3(lenet::kThreads);
-            cfg.dynamicSmemBytes = lsmem;
-            cfg.stream = dev->stream;
-            cudaLaunchAttribute attr;
-            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr.val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = &attr;
-            cfg.numAttrs = 1;
-            AG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, x, x8, alpha, y, lp));
-            AG_CHECK_LAUNCH();
-            return AG_OK;
-        }
+        const int r = launch_lenet<T>(dev, x, x8, alpha, bs, ic, ih, iw, n_conv, stages, n_dense, layers, y,
+                                      nullptr);
+        if (r != AG_ERR_UNSUPPORTED) return r;
     }
     Plan pl;
     pl.x8 = x8;

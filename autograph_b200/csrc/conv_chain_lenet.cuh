@@ -66,6 +66,9 @@ struct Plan {
     int early;                        // layers [0, early) are copied at kernel start, the rest after conv2
     int w1_off, w2_off, xa_off, xb_off, red_off, bar_off;
     int *status;
+    // When set, the kernel stops after the flatten and writes the activations [bs, 256] here
+    // (the dense layers then run as separate products over the whole batch).
+    void *flat_out;
 };
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -310,6 +313,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncthreads();
     AG_STAMP(3);
+    if (pl.flat_out != nullptr) {
+        T *flat = reinterpret_cast<T *>(pl.flat_out) + (int64_t)b0 * kFlat;
+        for (int i = tid; i < nimg * kFlat; i += kThreads) {
+            const int g = i >> 8, k = i & (kFlat - 1);
+            flat[i] = from_f32<T>(xa[k * ROWS + g]);   // exact: the values are already T's
+        }
+        return;
+    }
 
     // ---- the later dense layers' weights go where the convolutions' buffers were
     if (tid == kThreads - 1 && pl.early < pl.chain.n_layers) {
@@ -363,7 +374,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 // or 0 when the kernel does not take it (the caller then uses the generic kernel).
 inline size_t make_plan(Plan *pl, ag_dtype dtype, int64_t bs, int64_t ic, int64_t ih, int64_t iw,
                         int n_conv, const ag_conv_stage *stages, int n_dense,
-                        const dense_small::ChainLayer *layers) {
+                        const dense_small::ChainLayer *layers, void *flat_out = nullptr) {
+    pl->flat_out = flat_out;
     if (n_conv != 2 || ic != 1 || ih != IH || iw != IW) return 0;
     if (bs <= 0 || bs > (int64_t)kGroup * 0x7fffffff / 8) return 0;
     const int ocs[2] = {C1, C2};
@@ -426,6 +438,7 @@ inline size_t make_plan(Plan *pl, ag_dtype dtype, int64_t bs, int64_t ic, int64_
         pl->w_smem[l] = -1;
         const int64_t bytes = (int64_t)layers[l].inputs * layers[l].outputs * (int64_t)es;
         pl->w_bytes[l] = (int)bytes;
+        if (flat_out != nullptr) continue;   // the dense layers do not run in this kernel
         if (l == 0) {
             if (l0_floats) {
                 pl->w_smem[0] = take(l0_floats);

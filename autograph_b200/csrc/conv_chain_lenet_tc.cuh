@@ -243,16 +243,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (tid == 0) {
         const uint32_t act_addr = tc::smem_u32(s_act), w2b_addr = tc::smem_u32(s_w2b);
         const uint32_t idesc = tc::make_idesc(false, false, 128, 16);
-        for (int t = 0; t < tiles; ++t) {
+        // Tap by tap across the tiles: consecutive MMAs go to different accumulators, so they
+        // pipeline; 25 MMAs into ONE accumulator run one after the other (measured: 13 us
+        // against 2 us for the phase).
 #pragma unroll 1
-            for (int tap = 0; tap < F * F; ++tap) {
-                const int fi = tap / F, fj = tap - fi * F;
+        for (int tap = 0; tap < F * F; ++tap) {
+            const int fi = tap / F, fj = tap - fi * F;
+            const uint64_t b_desc = make_desc_sw32(w2b_addr + (uint32_t)tap * 512);
+            for (int t = 0; t < tiles; ++t) {
                 const uint64_t a_desc = make_desc_sw32(act_addr + (uint32_t)(t * 128 + fi * P1 + fj) * 32);
-                const uint64_t b_desc = make_desc_sw32(w2b_addr + (uint32_t)tap * 512);
                 tc::umma_bf16(tmem + (uint32_t)(t * 16), a_desc, b_desc, idesc, tap > 0 ? 1u : 0u);
             }
-            tc::umma_commit(bar_tile0 + 8 * t);
         }
+        for (int t = 0; t < tiles; ++t) tc::umma_commit(bar_tile0 + 8 * t);
     }
     // epilogue: warp group (t % 4) takes tile t; a thread owns one pixel row of the tile
     {

@@ -197,9 +197,10 @@ def test_conv_dense_chain_equals_separate_calls(dev, dtype, net):
     assert torch.equal(fused, v)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("bs", [1, 6, 7, 8, 50, 1000, 1037])
-def test_lenet5_geometry_kernel(dev, dtype, bs):
+@pytest.mark.parametrize("dtype,tensor_cores", [(torch.float32, False), (torch.bfloat16, False),
+                                                 (torch.bfloat16, True)])
+@pytest.mark.parametrize("bs", [1, 6, 7, 8, 50, 1000, 1037, 9000])
+def test_lenet5_geometry_kernel(dev, dtype, tensor_cores, bs, monkeypatch):
     """LeNet5 itself (no convolution bias) takes the kernels specialised for its geometry.  f32:
     the bits of the layer-by-layer calls.  bf16: the second convolution runs on the tensor
     cores, whose f32 sums are added in another order, so values agree within bf16 rounding (one
@@ -207,6 +208,9 @@ def test_lenet5_geometry_kernel(dev, dtype, bs):
     reference within the bf16 tolerance."""
     rng = np.random.default_rng(500 + bs)
     bf = dtype == torch.bfloat16
+    # AG_LENET_TC=1 (read per call) selects the bf16 kernel whose conv2 is on tcgen05; batch 9000
+    # takes the split form (the kernel stops after the flatten, dense layers over the batch)
+    monkeypatch.setenv("AG_LENET_TC", "1" if tensor_cores else "0")
     xn = _prep(rng.uniform(0, 1, (bs, 1, 28, 28)), dtype)
     shapes = [(6, 1, 5, 5), (16, 6, 5, 5), (256, 120), (120, 84), (84, 10)]
     fan = [25, 150, 256, 120, 84]
@@ -223,7 +227,7 @@ def test_lenet5_geometry_kernel(dev, dtype, bs):
     v = v.reshape(bs, -1)
     for wd, b, r in zip(Pd[2:], [None, None, bd], [True, True, False]):
         v = dev.dense_forward(v, wd, bias=b, relu=r)
-    if not bf:
+    if not tensor_cores:
         assert torch.equal(fused, v)
     else:
         scale = v.float().abs().max().item()

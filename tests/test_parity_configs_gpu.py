@@ -130,9 +130,11 @@ def test_lenet5_inference_65536(dev, dtype):
         # a row may differ only where its two best logits are closer than bf16 can resolve
         assert (margin[disagree] <= 2 ** -7).all()
         assert len(disagree) <= len(rows) // 100
-    # the same images in one launch and in 1000-image launches give the same bits
+    # the same images as a 1000-image batch: that size keeps the dense layers inside the
+    # one-kernel network, this one runs them as products over the whole batch, so the sums are
+    # added in another order
     part = model.forward_device(xd[:1000].contiguous()).float().cpu().numpy()
-    assert np.array_equal(part, logits[:1000])
+    assert _rel(part, logits[:1000]) <= (1e-2 if bf else 1e-6)
     model.close()
 
 
