@@ -486,16 +486,22 @@ class Device:
                                        ih, iw, size[0], size[1], strides[0], strides[1], _ptr(y)))
         return y
 
-    def max_pool2_backward(self, x, dy, size=(2, 2), strides=None):
-        """≙ the MaxPool2 backward edge: clone the input, run max_pool2_backward in place."""
+    def max_pool2_backward_inplace(self, dx, dy, size=(2, 2), strides=None):
+        """The reference's kernel form: dx holds the pool's input on entry and its gradient on
+        return (cells no window covers keep the input's value)."""
         strides = strides or size
-        dx = x.contiguous().clone()
+        if not dx.is_contiguous():
+            raise AgError(_capi.AG_ERR_INVALID, "dx must be contiguous")
         bs, c, ih, iw = dx.shape
         self._sync_in()
         self._check(lib().ag_max_pool2_backward(self._h, _dtype_code(dx.dtype), _ptr(dx), bs, c, ih,
                                                 iw, size[0], size[1], strides[0], strides[1],
                                                 _ptr(dy.contiguous())))
         return dx
+
+    def max_pool2_backward(self, x, dy, size=(2, 2), strides=None):
+        """≙ the MaxPool2 backward edge: clone the input, run max_pool2_backward in place."""
+        return self.max_pool2_backward_inplace(x.contiguous().clone(), dy, size, strides)
 
     def max_pool2_backward_from_input(self, x, dy, size=(2, 2), strides=None):
         """The same result in one pass: x is read, the gradient written (no clone)."""

@@ -514,7 +514,7 @@ def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):
     total_flops = sum(v["alg_flops"] for v in stages.values())
     layered_us = sum(v["us"] for v in stages.values())
     convs = [(P[0], None, True, (2, 2)), (P[1], None, True, (2, 2))]
-    add("whole network (conv_chain_kernel: 2 x conv+relu+pool, flatten, dense 256-128-84-10)",
+    add("whole network (lenet_chain_kernel: 2 x conv+relu+pool, flatten, dense 256-128-84-10)",
         [lambda i=i: dev.conv_dense_chain_forward(xs[i], convs, [P[2], P[3], P[4]],
                                                   [None, None, P[5]], [True, True, False])
          for i in range(32)],
@@ -534,7 +534,7 @@ def lenet5_roofline(torch, ag, dev, model, xs, K, peaks):
             "peak_source": "computed: 148 SMs x 128 lanes x 2 flop x 1.965 GHz (max SM clock)",
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch at batch 1000, from the
             # ncu capture of this kernel
-            "traffic": 3373312 if B == 1000 else None,
+            "traffic": 3405568 if B == 1000 else None,
             "us_per_launch": st["us"], "algorithmic_flops_per_launch": st["alg_flops"],
             "hbm": {"achieved_gbs": st["gbs"], "peak_gbs": peaks["hbm_gbs"],
                     "frac": st["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"],
@@ -697,11 +697,7 @@ def run_probe(args):
             x4 = a[: (n // 4096) * 4096].reshape(-1, 16, 16, 16)
             dy = b[: x4.numel() // 4].reshape(-1, 16, 8, 8)
             dx = x4.clone()
-            h = dev._h
-            def fn(i):
-                ag._capi.check(ag.lib().ag_max_pool2_backward(
-                    h, 0 if dtype == torch.float32 else 1, dx.data_ptr(), x4.shape[0], 16, 16, 16,
-                    2, 2, 2, 2, dy.data_ptr()))
+            fn = lambda i: dev.max_pool2_backward_inplace(dx, dy)
             nbytes = x4.numel() * es * 9 // 4
         elif name == "bias_grad":
             x2 = a[: (n // 512) * 512].reshape(-1, 512)
