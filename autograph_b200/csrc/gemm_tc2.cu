@@ -540,8 +540,9 @@ static int launch_pair(ag_device *dev, const CUtensorMap &ta, const CUtensorMap 
         if (dev->ordinal < 64) attr_done[dev->ordinal] = true;
     }
     const int tiles = (int)(ceil_div(p.M, pair::TILE_M) * ceil_div(p.N, pair::TILE_N));
+    (void)tiles;
     int pairs = dev->sm_count / 2;
-    if (tiles < pairs) pairs = tiles;
+    if (p.num_work < pairs) pairs = p.num_work;
     kernel<<<2 * pairs, pair::NUM_THREADS, pair::SMEM_BYTES, dev->stream>>>(ta, tb, tb_tail, p);
     AG_CHECK_LAUNCH();
     return AG_OK;
@@ -609,6 +610,13 @@ int gemm_bf16_pair(ag_device *dev, int m, int k, int n, float alpha, const __nv_
         p.tail_split = split;
         p.t_full = split > 1 ? tiles - rem : tiles;
         p.num_work = p.t_full + (split > 1 ? split * rem : 0);
+        // Fewer tiles than half the CTA pairs (1024^3: 16 tiles on 74 pairs): every tile is cut
+        // in two along n, which halves the time of the one and only wave.
+        if (tail_enabled && 2 * tiles <= dev->sm_count / 2) {
+            p.tail_split = 2;
+            p.t_full = 0;
+            p.num_work = 2 * tiles;
+        }
     }
     if (a_mn && b_mn) return launch_pair<true, true>(dev, ta, tb, tb_tail, p);
     if (a_mn) return launch_pair<true, false>(dev, ta, tb, tb_tail, p);

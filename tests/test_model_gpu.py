@@ -57,6 +57,30 @@ def test_lenet5_inference_bs1000(dev, dtype):
     model.close()
 
 
+@pytest.mark.parametrize("bs", [1, 3, 7, 8, 100, 1000, 1003, 9000])
+def test_lenet5_host_images_equal_device_images(dev, bs):
+    """f32 images in pinned host memory (read over PCIe by the kernel itself) give the logits of
+    the device-resident pass bit for bit, at every group size (1 to 7 images per CTA, ragged last
+    group, and the split form for large batches), and so does a host view that does not start
+    on a 16-byte boundary."""
+    import autograph_b200 as ag
+    model = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=7)
+    x = torch.from_numpy(np.random.default_rng(bs).uniform(0, 1, (bs, 1, 28, 28)).astype(np.float32))
+    xh = x.pin_memory()
+    out_h = torch.empty((bs, 10), dtype=torch.float32).pin_memory()
+    for _ in range(3):     # eager, captured and replayed forms of the call
+        out_h.fill_(float("nan"))
+        got = model.infer(xh, out_h)
+        ref = model.forward_device(x.to(dev.torch_device)).cpu()
+        assert torch.equal(got, ref)
+    # a host view that does not start on a 16-byte boundary takes the scalar staging loop
+    buf = torch.empty((bs * 784 + 1,), dtype=torch.float32).pin_memory()
+    buf[1:] = x.reshape(-1)
+    got = model.infer(buf[1:].reshape(bs, 1, 28, 28), out_h)
+    assert torch.equal(got, ref)
+    model.close()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("momentum", [None, 0.01])
 def test_lenet5_train_step_bs100(dev, dtype, momentum):
