@@ -494,55 +494,53 @@ static int launch(ag_device *dev, const CUtensorMap &tx, const CUtensorMap &tw, 
     return AG_OK;
 }
 
-// The common path.  `act` is the NCHW activation [bs][c_in][in_h][in_w]; the
-// output is NCHW [bs][c_out][out_h][out_w]; `transposed` selects the filter
-// repacking of the input gradient.
-static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_in, int64_t in_h,
-               int64_t in_w, const __nv_bfloat16 *w, int64_t w_oc, int64_t w_ic, int fh, int fw,
-               int pad_h, int pad_w, bool transposed, int64_t c_out, int64_t out_h, int64_t out_w,
-               const __nv_bfloat16 *bias, bool relu, __nv_bfloat16 *y) {
-    const int64_t cp = round_up(c_in, 64);
-    const int taps = fh * fw;
-    // Resident-filter kernel (conv_tc_halo.cu) when the filter bank and two activation
-    // boxes fit in shared memory; it works on the zero-framed image.
-    int hb_n = 0, hb_rows = 0, hb_stages = 0, hb_smem = 0;
-    const int64_t hp = in_h + 2 * pad_h, wp = in_w + 2 * pad_w;
-    const bool halo = halo_enabled() &&
-                      halo_plan(bs, cp, hp, wp, c_out, fh, fw, &hb_n, &hb_rows, &hb_stages, &hb_smem);
-    const int64_t act_bytes =
-        round_up((halo ? bs * hp * wp : bs * in_h * in_w) * cp * 2, 1024);
-    const int64_t wk_elems = c_out * taps * cp;
-    const int64_t wk_bytes = round_up(wk_elems * 2, 1024);
-    const int64_t ocp = round_up(c_out, 64);
-    const int64_t out_bytes = bs * out_h * out_w * ocp * 2;
-    void *ws = nullptr;
-    AG_TRY(staging(dev, (size_t)(act_bytes + wk_bytes + out_bytes), &ws));
-    __nv_bfloat16 *act_nhwc = (__nv_bfloat16 *)ws;
-    __nv_bfloat16 *wk = (__nv_bfloat16 *)((char *)ws + act_bytes);
-    __nv_bfloat16 *out_nhwc = (__nv_bfloat16 *)((char *)ws + act_bytes + wk_bytes);
+bool nhwc_wants_frame(const NhwcConv &c) {
+    const int64_t cp = round_up(c.c_in, 64);
+    int n = 0, rows = 0, stages = 0, smem = 0;
+    return halo_enabled() && halo_plan(c.bs, cp, c.in_h + 2 * c.pad_h, c.in_w + 2 * c.pad_w, c.c_out,
+                                       c.fh, c.fw, &n, &rows, &stages, &smem);
+}
 
-    if (halo)
-        AG_TRY(to_nhwc_framed(dev, act, bs, c_in, in_h, in_w, cp, pad_h, pad_w, act_nhwc));
-    else
-        AG_TRY(to_nhwc(dev, act, bs, c_in, in_h * in_w, cp, act_nhwc));
+int64_t nhwc_filter_scratch_bytes(const NhwcConv &c) {
+    return round_up(c.c_out * (int64_t)c.fh * c.fw * round_up(c.c_in, 64) * 2, 1024);
+}
+
+int from_nhwc(ag_device *dev, const __nv_bfloat16 *in, int64_t bs, int64_t c, int64_t hw, int64_t cp,
+              __nv_bfloat16 *out) {
+    nhwc_to_nchw_kernel<<<dim3((unsigned)ceil_div(hw, NCHW_PIX), (unsigned)ceil_div(c, 16), (unsigned)bs),
+                          256, 0, dev->stream>>>(in, out, (int)c, (int)hw, (int)cp);
+    AG_CHECK_LAUNCH();
+    return AG_OK;
+}
+
+// The tensor-core correlation on channels-last data.  `act` is [bs][in_h][in_w][cp], or, when
+// `framed` (required when nhwc_wants_frame says so, not allowed otherwise), the same inside a
+// zero frame of pad_h rows / pad_w columns; `out` is [bs][out_h * out_w][ocp]; `wk` is scratch of
+// nhwc_filter_scratch_bytes for the repacked filter bank.
+int correlate_nhwc(ag_device *dev, const NhwcConv &c, const __nv_bfloat16 *act_nhwc, bool framed,
+                   const __nv_bfloat16 *w, int64_t w_oc, int64_t w_ic, const __nv_bfloat16 *bias,
+                   bool relu, __nv_bfloat16 *wk, __nv_bfloat16 *out_nhwc) {
+    const int64_t bs = c.bs, in_h = c.in_h, in_w = c.in_w, c_out = c.c_out, out_h = c.out_h,
+                  out_w = c.out_w;
+    const int fh = c.fh, fw = c.fw, pad_h = c.pad_h, pad_w = c.pad_w;
+    const int64_t cp = round_up(c.c_in, 64);
+    const int taps = fh * fw;
+    const int64_t hp = in_h + 2 * pad_h, wp = in_w + 2 * pad_w;
+    const bool halo = nhwc_wants_frame(c);
+    AG_REQUIRE(halo == framed, AG_ERR_INVALID, "conv: activation frame does not match the kernel's plan");
+    const int64_t wk_elems = c_out * taps * cp;
+    const int64_t ocp = round_up(c_out, 64);
     const unsigned rgrid = (unsigned)ceil_div(wk_elems, 256);
-    if (transposed)
+    if (c.transposed)
         repack_filters_transposed_kernel<<<rgrid, 256, 0, dev->stream>>>(w, wk, (int)w_oc, (int)w_ic,
                                                                          taps, (int)cp);
     else
         repack_filters_kernel<<<rgrid, 256, 0, dev->stream>>>(w, wk, (int)w_oc, (int)w_ic, taps,
                                                               (int)cp);
     AG_CHECK_LAUNCH();
-    const int64_t out_hw = out_h * out_w;
-    if (halo) {
-        AG_TRY(run_halo(dev, act_nhwc, wk, bs, cp, hp, wp, fh, fw, c_out, out_h, out_w, bias, relu,
-                        out_nhwc));
-        nhwc_to_nchw_kernel<<<dim3((unsigned)ceil_div(out_hw, NCHW_PIX),
-                                   (unsigned)ceil_div(c_out, 16), (unsigned)bs),
-                              256, 0, dev->stream>>>(out_nhwc, y, (int)c_out, (int)out_hw, (int)ocp);
-        AG_CHECK_LAUNCH();
-        return AG_OK;
-    }
+    if (halo)
+        return run_halo(dev, act_nhwc, wk, bs, cp, hp, wp, fh, fw, c_out, out_h, out_w, bias, relu,
+                        out_nhwc);
 
     // Pixel tile: the TH x TW rectangle (TH * TW = 128) that wastes the fewest pixels.
     int best_shift = 3;
@@ -593,11 +591,40 @@ static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_i
         AG_TRY(launch<128>(dev, tx, tw, p));
     else
         AG_TRY(launch<256>(dev, tx, tw, p));
-    nhwc_to_nchw_kernel<<<dim3((unsigned)ceil_div(out_hw, NCHW_PIX), (unsigned)ceil_div(c_out, 16),
-                               (unsigned)bs),
-                          256, 0, dev->stream>>>(out_nhwc, y, (int)c_out, (int)out_hw, (int)ocp);
-    AG_CHECK_LAUNCH();
     return AG_OK;
+}
+
+// The common path of the NCHW entry points.  `act` is the NCHW activation [bs][c_in][in_h][in_w];
+// the output is NCHW [bs][c_out][out_h][out_w]; `transposed` selects the filter repacking of the
+// input gradient.
+static int run(ag_device *dev, const __nv_bfloat16 *act, int64_t bs, int64_t c_in, int64_t in_h,
+               int64_t in_w, const __nv_bfloat16 *w, int64_t w_oc, int64_t w_ic, int fh, int fw,
+               int pad_h, int pad_w, bool transposed, int64_t c_out, int64_t out_h, int64_t out_w,
+               const __nv_bfloat16 *bias, bool relu, __nv_bfloat16 *y) {
+    NhwcConv c;
+    c.bs = bs; c.c_in = c_in; c.in_h = in_h; c.in_w = in_w;
+    c.c_out = c_out; c.out_h = out_h; c.out_w = out_w;
+    c.fh = fh; c.fw = fw; c.pad_h = pad_h; c.pad_w = pad_w;
+    c.transposed = transposed;
+    const int64_t cp = round_up(c_in, 64);
+    const int64_t hp = in_h + 2 * pad_h, wp = in_w + 2 * pad_w;
+    const bool halo = nhwc_wants_frame(c);
+    const int64_t act_bytes =
+        round_up((halo ? bs * hp * wp : bs * in_h * in_w) * cp * 2, 1024);
+    const int64_t wk_bytes = nhwc_filter_scratch_bytes(c);
+    const int64_t ocp = round_up(c_out, 64);
+    const int64_t out_bytes = bs * out_h * out_w * ocp * 2;
+    void *ws = nullptr;
+    AG_TRY(staging(dev, (size_t)(act_bytes + wk_bytes + out_bytes), &ws));
+    __nv_bfloat16 *act_nhwc = (__nv_bfloat16 *)ws;
+    __nv_bfloat16 *wk = (__nv_bfloat16 *)((char *)ws + act_bytes);
+    __nv_bfloat16 *out_nhwc = (__nv_bfloat16 *)((char *)ws + act_bytes + wk_bytes);
+    if (halo)
+        AG_TRY(to_nhwc_framed(dev, act, bs, c_in, in_h, in_w, cp, pad_h, pad_w, act_nhwc));
+    else
+        AG_TRY(to_nhwc(dev, act, bs, c_in, in_h * in_w, cp, act_nhwc));
+    AG_TRY(correlate_nhwc(dev, c, act_nhwc, halo, w, w_oc, w_ic, bias, relu, wk, out_nhwc));
+    return from_nhwc(dev, out_nhwc, bs, c_out, out_h * out_w, ocp, y);
 }
 
 int forward(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t ic, int64_t ih, int64_t iw,

@@ -37,6 +37,28 @@ int to_nhwc(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64
 int to_nhwc_framed(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t c, int64_t h,
                    int64_t w, int64_t cp, int pad_h, int pad_w, __nv_bfloat16 *out);
 
+// Channels-last back to NCHW: in [bs][hw][cp] -> out [bs][c][hw].
+int from_nhwc(ag_device *dev, const __nv_bfloat16 *in, int64_t bs, int64_t c, int64_t hw, int64_t cp,
+              __nv_bfloat16 *out);
+
+// A stride-1 correlation on channels-last data, in the kernel's view: c_in channels of
+// in_h x in_w (zero padding pad_h / pad_w) into c_out channels of out_h x out_w with an fh x fw
+// filter.  `transposed` reads the filter bank [w_oc][w_ic][fh][fw] as the input gradient
+// does (channel axes swapped, taps reversed).  Channel counts in memory are rounded up to 64.
+struct NhwcConv {
+    int64_t bs, c_in, in_h, in_w;
+    int64_t c_out, out_h, out_w;
+    int fh, fw, pad_h, pad_w;
+    bool transposed;
+};
+// True when the kernel that takes this problem reads the activation inside a zero frame
+// ([bs][in_h + 2 pad_h][in_w + 2 pad_w][cp]) instead of relying on out-of-range fill.
+bool nhwc_wants_frame(const NhwcConv &c);
+int64_t nhwc_filter_scratch_bytes(const NhwcConv &c);
+int correlate_nhwc(ag_device *dev, const NhwcConv &c, const __nv_bfloat16 *act_nhwc, bool framed,
+                   const __nv_bfloat16 *w, int64_t w_oc, int64_t w_ic, const __nv_bfloat16 *bias,
+                   bool relu, __nv_bfloat16 *wk, __nv_bfloat16 *out_nhwc);
+
 // Resident-filter variant (conv_tc_halo.cu): plan (false when the shape does not fit: more
 // than 128 output channels, a box of more than 256 rows, or too little shared memory) and run
 // on the framed channels-last activation [bs][hp][wp][cp] and the repacked filter bank.
@@ -56,6 +78,14 @@ bool eligible_backward_weight(int64_t bs, int64_t ic, int64_t ih, int64_t iw, in
 int backward_weight(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t ic, int64_t ih,
                     int64_t iw, const __nv_bfloat16 *dy, int64_t oc, const ag_conv2_options *o,
                     float beta, __nv_bfloat16 *dw);
+
+// The same on channels-last data: x [bs][ih][iw][cp]; dy is addressed through its pitches in
+// elements (pixel = ocp channels; dy_row_pitch and dy_image_pitch let it sit inside a frame),
+// all multiples of 8.
+int backward_weight_nhwc(ag_device *dev, const __nv_bfloat16 *x_nhwc, int64_t bs, int64_t ic,
+                         int64_t ih, int64_t iw, const __nv_bfloat16 *dy_nhwc, int64_t dy_row_pitch,
+                         int64_t dy_image_pitch, int64_t oc, const ag_conv2_options *o, float beta,
+                         __nv_bfloat16 *dw);
 
 }  // namespace convtc
 }  // namespace ag

@@ -286,8 +286,6 @@ int backward_weight(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t 
     const int fh = o->filter[0], fw = o->filter[1];
     const int64_t oh = ih + 2 * o->padding[0] - fh + 1, ow = iw + 2 * o->padding[1] - fw + 1;
     const int64_t cp = round_up64(ic, 64), ocp = round_up64(oc, 64);
-    const int nt = (cp % 128 == 0 && fw * 128 <= 512) ? 128 : 64;
-
     const int64_t x_bytes = round_up64(bs * ih * iw * cp * 2, 1024);
     const int64_t dy_bytes = round_up64(bs * oh * ow * ocp * 2, 1024);
     void *st = nullptr;
@@ -296,6 +294,20 @@ int backward_weight(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t 
     __nv_bfloat16 *dyh = (__nv_bfloat16 *)((char *)st + x_bytes);
     AG_TRY(to_nhwc(dev, x, bs, ic, ih * iw, cp, xh));
     AG_TRY(to_nhwc(dev, dy, bs, oc, oh * ow, ocp, dyh));
+    return backward_weight_nhwc(dev, xh, bs, ic, ih, iw, dyh, ow * ocp, oh * ow * ocp, oc, o, beta, dw);
+}
+
+int backward_weight_nhwc(ag_device *dev, const __nv_bfloat16 *xh, int64_t bs, int64_t ic, int64_t ih,
+                         int64_t iw, const __nv_bfloat16 *dyh, int64_t dy_row_pitch,
+                         int64_t dy_image_pitch, int64_t oc, const ag_conv2_options *o, float beta,
+                         __nv_bfloat16 *dw) {
+    const int fh = o->filter[0], fw = o->filter[1];
+    const int64_t oh = ih + 2 * o->padding[0] - fh + 1, ow = iw + 2 * o->padding[1] - fw + 1;
+    const int64_t cp = round_up64(ic, 64), ocp = round_up64(oc, 64);
+    const int nt = (cp % 128 == 0 && fw * 128 <= 512) ? 128 : 64;
+    AG_REQUIRE(dy_row_pitch % 8 == 0 && dy_image_pitch % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(dyh) & 15) == 0 && (reinterpret_cast<uintptr_t>(xh) & 15) == 0,
+               AG_ERR_INVALID, "weight gradient: channels-last operands must keep 16-byte alignment");
 
     WgParams p;
     p.B = (int)bs; p.OH = (int)oh; p.OW = (int)ow;
@@ -345,7 +357,7 @@ int backward_weight(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t 
     CUtensorMap tdy, tx;
     {
         const uint64_t dims[4] = {(uint64_t)ocp, (uint64_t)ow, (uint64_t)oh, (uint64_t)bs};
-        const uint64_t strides[3] = {(uint64_t)ocp, (uint64_t)(ow * ocp), (uint64_t)(oh * ow * ocp)};
+        const uint64_t strides[3] = {(uint64_t)ocp, (uint64_t)dy_row_pitch, (uint64_t)dy_image_pitch};
         const uint32_t box[4] = {64, (uint32_t)p.TW, (uint32_t)th, 1};
         AG_TRY(make_tmap_bf16(&tdy, dyh, 4, dims, strides, box));
     }

@@ -9,6 +9,7 @@
 #include "../comm.cuh"
 #include "../common.cuh"
 #include "nn.hpp"
+#include "conv_stages.hpp"
 
 using namespace autograph;
 
@@ -450,6 +451,36 @@ Variable forward_chain(ag_model *m, Variable v, void *out_ptr = nullptr) {
                 v = conv->forward_fused(m->pool, v, true, pool_ok ? mp->filter : nullptr);
                 i += pool_ok ? 2 : 1;
                 continue;
+            }
+            // Recording gradients in bf16 with shapes the tensor-core kernels take: this and the
+            // following Conv2 -> Relu -> MaxPool2 stages run as one channels-last node.
+            if (conv->records_gradient(v) && relu1 && conv_stages_enabled() && v.value.ndim() == 4 &&
+                v.value.is_standard_layout() && v.value.dtype() == AG_BF16) {
+                auto run = std::make_shared<StageRun>();
+                int64_t c = v.value.dim(1), h = v.value.dim(2), w = v.value.dim(3);
+                size_t j = i;
+                while (j + 2 < n) {
+                    auto *cj = dynamic_cast<Conv2 *>(m->layers[j].get());
+                    auto *rj = dynamic_cast<Relu *>(m->layers[j + 1].get());
+                    auto *pj = dynamic_cast<MaxPool2 *>(m->layers[j + 2].get());
+                    StageDesc d;
+                    const bool needs_dx = j > i || (bool)v.node;
+                    if (!cj || !rj || !pj || !cj->weight.to_variable().node ||
+                        !plan_stage(*cj, *pj, v.value.dtype(), v.value.dim(0), c, h, w, needs_dx, &d))
+                        break;
+                    run->st.push_back(d);
+                    c = d.oc; h = d.ph; w = d.pw;
+                    j += 3;
+                }
+                if (!run->st.empty()) {
+                    run->pool = &m->pool;
+                    run->dev = m->dev;
+                    run->bs = v.value.dim(0);
+                    run->input_grad = (bool)v.node;
+                    v = conv_stage_run_forward(m->pool, run, v);
+                    i = j - 1;
+                    continue;
+                }
             }
             // Recording gradients, Relu and an even 2x2 pool next: one forward call that keeps
             // the convolution's output for the backward edges.
