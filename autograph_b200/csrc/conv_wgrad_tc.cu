@@ -224,18 +224,29 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
 }
 
 // dw[oc][ci][tap] = beta * dw + sum over splits (in order) of partial[s][oc][tap][ci]
+// Block of 32 x 8 threads: 32 consecutive outputs, the split planes dealt round-robin to the 8
+// rows (every load of a warp is 128 contiguous bytes of one plane); the 8 row sums are added in
+// row order, so the result does not depend on scheduling.
 __global__ void wgrad_reduce_kernel(const float *__restrict__ partial, int splits, int64_t m_total,
                                     int taps, int Cp, int OC, int IC, float beta,
                                     __nv_bfloat16 *__restrict__ dw) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (int64_t)OC * taps * IC) return;
-    const int ci = (int)(i % IC);
-    const int tap = (int)((i / IC) % taps);
-    const int oc = (int)(i / ((int64_t)IC * taps));
+    __shared__ float part[8][33];
+    const int64_t i = (int64_t)blockIdx.x * 32 + threadIdx.x;
+    const bool live = i < (int64_t)OC * taps * IC;
+    const int ci = live ? (int)(i % IC) : 0;
+    const int tap = live ? (int)((i / IC) % taps) : 0;
+    const int oc = live ? (int)(i / ((int64_t)IC * taps)) : 0;
     const int64_t plane = m_total * taps * Cp;
     const float *src = partial + ((int64_t)oc * taps + tap) * Cp + ci;
     float s = 0.f;
-    for (int z = 0; z < splits; ++z) s += src[(int64_t)z * plane];
+    if (live)
+        for (int z = threadIdx.y; z < splits; z += 8) s += src[(int64_t)z * plane];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y != 0 || !live) return;
+    s = part[0][threadIdx.x];
+#pragma unroll
+    for (int r = 1; r < 8; ++r) s += part[r][threadIdx.x];
     __nv_bfloat16 *d = dw + ((int64_t)oc * IC + ci) * taps + tap;
     if (beta != 0.f) s = fmaf(beta, __bfloat162float(*d), s);
     *d = __float2bfloat16_rn(s);
@@ -373,7 +384,7 @@ int backward_weight_nhwc(ag_device *dev, const __nv_bfloat16 *xh, int64_t bs, in
     else
         AG_TRY(launch_wgrad<64>(dev, tdy, tx, p, grid));
     const int64_t outs = oc * p.taps * ic;
-    wgrad_reduce_kernel<<<(unsigned)ceil_div(outs, 256), 256, 0, dev->stream>>>(
+    wgrad_reduce_kernel<<<(unsigned)ceil_div(outs, 32), dim3(32, 8), 0, dev->stream>>>(
         p.partial, splits, m_total, p.taps, (int)cp, (int)oc, (int)ic, beta, dw);
     AG_CHECK_LAUNCH();
     return AG_OK;

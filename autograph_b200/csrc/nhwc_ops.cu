@@ -20,31 +20,41 @@ struct Vec8 {
     }
 };
 
+// FH, FW > 0: the filter size is a compile-time constant (the divisions below become shifts
+// and multiplies; with run-time divisors the kernel is bound by them, 173 us against the 25 us
+// its 126 MB of stores take at the wide stack's first layer).
+template <int FH, int FW>
 __global__ void im2col_channels_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ out,
-                                       int ic, int ih, int iw, int fh, int fw, int oh, int ow, int cp,
-                                       int64_t total) {
-    const int groups = cp / 8;
+                                       int ic, int ih, int iw, int fh_rt, int fw_rt, int oh, int ow, int cp,
+                                       uint32_t per_image) {
+    const int fh = FH > 0 ? FH : fh_rt, fw = FW > 0 ? FW : fw_rt;
+    const uint32_t groups = (uint32_t)cp / 8;
     const int taps = fh * fw, k = ic * taps;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int g = (int)(i % groups);
-        int64_t t = i / groups;
-        const int ox = (int)(t % ow);
-        t /= ow;
-        const int oy = (int)(t % oh);
-        const int64_t b = t / oh;
+    const int64_t plane = (int64_t)ih * iw;
+    const int64_t b = blockIdx.y;   // one image per grid row: 32-bit index arithmetic inside it
+    out += b * (int64_t)per_image * 8;
+    // The stride of the loop is a multiple of the groups per pixel, so a thread keeps its channel
+    // group: the eight source offsets relative to the pixel are computed once.
+    const uint32_t first = blockIdx.x * blockDim.x + threadIdx.x;
+    const int g = (int)(first % groups);
+    int off[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const int c = g * 8 + e;
+        const int ci = c / taps, r = c - ci * taps;
+        const int fi = r / fw, fj = r - fi * fw;
+        off[e] = c < k ? (int)(ci * plane) + fi * iw + fj : -1;
+    }
+    const unsigned short *img = reinterpret_cast<const unsigned short *>(x) + b * ic * plane;
+    for (uint32_t i = first; i < per_image; i += gridDim.x * blockDim.x) {
+        const uint32_t t = i / groups;
+        const uint32_t oy = t / (uint32_t)ow, ox = t - oy * (uint32_t)ow;
         uint32_t wds[4] = {0u, 0u, 0u, 0u};
         if (g * 8 < k) {
-            const unsigned short *img = reinterpret_cast<const unsigned short *>(x) + b * ic * (int64_t)ih * iw;
+            const unsigned short *px = img + oy * (uint32_t)iw + ox;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                const int c = g * 8 + e;
-                unsigned short v = 0;
-                if (c < k) {
-                    const int ci = c / taps, r = c - ci * taps;
-                    const int fi = r / fw, fj = r - fi * fw;
-                    v = img[((int64_t)ci * ih + oy + fi) * iw + ox + fj];
-                }
+                const unsigned short v = off[e] >= 0 ? __ldg(px + off[e]) : (unsigned short)0;
                 wds[e >> 1] |= (uint32_t)v << ((e & 1) * 16);
             }
         }
@@ -206,10 +216,22 @@ int im2col_channels(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t 
                "im2col_channels: bad channel pitch or alignment");
     AG_REQUIRE(oh == ih - fh + 1 && ow == iw - fw + 1 && oh > 0 && ow > 0, AG_ERR_SHAPE,
                "im2col_channels: output shape does not match");
-    const int64_t total = bs * oh * ow * (cp / 8);
-    if (total == 0) return AG_OK;
-    im2col_channels_kernel<<<grid_for(dev, total), 256, 0, dev->stream>>>(
-        x, out, (int)ic, (int)ih, (int)iw, fh, fw, (int)oh, (int)ow, (int)cp, total);
+    const int64_t per_image = oh * ow * (cp / 8);
+    AG_REQUIRE(per_image < (int64_t(1) << 31) && bs <= 65535 && ic * ih * iw < (int64_t(1) << 31), AG_ERR_LIMIT,
+               "im2col_channels: image too large");
+    AG_REQUIRE(256 % (cp / 8) == 0, AG_ERR_UNSUPPORTED, "im2col_channels: channel pitch must be 64, 128 or 256");
+    if (bs == 0) return AG_OK;
+    const int64_t want = ceil_div(per_image, 256);
+    const dim3 grid((unsigned)(want > 4096 ? 4096 : want), (unsigned)bs);
+    if (fh == 3 && fw == 3)
+        im2col_channels_kernel<3, 3><<<grid, 256, 0, dev->stream>>>(
+            x, out, (int)ic, (int)ih, (int)iw, fh, fw, (int)oh, (int)ow, (int)cp, (uint32_t)per_image);
+    else if (fh == 5 && fw == 5)
+        im2col_channels_kernel<5, 5><<<grid, 256, 0, dev->stream>>>(
+            x, out, (int)ic, (int)ih, (int)iw, fh, fw, (int)oh, (int)ow, (int)cp, (uint32_t)per_image);
+    else
+        im2col_channels_kernel<0, 0><<<grid, 256, 0, dev->stream>>>(
+            x, out, (int)ic, (int)ih, (int)iw, fh, fw, (int)oh, (int)ow, (int)cp, (uint32_t)per_image);
     AG_CHECK_LAUNCH();
     return AG_OK;
 }
