@@ -221,7 +221,8 @@ int im2col_channels(ag_device *dev, const __nv_bfloat16 *x, int64_t bs, int64_t 
                "im2col_channels: image too large");
     AG_REQUIRE(256 % (cp / 8) == 0, AG_ERR_UNSUPPORTED, "im2col_channels: channel pitch must be 64, 128 or 256");
     if (bs == 0) return AG_OK;
-    const int64_t want = ceil_div(per_image, 256);
+    // eight pixels per thread, so that the offsets a thread computes up front are used eight times
+    const int64_t want = ceil_div(per_image, 256 * 8);
     const dim3 grid((unsigned)(want > 4096 ? 4096 : want), (unsigned)bs);
     if (fh == 3 && fw == 3)
         im2col_channels_kernel<3, 3><<<grid, 256, 0, dev->stream>>>(
