@@ -39,7 +39,12 @@ constexpr int TILE_M = 256;   // per pair; 128 rows per CTA
 constexpr int TILE_N = 256;   // per pair; each CTA stages 128 columns of B
 constexpr int BLOCK_K = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 7;
+// Ring depth.  Seven stages fill the CTA's shared memory; a profiler that adds to the launch's
+// resources cannot launch that, so a build for profiling may lower it (-DAG_TC2_STAGES=6).
+#ifndef AG_TC2_STAGES
+#define AG_TC2_STAGES 7
+#endif
+constexpr int STAGES = AG_TC2_STAGES;
 constexpr int A_BYTES = 128 * BLOCK_K * 2;  // 16 KiB
 constexpr int B_BYTES = 128 * BLOCK_K * 2;  // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
