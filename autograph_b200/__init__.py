@@ -31,13 +31,19 @@ def _torch():
     return torch
 
 
+_DTYPE_CODES = {}
+
+
 def _dtype_code(t) -> int:
-    torch = _torch()
-    table = {torch.float32: _capi.AG_F32, torch.bfloat16: _capi.AG_BF16, torch.uint8: _capi.AG_U8,
-             torch.uint16: _capi.AG_U16, torch.uint32: _capi.AG_U32}
-    if t not in table:
-        raise AgError(_capi.AG_ERR_DTYPE, f"dtype {t} unimplemented")
-    return table[t]
+    if not _DTYPE_CODES:
+        torch = _torch()
+        _DTYPE_CODES.update({torch.float32: _capi.AG_F32, torch.bfloat16: _capi.AG_BF16,
+                             torch.uint8: _capi.AG_U8, torch.uint16: _capi.AG_U16,
+                             torch.uint32: _capi.AG_U32})
+    try:
+        return _DTYPE_CODES[t]
+    except KeyError:
+        raise AgError(_capi.AG_ERR_DTYPE, f"dtype {t} unimplemented") from None
 
 
 def _ptr(t) -> ctypes.c_void_p:
@@ -77,6 +83,7 @@ class Device:
         with torch.cuda.device(index):
             self.stream = stream if stream is not None else torch.cuda.Stream(device=index)
             torch.cuda.set_stream(self.stream)
+        self._stream_ptr = self.stream.cuda_stream
         handle = ctypes.c_void_p()
         _capi.check(lib().ag_device_create_on_stream(index, ctypes.c_void_p(self.stream.cuda_stream),
                                                      ctypes.byref(handle)))
@@ -171,9 +178,12 @@ class Device:
         return out
 
     def _sync_in(self):
-        # Inputs were produced on torch's current stream; order this stream after it.
-        torch = _torch()
-        self.stream.wait_stream(torch.cuda.current_stream(self.index))
+        # Inputs were produced on torch's current stream; order this stream after it (nothing
+        # to do when that stream is this device's own, which is the case unless the caller
+        # changed torch's current stream after creating the device).
+        cur = _torch().cuda.current_stream(self.index)
+        if cur.cuda_stream != self._stream_ptr:
+            self.stream.wait_stream(cur)
 
     # -- linalg ----------------------------------------------------------------
     def gemm(self, alpha, a, b, beta, c):

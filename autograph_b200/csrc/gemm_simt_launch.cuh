@@ -25,7 +25,7 @@ inline CfgId pick_cfg(int M, int N, int sms) {
     if (N <= 16 && ceil_div(M, 128) * 2 < sms) return kCfgS16s;
     if (N <= 8) return kCfgS8;
     if (N <= 16) return kCfgS16;
-    int64_t tiles_l = ceil_div(M, 128) * ceil_div(N, 128);
+    int64_t tiles_l = ceil_div(M, CfgL::BM) * ceil_div(N, CfgL::BN);
     if (tiles_l >= sms) return kCfgL;
     int64_t tiles_m = ceil_div(M, 64) * ceil_div(N, 64);
     if (tiles_m * 2 >= sms) return kCfgM;
@@ -34,7 +34,7 @@ inline CfgId pick_cfg(int M, int N, int sms) {
 
 inline void cfg_dims(CfgId id, int &bm, int &bn) {
     switch (id) {
-        case kCfgL: bm = 128; bn = 128; break;
+        case kCfgL: bm = CfgL::BM; bn = CfgL::BN; break;
         case kCfgM: bm = 64; bn = 64; break;
         case kCfgXS: bm = 32; bn = 32; break;
         case kCfgS16: bm = 128; bn = 16; break;
