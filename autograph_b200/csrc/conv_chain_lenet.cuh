@@ -244,18 +244,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int by = blk >> 1, bx = blk & 1;
         const float *img = s_mid + g * (C1 * P1 * P1) + (2 * by) * P1 + 4 * bx;
         const float *wp = s_w2 + pair * W2_PAIR;
-        float acc[2][4][2];
+        // Two channels per instruction: fma.rn.f32x2 on the (channel 2 * pair, channel 2 * pair + 1)
+        // register pair, the pixel's value in both halves of the multiplier.  Same FMAs in the same
+        // order per accumulator, half the instructions to issue.
+        unsigned long long acc2[2][4];
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int b = 0; b < 4; ++b) acc[a][b][0] = acc[a][b][1] = 0.f;
+            for (int b = 0; b < 4; ++b) acc2[a][b] = 0ull;
         // The loop over input channels stays rolled: the phase runs once per launch, and 2400
         // FFMAs of straight-line code fetched for a single use cost more in instruction fetch
         // than the loop costs in branches (measured both ways; the patch-row loop inside, and
         // conv1's, are faster unrolled).
 #pragma unroll 1
         for (int ci = 0; ci < C1; ++ci) {
-            float wprev[W2_ROW];
+            unsigned long long wprev[W2_ROW / 2];
 #pragma unroll
             for (int pr = 0; pr < F + 1; ++pr) {
                 float p[8];
@@ -263,36 +266,44 @@ __global__ void __launch_bounds__(kThreads, 1)
                     *reinterpret_cast<const float4 *>(img + ci * (P1 * P1) + pr * P1);
                 *reinterpret_cast<float4 *>(p + 4) =
                     *reinterpret_cast<const float4 *>(img + ci * (P1 * P1) + pr * P1 + 4);
-                float wcur[W2_ROW];
+                unsigned long long pp[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) asm("mov.b64 %0, {%1, %1};" : "=l"(pp[q]) : "f"(p[q]));
+                unsigned long long wcur[W2_ROW / 2];
                 if (pr < F) {
 #pragma unroll
-                    for (int q = 0; q < W2_ROW / 4; ++q)
-                        *reinterpret_cast<float4 *>(wcur + 4 * q) =
-                            *reinterpret_cast<const float4 *>(wp + ci * W2_CI + pr * W2_ROW + 4 * q);
+                    for (int q = 0; q < W2_ROW / 4; ++q) {
+                        const ulonglong2 w2 =
+                            *reinterpret_cast<const ulonglong2 *>(wp + ci * W2_CI + pr * W2_ROW + 4 * q);
+                        wcur[2 * q] = w2.x;
+                        wcur[2 * q + 1] = w2.y;
+                    }
                 }
 #pragma unroll
                 for (int fj = 0; fj < F; ++fj) {
                     if (pr < F) {
 #pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            acc[0][b][0] = fmaf(p[fj + b], wcur[2 * fj], acc[0][b][0]);
-                            acc[0][b][1] = fmaf(p[fj + b], wcur[2 * fj + 1], acc[0][b][1]);
-                        }
+                        for (int b = 0; b < 4; ++b)
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[0][b]) : "l"(pp[fj + b]), "l"(wcur[fj]));
                     }
                     if (pr >= 1) {
 #pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            acc[1][b][0] = fmaf(p[fj + b], wprev[2 * fj], acc[1][b][0]);
-                            acc[1][b][1] = fmaf(p[fj + b], wprev[2 * fj + 1], acc[1][b][1]);
-                        }
+                        for (int b = 0; b < 4; ++b)
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[1][b]) : "l"(pp[fj + b]), "l"(wprev[fj]));
                     }
                 }
                 if (pr < F) {
 #pragma unroll
-                    for (int q = 0; q < W2_ROW; ++q) wprev[q] = wcur[q];
+                    for (int q = 0; q < W2_ROW / 2; ++q) wprev[q] = wcur[q];
                 }
             }
         }
+        float acc[2][4][2];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[a][b][0]), "=f"(acc[a][b][1]) : "l"(acc2[a][b]));
         // flattened (c, h, w) index of the dense chain's input, [k][ROWS]
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
