@@ -895,6 +895,28 @@ bool train_step_graph(ag_model *m, const void *x_host, const uint8_t *t_host, in
             t.grad_scale == m->grad_scale && t.with_update == with_update &&
             t.from_device == from_device)
             e = &t;
+    if (!e && with_update) {
+        // A learning rate this shape has not been captured with, while another one has: a
+        // schedule.  One graph without the update then serves every rate and the update follows
+        // as a plain launch, instead of one capture (and, past eight, one eviction) per rate.
+        bool other_rate = false;
+        for (auto &t : m->train_graphs)
+            if (t.bs == bs && t.c == c && t.h == h && t.w == w && t.with_update &&
+                t.from_device == from_device && t.lr != lr)
+                other_rate = true;
+        if (other_rate) {
+            if (!train_step_graph(m, x_host, t_host, bs, c, h, w, 0.f, nullptr, false, from_device))
+                return false;
+            apply_update(m, lr);
+            if (loss_host) {
+                if (cudaStreamSynchronize(stream) != cudaSuccess)
+                    throw Error(AG_ERR_CUDA, "cudaStreamSynchronize failed");
+                *loss_host = *m->loss_pinned;
+                m->loss_in_flight = false;
+            }
+            return true;
+        }
+    }
     if (!e) {
         if (m->train_graphs.size() >= 8) {
             m->drop(m->train_graphs.front());

@@ -163,6 +163,67 @@ def test_wide_stack_bf16_forward_backward(dev):
     model.close()
 
 
+def test_learning_rate_schedule_reuses_one_graph(dev):
+    """A different learning rate every step: the captured step without the update serves all of
+    them (the update follows as a plain launch) and the parameters equal those of the
+    enqueue-then-update form bit for bit."""
+    import autograph_b200 as ag
+    rng = np.random.default_rng(8100)
+    xs = [torch.from_numpy(rng.uniform(0, 1, (100, 1, 28, 28)).astype(np.float32)).pin_memory() for _ in range(3)]
+    ts = [torch.from_numpy(rng.integers(0, 10, 100).astype(np.uint8)).pin_memory() for _ in range(3)]
+    a = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=5)
+    b = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=5)
+    rates = [0.01, 0.01, 0.01, 0.02, 0.03, 0.01, 0.04, 0.05, 0.06, 0.07, 0.08, 0.09, 0.1, 0.11]
+    before = ag.kernel_launch_count()
+    for i, lr in enumerate(rates):
+        la = a.train_step(xs[i % 3], ts[i % 3], lr)
+        lb = b.train_forward_backward(xs[i % 3].to(dev.torch_device), ts[i % 3].to(dev.torch_device))[0]
+        b.apply_update(lr)
+        assert la == lb
+    assert ag.kernel_launch_count() > before
+    for i in range(len(a.parameter_lens)):
+        assert np.array_equal(a.get_parameter(i), b.get_parameter(i)), i
+    a.close()
+    b.close()
+
+
+STAGE_SPECS = {
+    # second stage inside a run that must hand a gradient to the layer before it (first convolution
+    # has too few output channels for the tensor cores), biases, odd planes (27 x 27 -> 13 x 13:
+    # cells no pool window covers)
+    "input_gradient_bias_odd": (8, 63, [
+        ("conv", 3, 16, (5, 5), True), ("relu",), ("pool", (2, 2)),
+        ("conv", 16, 64, (3, 3), True), ("relu",), ("pool", (2, 2)),
+        ("flatten",), ("dense", 64 * 13 * 13, 32, False), ("relu",), ("dense", 32, 10, True)]),
+    # a run of two stages: patches first layer with bias, odd second plane (17 x 17 -> 8 x 8)
+    "two_stages_bias_odd": (16, 40, [
+        ("conv", 3, 64, (3, 3), True), ("relu",), ("pool", (2, 2)),
+        ("conv", 64, 64, (3, 3), True), ("relu",), ("pool", (2, 2)),
+        ("flatten",), ("dense", 64 * 8 * 8, 32, False), ("relu",), ("dense", 32, 10, True)]),
+}
+
+
+@pytest.mark.parametrize("case", sorted(STAGE_SPECS))
+def test_channels_last_stage_runs(dev, case):
+    """Conv2 -> Relu -> MaxPool2 stages of a bf16 training pass that run channels-last as one
+    node: loss and every gradient against the oracle's layer-by-layer composition, for the forms
+    the wide stack does not reach (gradient handed to an earlier layer, biases, odd planes)."""
+    import autograph_b200 as ag
+    bs, size, spec = STAGE_SPECS[case]
+    P = _params(spec, 7300, True)
+    x = oracle.round_bf16(np.random.default_rng(7301).standard_normal((bs, 3, size, size)).astype(np.float32))
+    t = np.random.default_rng(7302).integers(0, 10, bs).astype(np.uint8)
+    model = ag.Model(dev, spec, torch.bfloat16, seed=1)
+    model.set_parameters(P)
+    xh = torch.from_numpy(x).to(torch.bfloat16).pin_memory()
+    loss = model.train_step(xh, torch.from_numpy(t).pin_memory(), 0.01)
+    ref_loss, grads, _, _ = models.train_step(spec, P, x, t.astype(np.uint32), 0.01, acc="f64", bf16=True)
+    assert abs(loss - ref_loss) <= 3e-2 * abs(ref_loss)
+    for i, g in enumerate(grads):
+        assert _rel(model.get_gradient(i), g.ravel()) <= 5e-2, i
+    model.close()
+
+
 def test_wide_stack_full_batch_properties(dev):
     """Config 3 at its full batch 256: rows are independent, so the first 8 rows of the
     batch-256 forward equal the batch-8 forward."""
