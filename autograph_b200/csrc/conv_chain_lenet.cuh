@@ -7,9 +7,10 @@
 //  * register tiles sized for the shared-memory return path.  Shared memory delivers 128 bytes
 //    per clock to the register file, broadcasts included, while the four schedulers retire 128
 //    FFMAs per clock: a thread has to get at least four FFMAs out of every float it loads.
-//    conv1: one item is 2 x 8 pixels x 3 channels (48 accumulators; 7 images are 504 items, one
+//    conv1: one item is 2 x 12 pixels x 2 channels (48 accumulators; 7 images are 504 items, one
 //    round of the 512 threads); conv2: 2 x 4 pixels x 2 channels (448 items: wider tiles leave
-//    too few warps to cover the load latency, measured).
+//    too few warps to cover the load latency, measured).  The two channels of an item are the
+//    halves of one fma.rn.f32x2: half the instructions for the same FMAs.
 //    Patch rows stream through registers one at a time (row r feeds filter row r of the
 //    block's first pixel row and filter row r-1 of its second, whose weights are kept from the
 //    previous step), so a thread holds one patch row and two filter rows, not a whole patch.
@@ -40,12 +41,13 @@ constexpr int IH = 28, IW = 28, F = 5;
 constexpr int C1 = 6, H1 = 24, P1 = 12;   // conv1 output channels / size, pooled size
 constexpr int C2 = 16, H2 = 8, P2 = 4;    // conv2
 constexpr int kFlat = C2 * P2 * P2;       // 256
-// Filter banks in shared memory.  conv1: [channel triple 2][tap 25][4] (three channels + a zero).
+// Filter banks in shared memory.  conv1: [channel pair 3][filter row 5][tap 5][2], rows padded to 12.
 // conv2: [channel pair 8][input channel 6][filter row 5][tap 5][2] with filter rows padded to
 // 12 floats: a filter row of a pair is three 16-byte loads; the pair pitch keeps the eight
 // pairs of a warp on different banks.
-constexpr int W1_TRIPLE = F * F * 4;      // 100
-constexpr int W1_FLOATS = 2 * W1_TRIPLE;  // 200
+constexpr int W1_ROW = 12;                // a filter row of a channel pair: 5 taps x 2 channels + 2 zeros
+constexpr int W1_PAIR = F * W1_ROW + 4;   // 64: the three pairs of a block on different banks
+constexpr int W1_FLOATS = (C1 / 2) * W1_PAIR;  // 192
 constexpr int W2_ROW = 12;
 constexpr int W2_CI = F * W2_ROW;         // 60
 constexpr int W2_PAIR = C1 * W2_CI + 4;   // 364
@@ -142,9 +144,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     {
         const T *w1 = reinterpret_cast<const T *>(pl.w1);
         for (int i = tid; i < W1_FLOATS; i += kThreads) {
-            const int triple = i / W1_TRIPLE, r = i - triple * W1_TRIPLE;
-            const int tap = r >> 2, o = r & 3;
-            s_w1[i] = o < 3 ? to_f32(w1[(triple * 3 + o) * (F * F) + tap]) : 0.f;
+            const int pair = i / W1_PAIR, r = i - pair * W1_PAIR;
+            const int fi = r / W1_ROW, r2 = r - fi * W1_ROW;
+            const int fj = r2 >> 1, o = r2 & 1;
+            s_w1[i] = (fi < F && fj < F) ? to_f32(w1[((pair * 2 + o) * F + fi) * F + fj]) : 0.f;
         }
         const T *w2 = reinterpret_cast<const T *>(pl.w2);
         float v[(W2_FLOATS + kThreads - 1) / kThreads];
@@ -167,60 +170,77 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     AG_STAMP(1);
 
-    // ---- conv1 + relu + pool: item = (image, 2 rows x 8 columns, channel triple)
+    // ---- conv1 + relu + pool: item = (image, 2 rows x 12 columns, channel pair).  The two
+    // channels of a pair are the halves of one fma.rn.f32x2 (the pixel's value in both halves of
+    // the multiplier): per patch row 120 packed FMAs and 20 moves instead of 240 FFMAs, the same
+    // sums in the same order.
     if (tid < nimg * 72) {
         const int g = tid / 72, r = tid - g * 72;
-        const int triple = r & 1, blk = r >> 1;        // the two triples of a block sit in adjacent lanes
-        const int by = blk / 3, bx = blk - by * 3;
-        const float *img = s_in + g * (IH * IW) + (2 * by) * IW + 8 * bx;
-        const float *wt = s_w1 + triple * W1_TRIPLE;
-        float acc[2][8][3];
+        const int pair = r % 3, blk = r / 3;           // the three pairs of a block sit in adjacent lanes
+        const int by = blk >> 1, hx = blk & 1;
+        const float *img = s_in + g * (IH * IW) + (2 * by) * IW + 12 * hx;
+        const float *wt = s_w1 + pair * W1_PAIR;
+        unsigned long long acc2[2][12];
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int b = 0; b < 8; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = 0.f;
-        float wprev[F][3];
+            for (int b = 0; b < 12; ++b) acc2[a][b] = 0ull;
+        unsigned long long wprev[W1_ROW / 2];
 #pragma unroll
         for (int pr = 0; pr < F + 1; ++pr) {       // patch row pr = filter row pr of pixel row 0
-            float p[12];                           // and filter row pr - 1 of pixel row 1
+            float p[16];                           // and filter row pr - 1 of pixel row 1
 #pragma unroll
-            for (int q = 0; q < 3; ++q)
+            for (int q = 0; q < 4; ++q)
                 *reinterpret_cast<float4 *>(p + 4 * q) =
                     *reinterpret_cast<const float4 *>(img + pr * IW + 4 * q);
-            float wcur[F][3];
+            unsigned long long wcur[W1_ROW / 2];
+            if (pr < F) {
 #pragma unroll
-            for (int fj = 0; fj < F; ++fj) {
-                if (pr < F) {
-                    const float4 w4 = *reinterpret_cast<const float4 *>(wt + (pr * F + fj) * 4);
-                    wcur[fj][0] = w4.x; wcur[fj][1] = w4.y; wcur[fj][2] = w4.z;
-#pragma unroll
-                    for (int b = 0; b < 8; ++b)
-#pragma unroll
-                        for (int o = 0; o < 3; ++o)
-                            acc[0][b][o] = fmaf(p[fj + b], wcur[fj][o], acc[0][b][o]);
+                for (int q = 0; q < W1_ROW / 4; ++q) {
+                    const ulonglong2 w2 = *reinterpret_cast<const ulonglong2 *>(wt + pr * W1_ROW + 4 * q);
+                    wcur[2 * q] = w2.x;
+                    wcur[2 * q + 1] = w2.y;
                 }
-                if (pr >= 1) {
+            }
 #pragma unroll
-                    for (int b = 0; b < 8; ++b)
+            for (int h = 0; h < 2; ++h) {          // six pixels at a time: ten doubled patch values live
+                unsigned long long pp[10];
 #pragma unroll
-                        for (int o = 0; o < 3; ++o)
-                            acc[1][b][o] = fmaf(p[fj + b], wprev[fj][o], acc[1][b][o]);
+                for (int q = 0; q < 10; ++q) asm("mov.b64 %0, {%1, %1};" : "=l"(pp[q]) : "f"(p[6 * h + q]));
+#pragma unroll
+                for (int fj = 0; fj < F; ++fj) {
+                    if (pr < F) {
+#pragma unroll
+                        for (int b = 0; b < 6; ++b)
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;"
+                                : "+l"(acc2[0][6 * h + b]) : "l"(pp[fj + b]), "l"(wcur[fj]));
+                    }
+                    if (pr >= 1) {
+#pragma unroll
+                        for (int b = 0; b < 6; ++b)
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;"
+                                : "+l"(acc2[1][6 * h + b]) : "l"(pp[fj + b]), "l"(wprev[fj]));
+                    }
                 }
             }
             if (pr < F) {
 #pragma unroll
-                for (int fj = 0; fj < F; ++fj)
-#pragma unroll
-                    for (int o = 0; o < 3; ++o) wprev[fj][o] = wcur[fj][o];
+                for (int q = 0; q < W1_ROW / 2; ++q) wprev[q] = wcur[q];
             }
         }
         // round to T, relu, 2x2 pool (window order (0,0),(0,1),(1,0),(1,1); first maximum wins)
-        float *dst = s_mid + (g * C1 + triple * 3) * (P1 * P1) + by * P1 + 4 * bx;
+        float acc[2][12][2];
 #pragma unroll
-        for (int o = 0; o < 3; ++o) {
-            float m[4];
+        for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int wx = 0; wx < 4; ++wx) {
+            for (int b = 0; b < 12; ++b)
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(acc[a][b][0]), "=f"(acc[a][b][1]) : "l"(acc2[a][b]));
+        float *dst = s_mid + (g * C1 + pair * 2) * (P1 * P1) + by * P1 + 6 * hx;
+#pragma unroll
+        for (int o = 0; o < 2; ++o) {
+            float m[6];
+#pragma unroll
+            for (int wx = 0; wx < 6; ++wx) {
                 float v00 = round_t<T>(acc[0][2 * wx][o]), v01 = round_t<T>(acc[0][2 * wx + 1][o]);
                 float v10 = round_t<T>(acc[1][2 * wx][o]), v11 = round_t<T>(acc[1][2 * wx + 1][o]);
                 v00 = v00 >= 0.f ? v00 : 0.f; v01 = v01 >= 0.f ? v01 : 0.f;
@@ -231,7 +251,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (v11 > mm) mm = v11;
                 m[wx] = mm;
             }
-            *reinterpret_cast<float4 *>(dst + o * (P1 * P1)) = make_float4(m[0], m[1], m[2], m[3]);
+#pragma unroll
+            for (int q = 0; q < 3; ++q)
+                *reinterpret_cast<float2 *>(dst + o * (P1 * P1) + 2 * q) = make_float2(m[2 * q], m[2 * q + 1]);
         }
     }
     __syncthreads();

@@ -32,6 +32,9 @@ namespace lenet_tc {
 
 using dense_small::ROWS;
 using namespace lenet;   // geometry constants, bulk_g2s, round_t
+// this kernel's first convolution keeps the [channel triple 2][tap 25][4] filter layout
+constexpr int W1_TRIPLE = F * F * 4;         // 100
+constexpr int W1_TC_FLOATS = 2 * W1_TRIPLE;  // 200
 
 constexpr int TILES = (kGroup * P1 * P1 + 127) / 128;   // 8 tiles of 128 pixel rows
 constexpr int ACT_ROWS = TILES * 128 + 64;          // rows a tile plus the largest tap shift (52) can reach
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     {
         const T *w1 = reinterpret_cast<const T *>(pl.w1);
-        for (int i = tid; i < W1_FLOATS; i += kThreads) {
+        for (int i = tid; i < W1_TC_FLOATS; i += kThreads) {
             const int triple = i / W1_TRIPLE, r = i - triple * W1_TRIPLE;
             const int tap = r >> 2, o = r & 3;
             s_w1[i] = o < 3 ? to_f32(w1[(triple * 3 + o) * (F * F) + tap]) : 0.f;
@@ -355,7 +358,7 @@ inline size_t make_plan(Plan *pl, int64_t bs, int64_t ic, int64_t ih, int64_t iw
     pl->red_off = pl->c2_off;               // red overlays the conv2 output (dead after the pool)
     if (pl->chain.red_floats * 4 > C2_BYTES) return 0;
     pl->in_off = take(kGroup * IH * IW * 4, 16);
-    pl->w1_off = take(W1_FLOATS * 4, 16);
+    pl->w1_off = take(W1_TC_FLOATS * 4, 16);
     pl->xa_off = take(kFlat * ROWS * 4, 16);
     pl->xb_off = take(kFlat * ROWS * 4, 16);
     pl->bar_off = take(8 * (1 + TILES), 16);
