@@ -468,6 +468,59 @@ __global__ void bias_grad_cols_kernel(const T *__restrict__ x, float *__restrict
     }
 }
 
+// The same for wide matrices whose rows keep 16-byte alignment: a thread owns the columns of one
+// 16-byte vector (4 f32 / 8 bf16) and has four rows' loads in flight before it adds them, in row
+// order, to its running sums.
+template <class T>
+__global__ void bias_grad_cols_vec_kernel(const T *__restrict__ x, float *__restrict__ partial,
+                                          int64_t rows, int64_t cols, int64_t rows_per_chunk,
+                                          T *__restrict__ y, float beta) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float part[8][32 * V + 1];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int64_t c = ((int64_t)blockIdx.x * 32 + cx) * V;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
+    const int64_t r1 = min(rows, r0 + rows_per_chunk);
+    float s[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) s[j] = 0.f;
+    if (c < cols) {
+        int64_t r = r0 + ry;
+        for (; r + 24 < r1; r += 32) {
+            Vec16<T> v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u].raw = *reinterpret_cast<const uint4 *>(x + (r + 8 * u) * cols + c);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < V; ++j) s[j] += v[u].get(j);
+        }
+        for (; r < r1; r += 8) {
+            Vec16<T> v;
+            v.raw = *reinterpret_cast<const uint4 *>(x + r * cols + c);
+#pragma unroll
+            for (int j = 0; j < V; ++j) s[j] += v.get(j);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) part[ry][cx * V + j] = s[j];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * V; i += blockDim.x) {
+        const int64_t col = (int64_t)blockIdx.x * 32 * V + i;
+        if (col >= cols) continue;
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += part[k][i];
+        if (y != nullptr) {  // a single chunk: this is the whole sum
+            if (beta != 0.f) t = __fadd_rn(t, __fmul_rn(beta, to_f32(y[col])));
+            y[col] = from_f32<T>(t);
+        } else {
+            partial[(int64_t)blockIdx.y * cols + col] = t;
+        }
+    }
+}
+
 template <class T>
 __global__ void bias_grad_inner_kernel(const T *__restrict__ x, float *__restrict__ partial,
                                        int64_t rows, int64_t cols, int64_t inner,
@@ -490,13 +543,22 @@ __global__ void bias_grad_inner_kernel(const T *__restrict__ x, float *__restric
     if (threadIdx.x == 0) partial[(int64_t)blockIdx.y * cols + c] = part[0];
 }
 
+// Block of 32 x 8 threads: 32 consecutive columns, the chunk rows dealt round-robin to the eight
+// thread rows; the eight sums are added in row order (reproducible).
 template <class T>
 __global__ void bias_grad_final_kernel(const float *__restrict__ partial, T *__restrict__ y,
                                        int64_t cols, int chunks, float beta) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float part[8][33];
+    const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
     float v = 0.f;
-    for (int k = 0; k < chunks; ++k) v += partial[(int64_t)k * cols + c];
+    if (c < cols)
+        for (int k = threadIdx.y; k < chunks; k += 8) v += partial[(int64_t)k * cols + c];
+    part[threadIdx.y][threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.y != 0 || c >= cols) return;
+    v = part[0][threadIdx.x];
+#pragma unroll
+    for (int r = 1; r < 8; ++r) v += part[r][threadIdx.x];
     if (beta != 0.f) v = __fadd_rn(v, __fmul_rn(beta, to_f32(y[c])));
     y[c] = from_f32<T>(v);
 }
@@ -504,9 +566,13 @@ __global__ void bias_grad_final_kernel(const float *__restrict__ partial, T *__r
 template <class T>
 static int bias_grad_run(ag_device *dev, const T *x, int64_t rows, int64_t cols, int64_t inner,
                          float beta, T *y) {
-    // Enough row chunks to fill the GPU, at most 1024.
-    int64_t col_blocks = inner == 1 ? ceil_div(cols, 32) : cols;
-    int64_t chunks = ceil_div((int64_t)dev->sm_count * 4, col_blocks);
+    // Wide, aligned matrices: 16-byte loads (a CTA covers 32 vectors of columns).
+    constexpr int V = Vec16<T>::N;
+    const bool vec = inner == 1 && cols % V == 0 && cols >= 32 * V && rows > 1024 &&
+                     (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    // Enough row chunks to fill the GPU (eight CTAs per SM for the vector form), at most 1024.
+    int64_t col_blocks = inner == 1 ? ceil_div(cols, vec ? 32 * V : 32) : cols;
+    int64_t chunks = ceil_div((int64_t)dev->sm_count * (vec ? 8 : 4), col_blocks);
     if (chunks > rows) chunks = rows;
     if (chunks > 1024) chunks = 1024;
     if (chunks < 1) chunks = 1;
@@ -524,14 +590,17 @@ static int bias_grad_run(ag_device *dev, const T *x, int64_t rows, int64_t cols,
     AG_TRY(workspace(dev, sizeof(float) * (size_t)chunks * (size_t)cols, &ws));
     dim3 grid((unsigned)col_blocks, (unsigned)chunks);
     AG_REQUIRE(col_blocks < (1ll << 31), AG_ERR_LIMIT, "too many columns");
-    if (inner == 1)
+    if (vec)
+        bias_grad_cols_vec_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols,
+                                                                    rows_per_chunk, nullptr, 0.f);
+    else if (inner == 1)
         bias_grad_cols_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols,
                                                                 rows_per_chunk, nullptr, 0.f);
     else
         bias_grad_inner_kernel<T><<<grid, 256, 0, dev->stream>>>(x, (float *)ws, rows, cols, inner,
                                                                  rows_per_chunk);
     AG_CHECK_LAUNCH();
-    bias_grad_final_kernel<T><<<(unsigned)ceil_div(cols, 256), 256, 0, dev->stream>>>(
+    bias_grad_final_kernel<T><<<(unsigned)ceil_div(cols, 32), dim3(32, 8), 0, dev->stream>>>(
         (const float *)ws, y, cols, (int)chunks, beta);
     AG_CHECK_LAUNCH();
     return AG_OK;
