@@ -5,8 +5,8 @@ Some users of the library run where device memory cannot be requested after star
 allocations on its worker threads).  They call this entry point with a device ordinal
 and a stream; its partial sums live in a fixed array inside the library.  The test
 checks it against ag_gemm on shapes that are split along k, twice in a row (the
-array keeps the previous call's contents), and checks the size limit.
-This file sorts last so that a failure here cannot hide any other test.
+array keeps the previous call's contents), and checks the size limit, that device memory
+does not change across calls and that the split path is the one taken.
 """
 import ctypes
 
