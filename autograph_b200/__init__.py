@@ -788,6 +788,21 @@ class Model:
         _capi.check(lib().ag_model_infer(self._h, _ptr(x_host), bs, c, h, w, _ptr(out_host)))
         return out_host
 
+    def infer_enqueue(self, x_host, out_host) -> int:
+        """Pipelined form of infer for two batches in flight: starts the copy of the pinned batch
+        and the network behind it, returns a ticket at once; infer_wait(ticket) blocks until
+        out_host (pinned) holds the logits."""
+        bs, c, h, w = x_host.shape
+        self._check(x_host, "x_host", self.dtype, False)
+        self._check(out_host, "out_host", self.dtype, False, (bs, self.out_features))
+        ticket = ctypes.c_int32(-1)
+        _capi.check(lib().ag_model_infer_enqueue(self._h, _ptr(x_host), bs, c, h, w, _ptr(out_host),
+                                                 ctypes.byref(ticket)))
+        return ticket.value
+
+    def infer_wait(self, ticket: int):
+        _capi.check(lib().ag_model_infer_wait(self._h, ticket))
+
     def infer_u8(self, x_host_u8, alpha=1.0 / 255.0, out_host=None):
         """u8 host images [bs,c,h,w] -> alpha * x in the model dtype -> host logits (blocking);
         ≙ images_to_device_and_scale + forward of the reference's MNIST example."""

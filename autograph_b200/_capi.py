@@ -95,6 +95,9 @@ _SIGNATURES = {
                                                POINTER(c_int32), _P]),
     "ag_scaled_cast_u8": (c_int, [_P, c_int, ctypes.c_float, _P, _P, c_int64]),
     "ag_model_infer_u8": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int64, ctypes.c_float, _P]),
+    "ag_model_infer_enqueue": (c_int, [_P, _P, c_int64, c_int64, c_int64, c_int64, _P,
+                                       ctypes.POINTER(ctypes.c_int32)]),
+    "ag_model_infer_wait": (c_int, [_P, ctypes.c_int32]),
     "ag_conv2_relu_max_pool2_forward": (c_int, [_P, c_int, _P, c_int64, c_int64, c_int64, c_int64,
                                                 _P, c_int64, _P, POINTER(ConvOptions), c_int,
                                                 c_int32, c_int32, _P]),

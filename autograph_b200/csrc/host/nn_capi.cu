@@ -87,6 +87,17 @@ struct ag_model {
     cudaEvent_t fork_event = nullptr, join_event[2] = {nullptr, nullptr};
     int slices = 0;  // 0: chosen from the batch size
     bool whole_network = true;  // try the one-kernel form of the network at inference
+    // Pipelined host inference (ag_model_infer_enqueue / _wait): two slots, each with a device
+    // copy of its batch; the copy engine fills one slot on its own stream while the network runs
+    // on the other.
+    struct InferSlot {
+        Tensor x_stage;
+        cudaEvent_t copied = nullptr, done = nullptr;
+        bool busy = false;
+    };
+    InferSlot infer_slots[2];
+    cudaStream_t copy_stream = nullptr;
+    int next_slot = 0;
     std::vector<std::unique_ptr<Layer>> layers;
     std::vector<Parameter *> params;
     std::vector<int64_t> offsets;  // element offset of each parameter in the buckets
@@ -143,6 +154,11 @@ struct ag_model {
             if (join_event[i]) cudaEventDestroy(join_event[i]);
         }
         if (fork_event) cudaEventDestroy(fork_event);
+        for (auto &sl : infer_slots) {
+            if (sl.copied) cudaEventDestroy(sl.copied);
+            if (sl.done) cudaEventDestroy(sl.done);
+        }
+        if (copy_stream) cudaStreamDestroy(copy_stream);
     }
 };
 
@@ -1196,6 +1212,66 @@ int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, i
         cudaError_t e = cudaStreamSynchronize((cudaStream_t)ag_device_stream(model->dev));
         if (e != cudaSuccess)
             throw Error(AG_ERR_CUDA, std::string("cudaStreamSynchronize failed: ") + cudaGetErrorString(e));
+    })
+}
+
+static void infer_enqueue_impl(ag_model *model, const void *x_host, int64_t bs, int64_t c, int64_t h,
+                               int64_t w, void *logits_host, int32_t *ticket) {
+        if (bs <= 0 || c <= 0 || h <= 0 || w <= 0) throw Error(AG_ERR_SHAPE, "bad input shape");
+        if (!x_host) throw Error(AG_ERR_INVALID, "input pointer is null");
+        void *out_dev = pinned_device_pointer(logits_host);
+        if (!is_pinned_host(x_host) || !out_dev)
+            throw Error(AG_ERR_INVALID, "pipelined inference needs pinned host buffers");
+        auto cuda_ok = [](cudaError_t e, const char *what) {
+            if (e != cudaSuccess)
+                throw Error(AG_ERR_CUDA, std::string(what) + " failed: " + cudaGetErrorString(e));
+        };
+        cudaStream_t stream = (cudaStream_t)ag_device_stream(model->dev);
+        if (!model->copy_stream)
+            cuda_ok(cudaStreamCreateWithFlags(&model->copy_stream, cudaStreamNonBlocking), "copy stream");
+        const int idx = model->next_slot;
+        ag_model::InferSlot &sl = model->infer_slots[idx];
+        if (!sl.copied) {
+            cuda_ok(cudaEventCreateWithFlags(&sl.copied, cudaEventDisableTiming), "event");
+            cuda_ok(cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming), "event");
+        }
+        if (sl.busy) throw Error(AG_ERR_INVALID, "both inference slots are in flight: wait for a ticket first");
+        const Shape shape = {bs, c, h, w};
+        if (!sl.x_stage.defined() || sl.x_stage.shape() != shape)
+            sl.x_stage = Tensor::uninit(model->pool, shape, model->dtype);
+        // the slot's previous network pass has been waited for (busy is false), so its copy of
+        // the batch may be overwritten; the copy runs on its own stream
+        cuda_ok(cudaMemcpyAsync(sl.x_stage.data(), x_host, sl.x_stage.nbytes(), cudaMemcpyHostToDevice,
+                                model->copy_stream), "input copy");
+        cuda_ok(cudaEventRecord(sl.copied, model->copy_stream), "event record");
+        cuda_ok(cudaStreamWaitEvent(stream, sl.copied, 0), "event wait");
+        Variable y = forward_chain(model, Variable{sl.x_stage, nullptr}, out_dev);
+        if (y.value.data() != out_dev)
+            cuda_ok(cudaMemcpyAsync(logits_host, y.value.data(), y.value.nbytes(), cudaMemcpyDeviceToHost,
+                                    stream), "output copy");
+        cuda_ok(cudaEventRecord(sl.done, stream), "event record");
+        sl.busy = true;
+        model->next_slot = idx ^ 1;
+        *ticket = idx;
+    }
+
+int ag_model_infer_enqueue(ag_model *model, const void *x_host, int64_t bs, int64_t c, int64_t h,
+                           int64_t w, void *logits_host, int32_t *ticket) {
+    AG_REQUIRE(model && logits_host && ticket, AG_ERR_INVALID, "null argument");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({ infer_enqueue_impl(model, x_host, bs, c, h, w, logits_host, ticket); })
+}
+
+int ag_model_infer_wait(ag_model *model, int32_t ticket) {
+    AG_REQUIRE(model && (ticket == 0 || ticket == 1), AG_ERR_INVALID, "bad ticket");
+    AG_ENTER(model->dev);
+    AG_HOST_GUARD({
+        ag_model::InferSlot &sl = model->infer_slots[ticket];
+        if (!sl.busy) throw Error(AG_ERR_INVALID, "nothing in flight under this ticket");
+        cudaError_t e = cudaEventSynchronize(sl.done);
+        sl.busy = false;
+        if (e != cudaSuccess)
+            throw Error(AG_ERR_CUDA, std::string("cudaEventSynchronize failed: ") + cudaGetErrorString(e));
     })
 }
 

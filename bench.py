@@ -17,7 +17,8 @@ window) and the median window is reported, so that a 20-step run is not one 0.6 
 One JSON line is printed by rank 0.  Besides the contract keys it carries
   roofline      the step's kernel against its binding bound (the FP32 pipe; HBM view inside)
   e2e           the same step through Model.infer with pinned host buffers (copies inside the
-                timed region); e2e_pageable: the same from pageable host memory
+                timed region); e2e_pipelined: two batches in flight through
+                ag_model_infer_enqueue / _wait; e2e_pageable: the same from pageable host memory
   infer_sharded_65536   configs[4a]: 65536 images split evenly over the ranks (strong scaling)
   train_dp      configs[4b]: 100 images per GPU, gradient all-reduce, SGD update
   gemm          the standalone dot sweep (configs[1]) in TFLOP/s, with `gemm_roofline`
@@ -307,6 +308,32 @@ def run_gpu(args):
            "h2d_bytes_per_step": BATCH * 784 * 4, "d2h_bytes_per_step": BATCH * 10 * 4,
            "steps": Ke, "ms_per_step": ms_e2e / Ke, "host_memory": "pinned",
            "repeats_ms_per_step": [w / Ke for w in e2e_windows]}
+    # The serving form of the same call: two batches in flight (ag_model_infer_enqueue / _wait),
+    # the copy engine moving batch i + 1 while the network runs on batch i.  Every step still
+    # has its H2D copy and its D2H logits inside the timed region; what differs from `e2e` is
+    # that a step's result is collected one step later.
+    try:
+        ohs = [torch.empty((BATCH, 10), dtype=torch.float32).pin_memory() for _ in range(2)]
+        tickets = []
+
+        def pstep(i):
+            if len(tickets) == 2:
+                model.infer_wait(tickets.pop(0))
+            tickets.append(model.infer_enqueue(xh[i % 4], ohs[i % 2]))
+
+        for i in range(W):
+            pstep(i)
+        pipe_windows = timed_windows(pstep, Ke)
+        while tickets:
+            model.infer_wait(tickets.pop(0))
+        ms_pipe = float(np.median(pipe_windows))
+        e2e_pipelined = {"value": world * BATCH * Ke / (ms_pipe * 1e-3), "unit": UNIT,
+                         "h2d_bytes_per_step": BATCH * 784 * 4, "d2h_bytes_per_step": BATCH * 10 * 4,
+                         "steps": Ke, "ms_per_step": ms_pipe / Ke, "in_flight": 2,
+                         "host_memory": "pinned",
+                         "repeats_ms_per_step": [w / Ke for w in pipe_windows]}
+    except Exception as exc:
+        e2e_pipelined = {"error": repr(exc)}
     # The same call from pageable host memory (what a caller's Vec hands over): the library
     # stages it through its own pinned buffer.
     try:
@@ -335,7 +362,8 @@ def run_gpu(args):
                    "timing": f"median of {REPEATS} windows of K steps, each window the max over ranks",
                    "peaks": peaks["source"]},
         "repeats_ms_per_step": [w / K for w in windows],
-        "e2e": e2e, "e2e_pageable": e2e_pageable, "gpu_launches": int(launches),
+        "e2e": e2e, "e2e_pipelined": e2e_pipelined, "e2e_pageable": e2e_pageable,
+        "gpu_launches": int(launches),
     }
 
     # configs[4a]: 65536 images sharded evenly by batch, no collective (strong scaling: the

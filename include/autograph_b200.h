@@ -475,6 +475,18 @@ AG_API int ag_model_set_grad_scale(ag_model *model, float scale);
  * (blocking). */
 AG_API int ag_model_infer(ag_model *model, const void *x_host, int64_t bs, int64_t c, int64_t h,
                           int64_t w, void *logits_host);
+/* Pipelined form of ag_model_infer for a caller that keeps two batches in flight (a serving loop):
+ * _enqueue copies the pinned batch to the device on the copy engine's own stream and enqueues the
+ * network behind it (logits land in the pinned logits_host); it returns at once with a ticket
+ * (0 or 1).  _wait blocks until that ticket's logits are in host memory.  At most two tickets are
+ * in flight; while one batch computes, the next one crosses PCIe, so the steady-state rate is
+ * that of the transfer alone.  Both buffers must be pinned (AG_ERR_INVALID otherwise) and must not
+ * be touched until the ticket has been waited for.
+ * ≙ two LeNet5Classifier::infer calls (autograph_backend.rs:44-69) overlapped. */
+AG_API int ag_model_infer_enqueue(ag_model *model, const void *x_host, int64_t bs, int64_t c,
+                                  int64_t h, int64_t w, void *logits_host, int32_t *ticket);
+AG_API int ag_model_infer_wait(ag_model *model, int32_t ticket);
+
 /* The same from u8 images, as the reference's MNIST example feeds its model
  * (examples/neural-network-mnist/src/main.rs:236-243): x = alpha * u8 in the model's dtype, then
  * the forward pass.  A one-kernel network reads the u8 images itself (from pinned host memory:

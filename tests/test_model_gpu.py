@@ -163,6 +163,42 @@ def test_wide_stack_bf16_forward_backward(dev):
     model.close()
 
 
+def test_pipelined_inference_equals_the_blocking_call(dev):
+    """Two batches in flight (the copy of one overlaps the network pass of the other): every
+    batch's logits are those of the blocking call; a third enqueue without a wait, a ticket that
+    is not in flight and pageable buffers are refused."""
+    import autograph_b200 as ag
+    model = ag.Model(dev, ag.LENET5_SPEC, torch.float32, seed=11)
+    rng = np.random.default_rng(8200)
+    xs = [torch.from_numpy(rng.uniform(0, 1, (1000, 1, 28, 28)).astype(np.float32)).pin_memory() for _ in range(5)]
+    want = [model.infer(x).clone() for x in xs]
+    outs = [torch.empty((1000, 10), dtype=torch.float32).pin_memory() for _ in range(2)]
+    for _ in range(2):
+        tickets = []
+        for i, x in enumerate(xs):
+            if len(tickets) == 2:
+                j, t = tickets.pop(0)
+                model.infer_wait(t)
+                assert torch.equal(outs[j % 2], want[j])
+            outs[i % 2].fill_(float("nan"))
+            tickets.append((i, model.infer_enqueue(x, outs[i % 2])))
+        with pytest.raises(ag.AgError):
+            model.infer_enqueue(xs[0], torch.empty((1000, 10)).pin_memory())   # both slots in flight
+        for j, t in tickets:
+            model.infer_wait(t)
+            assert torch.equal(outs[j % 2], want[j])
+    with pytest.raises(ag.AgError):
+        model.infer_wait(0)                                                    # nothing in flight
+    with pytest.raises(ag.AgError):
+        model.infer_enqueue(xs[0].clone(), outs[0])                            # pageable input
+    # another batch size re-sizes the slot
+    small = xs[0][:64].contiguous().pin_memory()
+    o = torch.empty((64, 10), dtype=torch.float32).pin_memory()
+    model.infer_wait(model.infer_enqueue(small, o))
+    assert torch.equal(o, want[0][:64])
+    model.close()
+
+
 def test_learning_rate_schedule_reuses_one_graph(dev):
     """A different learning rate every step: the captured step without the update serves all of
     them (the update follows as a plain launch) and the parameters equal those of the
