@@ -301,13 +301,7 @@ extern "C" int ag_gemm(ag_device *dev, ag_dtype dtype, int64_t m, int64_t k, int
     AG_REQUIRE(off_a >= 0 && off_b >= 0 && off_c >= 0, AG_ERR_INVALID, "negative offset");
     // Small plain products (row-major contiguous operands, alpha = 1, beta = 0) share the
     // latency-oriented kernel with ag_dense_forward.
-    // A bf16 product with at least 128 rows that the tensor cores take goes there (256^3: 10 us on
-    // the latency-oriented kernel, whose CTAs own eight rows each).
-    const bool bf16_tc = dtype == AG_BF16 && m >= 128 && k > 0 &&
-                         tc::gemm_bf16_eligible(m, k, n, (const __nv_bfloat16 *)a + off_a, rsa, csa,
-                                                (const __nv_bfloat16 *)b + off_b, rsb, csb,
-                                                (const __nv_bfloat16 *)c + off_c, rsc, csc);
-    if (!bf16_tc && alpha == 1.f && beta == 0.f && k > 0 && csa == 1 && rsa == k && csb == 1 && rsb == n &&
+    if (alpha == 1.f && beta == 0.f && k > 0 && csa == 1 && rsa == k && csb == 1 && rsb == n &&
         csc == 1 && rsc == n && dense_small::eligible(m, k, n)) {
         if (dtype == AG_F32)
             return dense_small::forward<float>(dev, (const float *)a + off_a, (int)m, (int)k,
