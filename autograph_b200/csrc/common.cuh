@@ -22,10 +22,13 @@ int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)))
 #define AG_CUDA_TRY(expr)                                                                      \
     do {                                                                                       \
         cudaError_t _e = (expr);                                                               \
-        if (_e != cudaSuccess)                                                                 \
+        if (_e != cudaSuccess) {                                                               \
+            /* reported here: it must not also fail the next call's launch check */           \
+            cudaGetLastError();                                                                \
             return ::ag::fail(_e == cudaErrorMemoryAllocation ? AG_ERR_OOM : AG_ERR_CUDA,      \
                               "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, \
                               __LINE__);                                                       \
+        }                                                                                      \
     } while (0)
 
 #define AG_TRY(expr)              \
