@@ -265,7 +265,12 @@ static int launch_lenet(ag_device *dev, const T *x, const uint8_t *x8, float alp
     // launched so that it may overlap the tail of a preceding launch of the same kernel
     // (the kernel itself waits for its predecessor before it reads or writes memory)
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ceil_div(bs, (int64_t)lp.group));
+    int64_t ctas = ceil_div(bs, (int64_t)lp.group);
+    // the group-walking form: f32 images, 16-byte aligned, one CTA per SM
+    lp.persist = lp.persist && sizeof(T) == 4 && x8 == nullptr && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                 ctas > dev->sm_count;
+    if (lp.persist) ctas = dev->sm_count;
+    cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(lenet::kThreads);
     cfg.dynamicSmemBytes = lsmem;
     cfg.stream = dev->stream;
@@ -295,7 +300,7 @@ int forward(ag_device *dev, const T *x, const uint8_t *x8, float alpha, int64_t 
     // dense weights for its 7 images; over the whole batch they are read once per 128-row tile.
     static const int64_t split_batch = [] {
         const char *e = getenv("AG_CHAIN_SPLIT_BATCH");
-        return e ? (int64_t)atoll(e) : (int64_t)8192;
+        return e ? (int64_t)atoll(e) : (int64_t)5120;
     }();
     if (!generic_only && split_batch > 0 && bs >= split_batch) {
         const ag_dtype dtype = sizeof(T) == 4 ? AG_F32 : AG_BF16;

@@ -68,6 +68,7 @@ struct Plan {
     int early;                        // layers [0, early) are copied at kernel start, the rest after conv2
     int w1_off, w2_off, xa_off, xb_off, red_off, bar_off;
     int *status;
+    int persist, in2_off;   // split form: CTAs walk over several groups (second image buffer at in2_off)
     // When set, the kernel stops after the flatten and writes the activations [bs, 256] here
     // (the dense layers then run as separate products over the whole batch).
     void *flat_out;
@@ -92,9 +93,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_abort;
     const int tid = threadIdx.x;
-    const int b0 = blockIdx.x * pl.group;
-    const int nimg = min(pl.group, pl.bs - b0);
+    int b0 = blockIdx.x * pl.group;
+    int nimg = min(pl.group, pl.bs - b0);
     float *s_in = smem + IN_OFF, *s_mid = smem + MID_OFF;
+    // Large f32 batches that stop after the flatten: fewer CTAs than groups, each CTA walks over
+    // its groups and fetches the next group's images (asynchronous copies into a second buffer)
+    // while it convolves the current one; the filter banks are staged once.
+    const bool persist = sizeof(T) == 4 && pl.persist != 0 && pl.flat_out != nullptr && x8 == nullptr;
+    float *s_in_next = smem + pl.in2_off;
+    int grp = blockIdx.x;
+    const int ngroups = (pl.bs + pl.group - 1) / pl.group;
     float *s_w1 = smem + pl.w1_off, *s_w2 = smem + pl.w2_off;
     float *xa = smem + pl.xa_off, *xb = smem + pl.xb_off;
     const uint32_t bar0 = tc::smem_u32(smem + pl.bar_off), bar1 = bar0 + 8;
@@ -170,6 +178,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     AG_STAMP(1);
 
+    for (;;) {
+    if (persist && grp + (int)gridDim.x < ngroups) {
+        const int nb0 = (grp + (int)gridDim.x) * pl.group;
+        const int total = min(pl.group, pl.bs - nb0) * (IH * IW / 4);
+        const float *src = reinterpret_cast<const float *>(x) + (int64_t)nb0 * (IH * IW);
+        for (int q = tid; q < total; q += kThreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tc::smem_u32(s_in_next + 4 * q)),
+                         "l"(src + 4 * q)
+                         : "memory");
+    }
     // ---- conv1 + relu + pool: item = (image, 2 rows x 12 columns, channel pair).  The two
     // channels of a pair are the halves of one fma.rn.f32x2 (the pixel's value in both halves of
     // the multiplier): per patch row 120 packed FMAs and 20 moves instead of 240 FFMAs, the same
@@ -352,7 +370,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int g = i >> 8, k = i & (kFlat - 1);
             flat[i] = from_f32<T>(xa[k * ROWS + g]);   // exact: the values are already T's
         }
-        return;
+        if (!persist || grp + (int)gridDim.x >= ngroups) return;
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();   // the next group's images have landed; xa and s_mid may be rewritten
+        grp += (int)gridDim.x;
+        b0 = grp * pl.group;
+        nimg = min(pl.group, pl.bs - b0);
+        float *t = s_in;
+        s_in = s_in_next;
+        s_in_next = t;
+        continue;
+    }
+    break;
     }
 
     // ---- the later dense layers' weights go where the convolutions' buffers were
@@ -409,6 +438,8 @@ inline size_t make_plan(Plan *pl, ag_dtype dtype, int64_t bs, int64_t ic, int64_
                         int n_conv, const ag_conv_stage *stages, int n_dense,
                         const dense_small::ChainLayer *layers, void *flat_out = nullptr) {
     pl->flat_out = flat_out;
+    pl->persist = 0;
+    pl->in2_off = 0;
     if (n_conv != 2 || ic != 1 || ih != IH || iw != IW) return 0;
     if (bs <= 0 || bs > (int64_t)kGroup * 0x7fffffff / 8) return 0;
     const int ocs[2] = {C1, C2};
@@ -451,6 +482,12 @@ inline size_t make_plan(Plan *pl, ag_dtype dtype, int64_t bs, int64_t ic, int64_
     if (CONV_END + fixed + l0_floats > kMaxFloats) l0_floats = 0;   // layer 0 stays in global memory
     const int spare = kMaxFloats - (CONV_END + fixed + l0_floats);
     if (spare < 0 || pl->chain.red_floats > CONV_END + spare) return 0;
+    // the second image buffer of the group-walking form sits in the spare region (nothing else
+    // uses it when the dense layers do not run in this kernel)
+    if (flat_out != nullptr && spare >= kGroup * IH * IW) {
+        pl->persist = 1;
+        pl->in2_off = CONV_END;
+    }
     int off = CONV_END + spare;
     auto take = [&](int floats) {
         const int at = off;
