@@ -266,9 +266,9 @@ static int launch_lenet(ag_device *dev, const T *x, const uint8_t *x8, float alp
     // (the kernel itself waits for its predecessor before it reads or writes memory)
     cudaLaunchConfig_t cfg = {};
     int64_t ctas = ceil_div(bs, (int64_t)lp.group);
-    // the group-walking form: f32 images, 16-byte aligned, one CTA per SM
-    lp.persist = lp.persist && sizeof(T) == 4 && x8 == nullptr && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
-                 ctas > dev->sm_count;
+    // the group-walking form: 16-byte aligned images and groups, one CTA per SM
+    lp.persist = lp.persist && x8 == nullptr && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                 (lp.group * 784 * sizeof(T)) % 16 == 0 && ctas > dev->sm_count;
     if (lp.persist) ctas = dev->sm_count;
     cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(lenet::kThreads);

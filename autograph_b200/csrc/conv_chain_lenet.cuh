@@ -96,10 +96,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     int b0 = blockIdx.x * pl.group;
     int nimg = min(pl.group, pl.bs - b0);
     float *s_in = smem + IN_OFF, *s_mid = smem + MID_OFF;
-    // Large f32 batches that stop after the flatten: fewer CTAs than groups, each CTA walks over
+    // Large batches that stop after the flatten: fewer CTAs than groups, each CTA walks over
     // its groups and fetches the next group's images (asynchronous copies into a second buffer)
     // while it convolves the current one; the filter banks are staged once.
-    const bool persist = sizeof(T) == 4 && pl.persist != 0 && pl.flat_out != nullptr && x8 == nullptr;
+    const bool persist = pl.persist != 0 && pl.flat_out != nullptr && x8 == nullptr;
     float *s_in_next = smem + pl.in2_off;
     int grp = blockIdx.x;
     const int ngroups = (pl.bs + pl.group - 1) / pl.group;
@@ -180,12 +180,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     for (;;) {
     if (persist && grp + (int)gridDim.x < ngroups) {
+        // 16-byte pieces of the next group's images as they lie in memory (f32: the buffer the
+        // convolution will read; bf16: raw, converted when the current group is done)
         const int nb0 = (grp + (int)gridDim.x) * pl.group;
-        const int total = min(pl.group, pl.bs - nb0) * (IH * IW / 4);
-        const float *src = reinterpret_cast<const float *>(x) + (int64_t)nb0 * (IH * IW);
+        const int total = min(pl.group, pl.bs - nb0) * (IH * IW * (int)sizeof(T) / 16);
+        const char *src = reinterpret_cast<const char *>(x + (int64_t)nb0 * (IH * IW));
         for (int q = tid; q < total; q += kThreads)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tc::smem_u32(s_in_next + 4 * q)),
-                         "l"(src + 4 * q)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(tc::smem_u32(s_in_next) + 16 * q),
+                         "l"(src + 16 * q)
                          : "memory");
     }
     // ---- conv1 + relu + pool: item = (image, 2 rows x 12 columns, channel pair).  The two
@@ -376,9 +378,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         grp += (int)gridDim.x;
         b0 = grp * pl.group;
         nimg = min(pl.group, pl.bs - b0);
-        float *t = s_in;
-        s_in = s_in_next;
-        s_in_next = t;
+        if constexpr (sizeof(T) == 4) {
+            float *t = s_in;
+            s_in = s_in_next;
+            s_in_next = t;
+        } else {
+            const T *raw = reinterpret_cast<const T *>(s_in_next);
+            for (int i = tid; i < nimg * (IH * IW) / 4; i += kThreads)
+                direct::load4_to_f32<T>(raw + 4 * i, s_in + 4 * i);
+            __syncthreads();
+        }
         continue;
     }
     break;
