@@ -127,23 +127,50 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------- CPU baseline
-def cpu_forward_rate(seconds: float, min_steps: int = 2):
-    """Images/s of the oracle's LeNet5 forward (direct f32 conv restating conv_direct.rs,
-    threaded GEMM) on all host cores, on batches of 1000 for about `seconds`."""
+def cpu_forward_windows(steps: int, warm_s: float, sample_s: float, warm_steps: int = 1):
+    """The oracle's LeNet5 forward (direct f32 conv restating conv_direct.rs, threaded GEMM) on
+    all host cores, batches of 1000: warms up for warm_s seconds, then times windows of `steps`
+    passes until there are REPEATS of them and sample_s seconds have passed.  Returns the list of
+    window times and the thread count.  Both the reference arm and the GPU arm's cpu_baseline
+    are measured by this one routine."""
     import oracle
     from oracle import models
     oracle.use_all_cores()
+    # The activations of a pass are fresh 14 MB numpy arrays.  glibc serves blocks of that size
+    # with mmap until it has seen such blocks freed, so a fresh process pays a round of page
+    # faults per pass (measured: 8.1 ms per pass against 7.0 ms in a process that had allocated
+    # and freed large blocks before).  Keep them on the heap in both arms.
+    try:
+        import ctypes
+        libc = ctypes.CDLL("libc.so.6")
+        libc.mallopt(-3, 1 << 30)   # M_MMAP_THRESHOLD
+        libc.mallopt(-1, 1 << 30)   # M_TRIM_THRESHOLD
+    except OSError:
+        pass
     P = models.init_params(models.LENET5, 2000)
     x = np.random.default_rng(1000).uniform(0, 1, (BATCH, 1, 28, 28)).astype(np.float32)
-    models.forward(models.LENET5, P, x, fast=True)  # warm-up
-    n, t0 = 0, time.perf_counter()
-    while True:
+    t_warm = time.perf_counter()
+    done = 0
+    while done < max(warm_steps, 1) or time.perf_counter() - t_warm < warm_s:
         models.forward(models.LENET5, P, x, fast=True)
-        n += 1
-        dt = time.perf_counter() - t0
-        if n >= min_steps and dt >= seconds:
+        done += 1
+    windows = []
+    t_begin = time.perf_counter()
+    while len(windows) < REPEATS or (time.perf_counter() - t_begin < sample_s and len(windows) < 400):
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            models.forward(models.LENET5, P, x, fast=True)
+        windows.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > 120.0:
             break
-    return n * BATCH / dt, oracle.num_threads(), n, dt
+    return windows, oracle.num_threads()
+
+
+def cpu_forward_rate(seconds: float, min_steps: int = 2):
+    """Images/s (median window), thread count, passes and seconds of cpu_forward_windows."""
+    windows, cores = cpu_forward_windows(20, 1.0, seconds)
+    dt = float(np.median(windows))
+    return 20 * BATCH / dt, cores, 20 * len(windows), float(sum(windows))
 
 
 def cpu_train_rate(seconds: float):
@@ -171,32 +198,13 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    import oracle
-    from oracle import models
-    oracle.use_all_cores()
-    P = models.init_params(models.LENET5, 2000)
-    x = np.random.default_rng(1000).uniform(0, 1, (BATCH, 1, 28, 28)).astype(np.float32)
-    # Warm up for at least three seconds (thread pool, caches, host clocks: a cold start reads
-    # about 20 % low), then time windows of K steps until there are REPEATS of them and eight
-    # seconds have passed; the median window counts.
-    t_warm = time.perf_counter()
-    done = 0
-    while done < max(args.warmup, 1) or time.perf_counter() - t_warm < 3.0:
-        models.forward(models.LENET5, P, x, fast=True)
-        done += 1
+    # Warm up for at least three seconds (thread pool, caches, host clocks), then time windows of
+    # K steps until there are REPEATS of them and eight seconds have passed; the median window
+    # counts.
     steps = min(args.steps, 2000)
-    windows = []
-    t_begin = time.perf_counter()
-    while len(windows) < REPEATS or (time.perf_counter() - t_begin < 8.0 and len(windows) < 400):
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            models.forward(models.LENET5, P, x, fast=True)
-        windows.append(time.perf_counter() - t0)
-        if time.perf_counter() - t_begin > 120.0:
-            break
+    windows, cores = cpu_forward_windows(steps, 3.0, 8.0, args.warmup)
     dt = float(np.median(windows))
     value = steps * BATCH / dt
-    cores = oracle.num_threads()
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
@@ -422,7 +430,8 @@ def run_gpu(args):
         secs = 3.0 if args.quick else 12.0
         rate, cores, n, dt = cpu_forward_rate(secs)
         line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": f"{n} forward passes of 1000 images in {dt:.1f} s"}
+                                "sample": f"median window of {n} forward passes of 1000 images "
+                                          f"in {dt:.1f} s (windows of 20)"}
         if not args.quick:
             try:
                 sps, cores, n, dt = cpu_train_rate(4.0)
