@@ -154,6 +154,11 @@ struct ag_model {
             if (join_event[i]) cudaEventDestroy(join_event[i]);
         }
         if (fork_event) cudaEventDestroy(fork_event);
+        if (copy_stream) {
+            // batches still in flight under a ticket: let their copies and network passes finish
+            cudaStreamSynchronize(copy_stream);
+            cudaStreamSynchronize((cudaStream_t)ag_device_stream(dev));
+        }
         for (auto &sl : infer_slots) {
             if (sl.copied) cudaEventDestroy(sl.copied);
             if (sl.done) cudaEventDestroy(sl.done);
