@@ -32,40 +32,13 @@ __global__ void __launch_bounds__(1024)
     }
     __syncthreads();
 
-    const int n = threadIdx.x % np, slice = threadIdx.x / np;
-    float acc[ROWS];
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
-    if (n < N && slice < slices) {
-        const int k0 = slice * kchunk, k1 = min(K, k0 + kchunk);
-        const T *wp = w + (int64_t)k0 * N + n;
-#pragma unroll 8
-        for (int k = k0; k < k1; ++k, wp += N) {
-            const float wv = to_f32(*wp);
-            const float4 a = *reinterpret_cast<const float4 *>(xs + k * ROWS);
-            const float4 b = *reinterpret_cast<const float4 *>(xs + k * ROWS + 4);
-            acc[0] = fmaf(a.x, wv, acc[0]); acc[1] = fmaf(a.y, wv, acc[1]);
-            acc[2] = fmaf(a.z, wv, acc[2]); acc[3] = fmaf(a.w, wv, acc[3]);
-            acc[4] = fmaf(b.x, wv, acc[4]); acc[5] = fmaf(b.y, wv, acc[5]);
-            acc[6] = fmaf(b.z, wv, acc[6]); acc[7] = fmaf(b.w, wv, acc[7]);
-        }
-    }
-    if (slice < slices) {
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) red[(slice * ROWS + r) * np + n] = acc[r];
-    }
-    __syncthreads();
-
-    for (int i = threadIdx.x; i < ROWS * np; i += blockDim.x) {
-        const int r = i / np, c = i - r * np;
-        if (r >= rows || c >= N) continue;
-        float s = 0.f;
-        for (int sl = 0; sl < slices; ++sl) s += red[(sl * ROWS + r) * np + c];
-        float v = to_f32(from_f32<T>(s));
-        if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, to_f32(bias[c]))));
-        if (relu) v = (v >= 0.f) ? v : 0.f;
-        y[(int64_t)(m0 + r) * N + c] = from_f32<T>(v);
-    }
+    // one layer of the chain code: the same sums in the same order as inside every fused kernel
+    ChainStep st;
+    st.w = w; st.bias = bias;
+    st.K = K; st.N = N; st.np = np; st.slices = slices; st.kchunk = kchunk; st.relu = relu;
+    st.pre = nullptr; st.act = nullptr;
+    st.transposed = 0; st.gate = nullptr;
+    chain_layer<T>(st, w, xs, nullptr, red, m0, rows, true, y);
 }
 
 bool eligible(int64_t m, int64_t k, int64_t n) {

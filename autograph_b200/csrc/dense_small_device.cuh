@@ -136,6 +136,75 @@ __device__ __forceinline__ void load2_as(const __nv_bfloat16 *p, float &a, float
     }
 }
 
+template <bool SMEM>
+__device__ __forceinline__ float load1_as(const float *p) {
+    if constexpr (SMEM) {
+        float v;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+        return v;
+    } else {
+        return *p;
+    }
+}
+template <bool SMEM>
+__device__ __forceinline__ float load1_as(const __nv_bfloat16 *p) {
+    if constexpr (SMEM) {
+        unsigned short v;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+        return __uint_as_float((uint32_t)v << 16);
+    } else {
+        return to_f32(*p);
+    }
+}
+
+// A layer with few outputs (the 84 -> 10 classifier head): split over (column, k slice) it is
+// all barriers and reduction.  Here every output (row, column) belongs to four adjacent lanes;
+// lane q adds the products of k = q, q + 4, ... in k order and the four sums are added as
+// (p0 + p1) + (p2 + p3) by two shuffles -- no scratch, one barrier.  The order does not depend
+// on the CTA size, and every kernel that runs such a layer comes through here, so the bits are
+// the same everywhere.
+__device__ __forceinline__ bool narrow_step(const ChainStep &st) {
+    return !st.transposed && st.gate == nullptr && st.N <= 16 && st.K <= 1024;
+}
+
+template <class T, bool SMEM>
+__device__ __forceinline__ void narrow_layer(const ChainStep &st, const T *w, const float *xa, float *xb,
+                                             int m0, int rows, bool last, T *__restrict__ y) {
+    const T *bias = reinterpret_cast<const T *>(st.bias);
+    const int total = ROWS * st.N * 4;
+    const int padded = (total + 31) & ~31;   // whole warps take part in the shuffles
+    for (int it = threadIdx.x; it < padded; it += blockDim.x) {
+        const bool live = it < total;
+        const int q = it & 3, o = it >> 2;
+        const int c = live ? o % st.N : 0, r = live ? o / st.N : 0;
+        float p = 0.f;
+        float bv = 0.f;
+        if (live) {
+            if (bias != nullptr && q == 0) bv = to_f32(bias[c]);   // in flight during the sums
+            const T *wp = w + c;
+#pragma unroll 4
+            for (int k = q; k < st.K; k += 4)
+                p = fmaf(xa[k * ROWS + r], load1_as<SMEM>(wp + (int64_t)k * st.N), p);
+        }
+        p += __shfl_xor_sync(0xffffffffu, p, 1);
+        p += __shfl_xor_sync(0xffffffffu, p, 2);
+        if (!live || q != 0) continue;
+        float v = to_f32(from_f32<T>(p));
+        if (bias != nullptr) v = to_f32(from_f32<T>(__fadd_rn(v, bv)));
+        if (st.pre != nullptr && r < rows)
+            reinterpret_cast<T *>(st.pre)[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
+        if (st.relu) v = (v >= 0.f) ? v : 0.f;
+        if (st.act != nullptr && r < rows)
+            reinterpret_cast<T *>(st.act)[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
+        if (last) {
+            if (y != nullptr && r < rows) y[(int64_t)(m0 + r) * st.N + c] = from_f32<T>(v);
+        } else {
+            xb[c * ROWS + r] = v;
+        }
+    }
+    __syncthreads();
+}
+
 // One layer of the chain: xa [K][ROWS] -> xb [N][ROWS] (or y for the last layer).  `w` is the
 // layer's weight matrix as the kernel should read it: st.w, or a copy of it in shared memory.
 // QUADS: a work item is four adjacent columns x four rows (half of ROWS) where the layer allows
@@ -147,6 +216,10 @@ template <class T, bool QUADS = false, bool SMEM = false>
 __device__ __forceinline__ void chain_layer(const ChainStep &st, const T *w, const float *xa,
                                             float *xb, float *red, int m0, int rows, bool last,
                                             T *__restrict__ y) {
+    if (narrow_step(st)) {
+        narrow_layer<T, SMEM>(st, w, xa, xb, m0, rows, last, y);
+        return;
+    }
     {
         const T *bias = reinterpret_cast<const T *>(st.bias);
         const bool quads = QUADS && !st.transposed && (st.N % 4 == 0) &&
